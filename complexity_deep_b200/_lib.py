@@ -1,0 +1,74 @@
+"""ctypes binding of libcdeep.so (include/cdeep.h).
+
+There is no fallback: if the library is missing the import of any accelerated module
+raises, and every non-zero status code becomes a Python exception.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_char_p, c_float, c_int, c_size_t, c_void_p
+
+LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libcdeep.so")
+
+ABI_VERSION = 1
+
+# name -> (restype, argtypes); mirrors include/cdeep.h one to one
+SIGNATURES = {
+    "cd_version": (c_int, []),
+    "cd_error_string": (c_char_p, [c_int]),
+    "cd_last_cuda_error": (c_char_p, []),
+    "cd_status_fetch": (c_int, [ctypes.POINTER(c_int)]),
+    "cd_route_workspace_bytes": (c_size_t, [c_int, c_int]),
+    "cd_route": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                         c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "cd_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
+                           c_int, c_int, c_void_p]),
+    "cd_gather_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "cd_qk_norm_rope": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int,
+                                c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "cd_gate_up_packed_rows": (c_int, [c_int, c_int]),
+    "cd_moe_up": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+                          c_int, c_void_p]),
+    "cd_moe_down": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
+                            c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "cd_mu_qkv": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                          c_void_p]),
+    "cd_mu_proj": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_float, c_int, c_float, c_float,
+                           c_void_p, c_int, c_int, c_void_p]),
+    "cd_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+}
+
+_lib = None
+
+
+class CdeepError(RuntimeError):
+    """A libcdeep entry point returned a non-zero status."""
+
+
+def load() -> ctypes.CDLL:
+    """Loads the library once; raises when it is missing or its ABI version differs."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m complexity_deep_b200.build` "
+            "(nvcc, sm_100a). There is no CPU or PyTorch fallback for these kernels.")
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if a declared symbol is not exported
+        fn.restype = res
+        fn.argtypes = args
+    if lib.cd_version() != ABI_VERSION:
+        raise ImportError(f"libcdeep ABI {lib.cd_version()} != expected {ABI_VERSION}; rebuild")
+    _lib = lib
+    return lib
+
+
+def check(status: int, what: str) -> None:
+    if status != 0:
+        lib = load()
+        msg = lib.cd_error_string(status).decode()
+        detail = lib.cd_last_cuda_error().decode() if status == 2 else ""
+        raise CdeepError(f"{what}: {msg}" + (f" ({detail})" if detail else ""))

@@ -1,0 +1,131 @@
+"""Grouped-query attention with mu-guided projections — drop-in for the reference's
+``ComplexityAttention`` (complexity_deep/core/attention.py:34-199): same constructor, same
+parameters (q/k/v/o_proj, mu_to_q/k/v, q_norm/k_norm, rotary_emb), same forward signature
+and the same scaled_dot_product_attention call (including its ``is_causal`` rule).
+
+What changes is how q, k, v are produced:
+  * one K-concatenated GEMM ``[x | mu_prev] @ [W ; W_mu]^T`` (cd_mu_qkv) reading x and
+    mu_prev in place and the stacked weights from a cache, instead of a ``torch.cat`` of the
+    activations, three ``torch.cat`` of the weights and three GEMMs per call (:120-127);
+  * Q/K RMSNorm and RoPE applied in place by one kernel (cd_qk_norm_rope) instead of
+    ~10 elementwise passes (:138-155);
+  * grouped KV heads are handed to SDPA with ``enable_gqa`` instead of being copied by
+    ``repeat_interleave`` (:164-165) — the same arithmetic without the copies;
+  * ``o_proj`` runs on the tcgen05 GEMM, optionally with the residual add fused.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .. import ops
+from ._cache import DerivedCache
+from .rotary import RotaryEmbedding
+
+
+class ComplexityAttention(nn.Module):
+    def __init__(
+        self,
+        hidden_size: int,
+        num_attention_heads: int,
+        num_key_value_heads: int,
+        max_position_embeddings: int = 2048,
+        rope_theta: float = 10000.0,
+        attention_dropout: float = 0.0,
+        use_qk_norm: bool = True,
+    ):
+        super().__init__()
+        if hidden_size % num_attention_heads or num_attention_heads % num_key_value_heads:
+            raise AssertionError("hidden_size / heads / kv heads are not divisible")
+        self.hidden_size = hidden_size
+        self.num_heads = num_attention_heads
+        self.num_kv_heads = num_key_value_heads
+        self.head_dim = hidden_size // num_attention_heads
+        self.num_kv_groups = num_attention_heads // num_key_value_heads
+        q_dim = self.num_heads * self.head_dim
+        kv_dim = self.num_kv_heads * self.head_dim
+
+        self.q_proj = nn.Linear(hidden_size, q_dim, bias=False)
+        self.k_proj = nn.Linear(hidden_size, kv_dim, bias=False)
+        self.v_proj = nn.Linear(hidden_size, kv_dim, bias=False)
+        self.o_proj = nn.Linear(q_dim, hidden_size, bias=False)
+        self.mu_to_q = nn.Linear(hidden_size, q_dim, bias=False)
+        self.mu_to_k = nn.Linear(hidden_size, kv_dim, bias=False)
+        self.mu_to_v = nn.Linear(hidden_size, kv_dim, bias=False)
+
+        self.use_qk_norm = use_qk_norm
+        if use_qk_norm:
+            self.q_norm = nn.RMSNorm(self.head_dim, eps=1e-6)
+            self.k_norm = nn.RMSNorm(self.head_dim, eps=1e-6)
+        self.rotary_emb = RotaryEmbedding(self.head_dim, max_seq_len=max_position_embeddings,
+                                          theta=rope_theta)
+        self.attention_dropout = attention_dropout
+        self._derived = DerivedCache()
+
+    # ------------------------------------------------------------------ stacked weights
+    def _w_qkv(self) -> torch.Tensor:
+        src = (self.q_proj.weight, self.k_proj.weight, self.v_proj.weight)
+        return self._derived.get("w_qkv", src, lambda: torch.cat([w.detach() for w in src], 0))
+
+    def _w_mu(self) -> torch.Tensor:
+        src = (self.mu_to_q.weight, self.mu_to_k.weight, self.mu_to_v.weight)
+        return self._derived.get("w_mu", src, lambda: torch.cat([w.detach() for w in src], 0))
+
+    # ------------------------------------------------------------------ forward
+    def _attend(self, hidden_states, attention_mask, past_key_value, use_cache, mu_prev):
+        """Everything up to (not including) o_proj; returns ([T, q_dim], new_kv)."""
+        B, S, H = hidden_states.shape
+        hq, hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
+        x2 = hidden_states.reshape(B * S, H).contiguous()
+        mu2 = None
+        if mu_prev is not None:
+            mu2 = mu_prev.reshape(B * S, H).contiguous()  # materialises a broadcast mu_init
+        qkv = ops.mu_qkv(x2, mu2, self._w_qkv(), self._w_mu() if mu2 is not None else None)
+
+        past_len = past_key_value[0].shape[2] if past_key_value is not None else 0
+        cos, sin = self.rotary_emb.tables_fp32(past_len + S)
+        ops.qk_norm_rope_(qkv, self.q_norm.weight if self.use_qk_norm else None,
+                          self.k_norm.weight if self.use_qk_norm else None, cos, sin, 1e-6, S,
+                          past_len, hq, hkv, D)
+
+        q = qkv[:, : hq * D].view(B, S, hq, D).transpose(1, 2)
+        k = qkv[:, hq * D: (hq + hkv) * D].view(B, S, hkv, D).transpose(1, 2)
+        v = qkv[:, (hq + hkv) * D:].view(B, S, hkv, D).transpose(1, 2)
+        if past_key_value is not None:
+            k = torch.cat([past_key_value[0], k], dim=2)
+            v = torch.cat([past_key_value[1], v], dim=2)
+        new_kv = (k, v) if use_cache else None
+
+        attn = F.scaled_dot_product_attention(
+            q, k, v,
+            attn_mask=attention_mask,
+            dropout_p=self.attention_dropout if self.training else 0.0,
+            is_causal=(attention_mask is None),
+            enable_gqa=self.num_kv_groups > 1,
+        )
+        return attn.transpose(1, 2).reshape(B * S, hq * D).contiguous(), new_kv
+
+    def forward(
+        self,
+        hidden_states: torch.Tensor,
+        attention_mask: Optional[torch.Tensor] = None,
+        past_key_value: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+        use_cache: bool = False,
+        mu_prev: Optional[torch.Tensor] = None,
+    ) -> Tuple[torch.Tensor, Optional[Tuple[torch.Tensor, torch.Tensor]]]:
+        B, S, H = hidden_states.shape
+        attn, new_kv = self._attend(hidden_states, attention_mask, past_key_value, use_cache,
+                                    mu_prev)
+        return ops.linear(attn, self.o_proj.weight).view(B, S, H), new_kv
+
+    def forward_with_residual(self, hidden_states, residual, attention_mask=None,
+                              past_key_value=None, use_cache=False, mu_prev=None):
+        """Same as forward, returning ``residual + o_proj(attn)`` from the GEMM epilogue."""
+        B, S, H = hidden_states.shape
+        attn, new_kv = self._attend(hidden_states, attention_mask, past_key_value, use_cache,
+                                    mu_prev)
+        out = ops.linear(attn, self.o_proj.weight, residual.reshape(B * S, H))
+        return out.view(B, S, H), new_kv

@@ -1,0 +1,153 @@
+"""Decoder block and mu guidance — drop-ins for the reference's ``TransformerBlock`` and
+``MuGuidance`` (complexity_deep/core/layer.py:27-190): same constructors, same sub-module
+names (input_layernorm, self_attn, post_attention_layernorm, mlp, mu_guidance), same
+forward signature and return triple.
+
+``TransformerBlock.forward`` has two routes that produce the same values:
+  * the fused route (default): the attention residual add runs in o_proj's epilogue, the
+    post-attention RMSNorm writes its rows straight into expert-sorted order, and the MoE
+    down-projection's epilogue un-permutes, combines shared + routed and adds the residual;
+  * the module route, taken when a caller has registered hooks on a sub-module (analysis
+    scripts hook ``layer.mlp``): each sub-module is then invoked through ``__call__`` with
+    the reference's inputs and outputs, and the residual adds are separate.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+import torch.nn as nn
+
+from .. import ops
+from .attention import ComplexityAttention
+from .mlp import SwiGLU
+from .normalization import RMSNorm
+from .token_routed_mlp import TokenRoutedMLP
+
+
+def _has_hooks(m: nn.Module) -> bool:
+    return bool(m._forward_hooks or m._forward_pre_hooks or m._backward_hooks
+                or getattr(m, "_forward_hooks_with_kwargs", None)
+                or getattr(m, "_forward_pre_hooks_with_kwargs", None))
+
+
+class MuGuidance(nn.Module):
+    """mu_contextual = clamp(mu, mu_min, mu_max) + mu_proj(hidden_states)  (layer.py:54-61)."""
+
+    def __init__(self, hidden_size: int, mu_min: float = 0.0, mu_max: float = 2.0):
+        super().__init__()
+        self.mu_min, self.mu_max = mu_min, mu_max
+        self.mu = nn.Parameter(torch.full((hidden_size,), (mu_min + mu_max) / 2))
+        self.mu_proj = nn.Linear(hidden_size, hidden_size, bias=False)
+        nn.init.zeros_(self.mu_proj.weight)
+
+    def forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
+        shape = hidden_states.shape
+        h2 = hidden_states.reshape(-1, shape[-1]).contiguous()
+        return ops.mu_proj(h2, self.mu_proj.weight, self.mu, self.mu_min, self.mu_max).view(shape)
+
+
+class TransformerBlock(nn.Module):
+    def __init__(
+        self,
+        hidden_size: int,
+        intermediate_size: int,
+        num_attention_heads: int,
+        num_key_value_heads: int,
+        max_position_embeddings: int = 2048,
+        rms_norm_eps: float = 1e-6,
+        rope_theta: float = 10000.0,
+        attention_dropout: float = 0.0,
+        use_token_routed_mlp: bool = True,
+        num_experts: int = 4,
+        vocab_size: int = 100_000,
+        shared_expert: bool = True,
+        token_frequencies: Optional[torch.Tensor] = None,
+        use_qk_norm: bool = True,
+        use_mu_guidance: bool = True,
+    ):
+        super().__init__()
+        self.hidden_size = hidden_size
+        self.use_token_routed_mlp = use_token_routed_mlp
+        self.input_layernorm = RMSNorm(hidden_size, eps=rms_norm_eps)
+        self.self_attn = ComplexityAttention(
+            hidden_size=hidden_size,
+            num_attention_heads=num_attention_heads,
+            num_key_value_heads=num_key_value_heads,
+            max_position_embeddings=max_position_embeddings,
+            rope_theta=rope_theta,
+            attention_dropout=attention_dropout,
+            use_qk_norm=use_qk_norm,
+        )
+        self.post_attention_layernorm = RMSNorm(hidden_size, eps=rms_norm_eps)
+        if use_token_routed_mlp:
+            self.mlp = TokenRoutedMLP(
+                hidden_size=hidden_size,
+                intermediate_size=intermediate_size,
+                num_experts=num_experts,
+                vocab_size=vocab_size,
+                shared_expert=shared_expert,
+                token_frequencies=token_frequencies,
+            )
+        else:
+            self.mlp = SwiGLU(hidden_size=hidden_size, intermediate_size=intermediate_size)
+        self.use_mu_guidance = use_mu_guidance
+        self.mu_guidance = MuGuidance(hidden_size=hidden_size) if use_mu_guidance else None
+
+    def _fusable(self, token_ids) -> bool:
+        subs = [self.input_layernorm, self.self_attn, self.post_attention_layernorm, self.mlp]
+        if any(_has_hooks(m) for m in subs):
+            return False
+        return not (self.use_token_routed_mlp and token_ids is None)
+
+    def forward(
+        self,
+        hidden_states: torch.Tensor,
+        attention_mask: Optional[torch.Tensor] = None,
+        past_key_value: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+        use_cache: bool = False,
+        token_ids: Optional[torch.Tensor] = None,
+        mu_prev: Optional[torch.Tensor] = None,
+    ) -> Tuple[torch.Tensor, Optional[Tuple[torch.Tensor, torch.Tensor]], Optional[torch.Tensor]]:
+        if self._fusable(token_ids):
+            hidden_states, new_kv = self._forward_fused(
+                hidden_states, attention_mask, past_key_value, use_cache, token_ids, mu_prev)
+        else:
+            residual = hidden_states
+            hidden_states = self.input_layernorm(hidden_states)
+            hidden_states, new_kv = self.self_attn(
+                hidden_states, attention_mask=attention_mask, past_key_value=past_key_value,
+                use_cache=use_cache, mu_prev=mu_prev)
+            hidden_states = residual + hidden_states
+            residual = hidden_states
+            hidden_states = self.post_attention_layernorm(hidden_states)
+            if self.use_token_routed_mlp:
+                hidden_states = self.mlp(hidden_states, token_ids=token_ids)
+            else:
+                hidden_states = self.mlp(hidden_states)
+            hidden_states = residual + hidden_states
+
+        mu_contextual = self.mu_guidance(hidden_states) if self.mu_guidance is not None else None
+        return hidden_states, new_kv, mu_contextual
+
+    def _forward_fused(self, hidden_states, attention_mask, past_key_value, use_cache, token_ids,
+                       mu_prev):
+        B, S, H = hidden_states.shape
+        h0 = hidden_states.reshape(B * S, H).contiguous()
+        ln1 = self.input_layernorm
+        normed = ops.rmsnorm(h0, ln1.weight, ln1.eps).view(B, S, H)
+        # h1 = h0 + o_proj(attention(...)): residual added in the GEMM epilogue
+        h1, new_kv = self.self_attn.forward_with_residual(
+            normed, h0, attention_mask=attention_mask, past_key_value=past_key_value,
+            use_cache=use_cache, mu_prev=mu_prev)
+        h1 = h1.view(B * S, H)
+        ln2 = self.post_attention_layernorm
+        if self.use_token_routed_mlp:
+            routing = self.mlp.routing(token_ids)
+            # normalised rows land directly in expert-sorted order
+            x_sorted = ops.rmsnorm(h1, ln2.weight, ln2.eps, dst_rows=routing.inv_perm)
+            h2 = self.mlp.forward_sorted(x_sorted, routing, residual=h1)
+        else:
+            x = ops.rmsnorm(h1, ln2.weight, ln2.eps)
+            h2 = self.mlp._run(x, residual=h1)
+        return h2.view(B, S, H), new_kv

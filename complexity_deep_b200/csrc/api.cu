@@ -1,0 +1,241 @@
+// extern "C" entry points of libcdeep.so (declared in include/cdeep.h).
+#include <cstdio>
+#include <cuda_runtime.h>
+#include "../../include/cdeep.h"
+#include "gemm_sm100.cuh"
+#include "kernels.h"
+
+namespace cdeep {
+thread_local char g_cuda_err[256] = "";
+int cuda_fail(cudaError_t e, const char* what) {
+  snprintf(g_cuda_err, sizeof(g_cuda_err), "%s: %s", what, cudaGetErrorString(e));
+  return CD_ERR_CUDA;
+}
+}  // namespace cdeep
+
+using namespace cdeep;
+
+static inline cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+extern "C" {
+
+int cd_version(void) { return 1; }
+
+const char* cd_error_string(int status) {
+  switch (status) {
+    case CD_OK: return "ok";
+    case CD_ERR_INVALID: return "invalid argument";
+    case CD_ERR_CUDA: return "CUDA call failed";
+    case CD_ERR_UNSUPPORTED: return "unsupported shape";
+    case CD_ERR_TIMEOUT: return "a kernel gave up on a bounded wait";
+    default: return "unknown status";
+  }
+}
+
+const char* cd_last_cuda_error(void) { return g_cuda_err; }
+
+int cd_status_fetch(int* h_status) {
+  if (!h_status) return CD_ERR_INVALID;
+  int* d = device_status_word();
+  if (!d) return CD_ERR_CUDA;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceSynchronize");
+  e = cudaMemcpy(h_status, d, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpy(status)");
+  if (*h_status != 0) {
+    e = cudaMemset(d, 0, sizeof(int));
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemset(status)");
+  }
+  return CD_OK;
+}
+
+size_t cd_route_workspace_bytes(int T, int E) {
+  if (T < 0 || E < 1) return 0;
+  return route_workspace_bytes(T, E);
+}
+
+int cd_route(const int64_t* ids, const int64_t* table, int V, int E, int T, int32_t* expert_ids,
+             int32_t* counts, int32_t* offsets, int32_t* perm, int32_t* inv_perm, void* ws,
+             size_t ws_bytes, void* stream) {
+  if (T < 0 || V < 1 || E < 1 || E > kMaxGroups) return CD_ERR_INVALID;
+  if (!table || !counts || !offsets || !ws) return CD_ERR_INVALID;
+  if (T > 0 && (!ids || !expert_ids || !perm || !inv_perm)) return CD_ERR_INVALID;
+  if (ws_bytes < route_workspace_bytes(T, E)) return CD_ERR_INVALID;
+  cudaError_t e = launch_route(reinterpret_cast<const long long*>(ids),
+                               reinterpret_cast<const long long*>(table), V, E, T, expert_ids,
+                               counts, offsets, perm, inv_perm, static_cast<int*>(ws),
+                               as_stream(stream));
+  return e == cudaSuccess ? CD_OK : cuda_fail(e, "route launch");
+}
+
+int cd_rmsnorm(const void* x, const void* residual, const void* weight, float eps, void* sum_out,
+               void* out, const int32_t* dst_rows, int T, int H, void* stream) {
+  if (T < 0 || H < 1 || !weight) return CD_ERR_INVALID;
+  if (T > 0 && (!x || !out)) return CD_ERR_INVALID;
+  if ((H & 7) == 0 && !(aligned16(x) && aligned16(residual) && aligned16(weight) &&
+                        aligned16(sum_out) && aligned16(out)))
+    return CD_ERR_INVALID;
+  cudaError_t e =
+      launch_rmsnorm(x, residual, weight, eps, sum_out, out, dst_rows, T, H, as_stream(stream));
+  return e == cudaSuccess ? CD_OK : cuda_fail(e, "rmsnorm launch");
+}
+
+int cd_gather_rows(const void* x, const int32_t* src_rows, void* out, int T, int H, void* stream) {
+  if (T < 0 || H < 1) return CD_ERR_INVALID;
+  if (T > 0 && (!x || !src_rows || !out)) return CD_ERR_INVALID;
+  if ((H & 7) == 0 && !(aligned16(x) && aligned16(out))) return CD_ERR_INVALID;
+  cudaError_t e = launch_gather_rows(x, src_rows, out, T, H, as_stream(stream));
+  return e == cudaSuccess ? CD_OK : cuda_fail(e, "gather launch");
+}
+
+int cd_qk_norm_rope(void* qkv, const void* q_w, const void* k_w, const float* cos_t,
+                    const float* sin_t, float eps, int T, int S, int pos0, int hq, int hkv, int D,
+                    void* stream) {
+  if (T < 0 || S < 1 || pos0 < 0 || hq < 1 || hkv < 1 || D < 4 || (D & 3)) return CD_ERR_INVALID;
+  if (!cos_t || !sin_t || (T > 0 && !qkv)) return CD_ERR_INVALID;
+  if ((q_w == nullptr) != (k_w == nullptr)) return CD_ERR_INVALID;
+  cudaError_t e = launch_qk_norm_rope(qkv, q_w, k_w, cos_t, sin_t, eps, T, S, pos0, hq, hkv, D,
+                                      as_stream(stream));
+  return e == cudaSuccess ? CD_OK : cuda_fail(e, "qk_norm_rope launch");
+}
+
+int cd_gate_up_packed_rows(int I, int block_n) {
+  if (I < 1 || (block_n != 128 && block_n != 256)) return 0;
+  const int half = block_n / 2;
+  return ((I + half - 1) / half) * block_n;
+}
+
+int cd_moe_up(const void* x_sorted, const int32_t* seg_offsets, int num_groups,
+              const void* packed_w, void* h, int T, int H, int I, int block_n, void* stream) {
+  if (T < 0 || H < 8 || I < 8 || (H & 7) || (I & 7) || num_groups < 1) return CD_ERR_INVALID;
+  const int rows = cd_gate_up_packed_rows(I, block_n);
+  if (rows == 0) return CD_ERR_INVALID;
+  GemmOperand op{};
+  op.a = x_sorted;
+  op.lda = H;
+  op.b = packed_w;
+  op.ldb = H;
+  op.b_rows = static_cast<long long>(rows) * num_groups;
+  op.b_group_rows = rows;
+  op.K = H;
+  GemmEpilogueArgs epi{};
+  epi.kind = kEpiSwiGLU;
+  epi.out = h;
+  epi.ldo = I;
+  epi.out_cols = I;
+  return launch_gemm(T, rows, num_groups, seg_offsets, op, nullptr, epi, block_n,
+                     as_stream(stream));
+}
+
+int cd_moe_down(const void* h_routed, int I_e, const void* wd_routed, const void* h_shared,
+                int I_s, const void* wd_shared, const int32_t* seg_offsets, int E,
+                const int32_t* row_map, const void* residual, void* out, int T, int H,
+                void* stream) {
+  if (T < 0 || H < 8 || (H & 7) || I_e < 8 || (I_e & 7) || E < 1) return CD_ERR_INVALID;
+  if ((h_shared == nullptr) != (wd_shared == nullptr)) return CD_ERR_INVALID;
+  if (h_shared && (I_s < 8 || (I_s & 7))) return CD_ERR_INVALID;
+  GemmOperand op0{};
+  op0.a = h_routed;
+  op0.lda = I_e;
+  op0.b = wd_routed;
+  op0.ldb = I_e;
+  op0.b_rows = static_cast<long long>(E) * H;
+  op0.b_group_rows = H;
+  op0.K = I_e;
+  GemmOperand op1{};
+  if (h_shared) {
+    op1.a = h_shared;
+    op1.lda = I_s;
+    op1.b = wd_shared;
+    op1.ldb = I_s;
+    op1.b_rows = H;
+    op1.b_group_rows = 0;
+    op1.K = I_s;
+  }
+  GemmEpilogueArgs epi{};
+  epi.kind = kEpiStore;
+  epi.out = out;
+  epi.ldo = H;
+  epi.out_cols = H;
+  epi.row_map = row_map;
+  epi.residual = residual;
+  epi.ldr = H;
+  return launch_gemm(T, H, E, seg_offsets, op0, h_shared ? &op1 : nullptr, epi,
+                     H > 128 ? 256 : 128, as_stream(stream));
+}
+
+int cd_mu_qkv(const void* x, const void* mu_prev, const void* w, const void* w_mu, void* qkv,
+              int T, int H, int N, void* stream) {
+  if (T < 0 || H < 8 || (H & 7) || N < 8 || (N & 7)) return CD_ERR_INVALID;
+  if ((mu_prev == nullptr) != (w_mu == nullptr)) return CD_ERR_INVALID;
+  GemmOperand op0{};
+  op0.a = x;
+  op0.lda = H;
+  op0.b = w;
+  op0.ldb = H;
+  op0.b_rows = N;
+  op0.K = H;
+  GemmOperand op1{};
+  if (mu_prev) {
+    op1.a = mu_prev;
+    op1.lda = H;
+    op1.b = w_mu;
+    op1.ldb = H;
+    op1.b_rows = N;
+    op1.K = H;
+  }
+  GemmEpilogueArgs epi{};
+  epi.kind = kEpiStore;
+  epi.out = qkv;
+  epi.ldo = N;
+  epi.out_cols = N;
+  return launch_gemm(T, N, 1, nullptr, op0, mu_prev ? &op1 : nullptr, epi, N > 128 ? 256 : 128,
+                     as_stream(stream));
+}
+
+int cd_mu_proj(const void* h, const void* w, const void* mu_param, float mu_min, float mu_max,
+               int clamp_out, float out_lo, float out_hi, void* out, int T, int H, void* stream) {
+  if (T < 0 || H < 8 || (H & 7) || !mu_param) return CD_ERR_INVALID;
+  GemmOperand op0{};
+  op0.a = h;
+  op0.lda = H;
+  op0.b = w;
+  op0.ldb = H;
+  op0.b_rows = H;
+  op0.K = H;
+  GemmEpilogueArgs epi{};
+  epi.kind = kEpiStore;
+  epi.out = out;
+  epi.ldo = H;
+  epi.out_cols = H;
+  epi.bias = mu_param;
+  epi.bias_lo = mu_min;
+  epi.bias_hi = mu_max;
+  epi.do_clamp = clamp_out;
+  epi.clamp_lo = out_lo;
+  epi.clamp_hi = out_hi;
+  return launch_gemm(T, H, 1, nullptr, op0, nullptr, epi, H > 128 ? 256 : 128, as_stream(stream));
+}
+
+int cd_linear(const void* x, const void* w, const void* residual, void* out, int T, int K, int N,
+              void* stream) {
+  if (T < 0 || K < 8 || (K & 7) || N < 8 || (N & 7)) return CD_ERR_INVALID;
+  GemmOperand op0{};
+  op0.a = x;
+  op0.lda = K;
+  op0.b = w;
+  op0.ldb = K;
+  op0.b_rows = N;
+  op0.K = K;
+  GemmEpilogueArgs epi{};
+  epi.kind = kEpiStore;
+  epi.out = out;
+  epi.ldo = N;
+  epi.out_cols = N;
+  epi.residual = residual;
+  epi.ldr = N;
+  return launch_gemm(T, N, 1, nullptr, op0, nullptr, epi, N > 128 ? 256 : 128, as_stream(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,204 @@
+// Host side of the tcgen05 GEMM: tensor-map encoding, shape checks, launch.
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include "../../include/cdeep.h"
+#include "gemm_sm100.cuh"
+#include "kernels.h"
+
+namespace cdeep {
+
+namespace {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver API is reached through the runtime so that the library links against
+// nothing but cudart and still loads on a machine without a driver.
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+            cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// 2-D bf16 tensor [rows, cols] with `ld` elements between rows; box = [box_rows, 64 cols],
+// 128-byte swizzle (one box row = 128 bytes = one swizzle row), zero fill out of bounds.
+bool make_map(CUtensorMap* m, const void* base, long long rows, long long cols, long long ld,
+              int box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(kBlockK), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+struct DeviceInfo {
+  int sm_count = 0;
+  bool attr_set[2][2] = {{false, false}, {false, false}};
+  int* status = nullptr;
+};
+constexpr int kMaxDevices = 64;
+DeviceInfo g_dev[kMaxDevices];
+std::mutex g_mu;
+
+__device__ int g_status_word;  // raised by a kernel whose bounded wait ran out
+
+template <int BN, int EPI>
+cudaError_t launch_one(int grid, const CUtensorMap& a0, const CUtensorMap& b0,
+                       const CUtensorMap& a1, const CUtensorMap& b1, const GemmParams& p,
+                       DeviceInfo& di, cudaStream_t stream) {
+  constexpr int bi = (BN == 256) ? 1 : 0;
+  auto kern = gemm_bf16_sm100_kernel<BN, EPI>;
+  if (!di.attr_set[bi][EPI]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         GemmSmem<BN>::kDynamic);
+    if (e != cudaSuccess) return e;
+    di.attr_set[bi][EPI] = true;
+  }
+  kern<<<grid, kGemmThreads, GemmSmem<BN>::kDynamic, stream>>>(a0, b0, a1, b1, p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+static DeviceInfo* device_info(int* status_out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    *status_out = cuda_fail(e, "cudaGetDevice");
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lk(g_mu);
+  DeviceInfo& di = g_dev[dev];
+  if (di.sm_count == 0) {
+    int sms = 0;
+    e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) {
+      *status_out = cuda_fail(e, "cudaDeviceGetAttribute");
+      return nullptr;
+    }
+    void* sp = nullptr;
+    e = cudaGetSymbolAddress(&sp, g_status_word);
+    if (e != cudaSuccess) {
+      *status_out = cuda_fail(e, "cudaGetSymbolAddress(status)");
+      return nullptr;
+    }
+    di.status = static_cast<int*>(sp);
+    di.sm_count = sms;
+  }
+  *status_out = CD_OK;
+  return &di;
+}
+
+int* device_status_word() {
+  int st;
+  DeviceInfo* di = device_info(&st);
+  return di ? di->status : nullptr;
+}
+
+int launch_gemm(int M, int N, int num_groups, const int* seg_offsets, const GemmOperand& op0,
+                const GemmOperand* op1, const GemmEpilogueArgs& epi, int block_n,
+                cudaStream_t stream) {
+  if (M < 0 || N <= 0 || num_groups < 1 || num_groups > kMaxGroups) return CD_ERR_INVALID;
+  if (block_n != 128 && block_n != 256) return CD_ERR_INVALID;
+  if (num_groups > 1 && !seg_offsets) return CD_ERR_INVALID;
+  if (op0.K <= 0 || (op0.K & 7) || (op0.lda & 7) || (op0.ldb & 7)) return CD_ERR_INVALID;
+  if (op1 && (op1->K <= 0 || (op1->K & 7) || (op1->lda & 7) || (op1->ldb & 7)))
+    return CD_ERR_INVALID;
+  if ((epi.ldo & 7) || (epi.out_cols & 7) || (epi.residual && (epi.ldr & 7)))
+    return CD_ERR_INVALID;
+  auto aligned16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (!op0.a || !op0.b || !epi.out || !aligned16(op0.a) || !aligned16(op0.b) ||
+      !aligned16(epi.out) || !aligned16(epi.residual) || !aligned16(epi.bias))
+    return CD_ERR_INVALID;
+  if (op1 && (!op1->a || !op1->b || !aligned16(op1->a) || !aligned16(op1->b)))
+    return CD_ERR_INVALID;
+  if (M == 0) return CD_OK;
+
+  int st;
+  DeviceInfo* di = device_info(&st);
+  if (!di) return st;
+
+  CUtensorMap a0, b0, a1, b1;
+  if (!make_map(&a0, op0.a, M, op0.K, op0.lda, kBlockM) ||
+      !make_map(&b0, op0.b, op0.b_rows, op0.K, op0.ldb, block_n)) {
+    snprintf(g_cuda_err, sizeof(g_cuda_err), "cuTensorMapEncodeTiled failed (operand 0)");
+    return CD_ERR_CUDA;
+  }
+  if (op1) {
+    if (!make_map(&a1, op1->a, M, op1->K, op1->lda, kBlockM) ||
+        !make_map(&b1, op1->b, op1->b_rows, op1->K, op1->ldb, block_n)) {
+      snprintf(g_cuda_err, sizeof(g_cuda_err), "cuTensorMapEncodeTiled failed (operand 1)");
+      return CD_ERR_CUDA;
+    }
+  } else {
+    a1 = a0;
+    b1 = b0;
+  }
+
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = M;
+  p.N = N;
+  p.K0 = op0.K;
+  p.K1 = op1 ? op1->K : 0;
+  p.num_groups = num_groups;
+  p.seg_offsets = seg_offsets;
+  p.b0_group_rows = op0.b_group_rows;
+  p.b1_group_rows = op1 ? op1->b_group_rows : 0;
+  p.band = 16;
+  p.out = static_cast<__nv_bfloat16*>(epi.out);
+  p.ldo = epi.ldo;
+  p.out_cols = epi.out_cols;
+  p.row_map = epi.row_map;
+  p.residual = static_cast<const __nv_bfloat16*>(epi.residual);
+  p.ldr = epi.ldr;
+  p.bias = static_cast<const __nv_bfloat16*>(epi.bias);
+  p.bias_lo = epi.bias_lo;
+  p.bias_hi = epi.bias_hi;
+  p.do_clamp = epi.do_clamp;
+  p.clamp_lo = epi.clamp_lo;
+  p.clamp_hi = epi.clamp_hi;
+  p.status = di->status;
+
+  // Upper bound of the tile count without reading the segment sizes (they live on the
+  // device): every group adds at most one partial m-tile.
+  const long long n_tiles = (N + block_n - 1) / block_n;
+  const long long m_tiles_max = (M + kBlockM - 1) / kBlockM + (num_groups > 1 ? num_groups : 0);
+  long long grid = m_tiles_max * n_tiles;
+  if (grid > di->sm_count) grid = di->sm_count;
+  if (grid < 1) grid = 1;
+
+  cudaError_t e;
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (block_n == 256) {
+    e = (epi.kind == kEpiSwiGLU)
+            ? launch_one<256, kEpiSwiGLU>(static_cast<int>(grid), a0, b0, a1, b1, p, *di, stream)
+            : launch_one<256, kEpiStore>(static_cast<int>(grid), a0, b0, a1, b1, p, *di, stream);
+  } else {
+    e = (epi.kind == kEpiSwiGLU)
+            ? launch_one<128, kEpiSwiGLU>(static_cast<int>(grid), a0, b0, a1, b1, p, *di, stream)
+            : launch_one<128, kEpiStore>(static_cast<int>(grid), a0, b0, a1, b1, p, *di, stream);
+  }
+  if (e != cudaSuccess) return cuda_fail(e, "gemm launch");
+  return CD_OK;
+}
+
+}  // namespace cdeep

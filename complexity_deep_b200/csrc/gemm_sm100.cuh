@@ -1,0 +1,390 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a: TMA-fed shared-memory pipeline,
+// tcgen05.mma accumulating in TMEM (two accumulators, so the epilogue of one tile runs
+// under the main loop of the next), ragged per-expert row segments, two K segments
+// (K-concatenation without materialising the concatenated operand), fused epilogues.
+//
+//   C[rows of group g, :] = A0[rows, :K0] * B0[g]^T  +  A1[rows, :K1] * B1[g]^T
+//
+// A0/A1 are row-major [M, K*] activations, B0/B1 are K-major weights [groups * N, K*]
+// (nn.Linear layout: one output feature per row).  Groups are contiguous row ranges of A
+// given by `seg_offsets` on the device, so no host synchronisation is needed to schedule
+// ragged expert segments.  Rows of a 128-row tile that lie past the end of its segment are
+// computed (they are real rows of the next segment, or TMA zero fill) and never stored.
+//
+// This one kernel covers, through its epilogue and operand set-up:
+//   * the routed and the shared SwiGLU up-projections with silu(gate)*up fused
+//     (reference: complexity_deep/core/token_routed_mlp.py:157-160,171-173),
+//   * the down projections of routed + shared experts as ONE fp32 accumulation, the
+//     un-permutation of rows and the block's residual add (token_routed_mlp.py:174-178,
+//     complexity_deep/core/layer.py:183),
+//   * the mu-guided QKV projection [x | mu_prev] @ [W ; W_mu]^T
+//     (complexity_deep/core/attention.py:120-127),
+//   * mu_proj with the clamp(mu) term (complexity_deep/core/layer.py:61) and the model's
+//     output clamp (complexity_deep/models/modeling.py:199-200),
+//   * plain projections with an optional residual (o_proj, lm_head).
+#pragma once
+#include <cuda_bf16.h>
+#include "ptx.cuh"
+
+namespace cdeep {
+
+constexpr int kBlockM = 128;       // rows per tile = TMEM lanes
+constexpr int kBlockK = 64;        // bf16 elements per k-block = one 128-byte swizzle row
+constexpr int kUmmaK = 16;         // K of one tcgen05.mma for 16-bit inputs
+constexpr int kMaxGroups = 256;
+constexpr int kGemmThreads = 192;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
+
+enum GemmEpilogue : int {
+  kEpiStore = 0,   // out[row_map(r), n] = clamp(acc + bias[n] + residual[row_map(r), n])
+  kEpiSwiGLU = 1,  // out[r, j] = silu(acc[r, gate(j)]) * acc[r, up(j)]
+};
+
+struct GemmParams {
+  int M;                   // rows of A
+  int N;                   // rows of B per group (= accumulator columns per group)
+  int K0, K1;              // K extents of the two segments (K1 == 0: one segment)
+  int num_groups;          // row segments; 1 = dense
+  const int* seg_offsets;  // device [num_groups + 1]; nullptr = one segment [0, M)
+  int b0_group_rows;       // B0 row offset per group (0: all groups share B0)
+  int b1_group_rows;       // same for B1
+  int band;                // m-tiles per scheduling band (L2 reuse of the A band)
+  // epilogue
+  __nv_bfloat16* out;
+  int ldo;
+  int out_cols;            // valid output columns (N for store, N/2-ish width I for SwiGLU)
+  const int* row_map;      // sorted row -> destination row (nullptr = identity)
+  const __nv_bfloat16* residual;  // indexed like out (nullptr = none)
+  int ldr;
+  const __nv_bfloat16* bias;      // per output column, clamped to [bias_lo, bias_hi] (nullptr = none)
+  float bias_lo, bias_hi;
+  int do_clamp;            // clamp the result to [clamp_lo, clamp_hi]
+  float clamp_lo, clamp_hi;
+  int* status;             // device word; set non-zero when a bounded wait ran out
+};
+
+template <int BN>
+struct GemmSmem {
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kABytes = kBlockM * kBlockK * 2;
+  static constexpr int kBBytes = BN * kBlockK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kTileBytes = kStages * kStageBytes;
+  // after the tiles: barriers, TMEM base, abort flag, schedule tables
+  static constexpr int kBarOff = kTileBytes;
+  static constexpr int kNumBars = 2 * kStages + 4;
+  static constexpr int kMiscOff = kBarOff + kNumBars * 8;
+  static constexpr int kPrefixOff = kMiscOff + 16;
+  static constexpr int kSegOff = kPrefixOff + (kMaxGroups + 1) * 4;
+  static constexpr int kTotal = kSegOff + (kMaxGroups + 1) * 4;
+  static constexpr int kDynamic = kTotal + 1024;  // slack for 1024-byte alignment
+};
+
+struct TileCoord {
+  int group;
+  int m0;       // first row of the tile (global row of A)
+  int n0;       // first accumulator column within the group
+  int row_end;  // one past the last valid row of the segment
+};
+
+// Maps a linear tile index to its coordinates.  Within a group, tiles are ordered in bands
+// of `band` m-tiles; inside a band the m index runs fastest, so the CTAs that run together
+// share a small set of B tiles while the A band stays in L2.
+__device__ __forceinline__ TileCoord decode_tile(int t, int& gcur, const int* prefix,
+                                                 const int* seg, int n_tiles, int band,
+                                                 int bn) {
+  while (t >= prefix[gcur + 1]) ++gcur;
+  const int local = t - prefix[gcur];
+  const int lo = seg[gcur], hi = seg[gcur + 1];
+  const int m_tiles = (hi - lo + kBlockM - 1) / kBlockM;
+  const int per_band = band * n_tiles;
+  const int b = local / per_band;
+  const int within = local - b * per_band;
+  const int m_first = b * band;
+  const int bh = min(band, m_tiles - m_first);
+  const int n_idx = within / bh;
+  const int m_idx = m_first + (within - n_idx * bh);
+  TileCoord c;
+  c.group = gcur;
+  c.m0 = lo + m_idx * kBlockM;
+  c.n0 = n_idx * bn;
+  c.row_end = hi;
+  return c;
+}
+
+__device__ __forceinline__ float silu_f(float g) { return g / (1.0f + __expf(-g)); }
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
+                       const __grid_constant__ CUtensorMap tmB0,
+                       const __grid_constant__ CUtensorMap tmA1,
+                       const __grid_constant__ CUtensorMap tmB1, const GemmParams p) {
+  using L = GemmSmem<BN>;
+  constexpr int S = L::kStages;
+  constexpr uint32_t kTmemCols = 2 * BN;  // two accumulators of BN fp32 columns
+  static_assert(kTmemCols == 256 || kTmemCols == 512, "TMEM allocation must be a power of two");
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+  uint64_t* empty_bar = full_bar + S;
+  uint64_t* tmem_full = empty_bar + S;   // [2]
+  uint64_t* tmem_empty = tmem_full + 2;  // [2]
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(smem + L::kMiscOff);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kMiscOff + 4);
+  int* prefix = reinterpret_cast<int*>(smem + L::kPrefixOff);
+  int* seg = reinterpret_cast<int*>(smem + L::kSegOff);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int n_tiles = (p.N + BN - 1) / BN;
+  const int kb0 = (p.K0 + kBlockK - 1) / kBlockK;
+  const int kb1 = (p.K1 + kBlockK - 1) / kBlockK;
+  const int kb_total = kb0 + kb1;
+
+  // ---------------------------------------------------------------- set-up
+  if (warp == 0 && lane == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_empty[a], 4);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmA0);
+    tma_prefetch_desc(&tmB0);
+    if (p.K1 > 0) {
+      tma_prefetch_desc(&tmA1);
+      tma_prefetch_desc(&tmB1);
+    }
+  } else if (warp == 1) {
+    tmem_alloc(tmem_base_slot, kTmemCols);
+    tmem_relinquish();
+  } else if (warp == 2 && lane == 0) {
+    int acc = 0;
+    prefix[0] = 0;
+    for (int g = 0; g < p.num_groups; ++g) {
+      const int lo = p.seg_offsets ? p.seg_offsets[g] : 0;
+      const int hi = p.seg_offsets ? p.seg_offsets[g + 1] : p.M;
+      seg[g] = lo;
+      seg[g + 1] = hi;
+      acc += ((hi - lo + kBlockM - 1) / kBlockM) * n_tiles;
+      prefix[g + 1] = acc;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+
+  const uint32_t tmem_base = *tmem_base_slot;
+  const int total_tiles = prefix[p.num_groups];
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      int gcur = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const TileCoord c = decode_tile(t, gcur, prefix, seg, n_tiles, p.band, BN);
+        const int b0_row = c.group * p.b0_group_rows + c.n0;
+        const int b1_row = c.group * p.b1_group_rows + c.n0;
+        for (int kb = 0; kb < kb_total; ++kb, ++it) {
+          const uint32_t s = it % S;
+          const uint32_t ph = (it / S) & 1u;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) {
+            ok = false;
+            break;
+          }
+          uint8_t* a_dst = smem + s * L::kStageBytes;
+          uint8_t* b_dst = a_dst + L::kABytes;
+          mbar_arrive_expect_tx(&full_bar[s], L::kStageBytes);
+          if (kb < kb0) {
+            tma_load_2d(a_dst, &tmA0, &full_bar[s], kb * kBlockK, c.m0);
+            tma_load_2d(b_dst, &tmB0, &full_bar[s], kb * kBlockK, b0_row);
+          } else {
+            tma_load_2d(a_dst, &tmA1, &full_bar[s], (kb - kb0) * kBlockK, c.m0);
+            tma_load_2d(b_dst, &tmB1, &full_bar[s], (kb - kb0) * kBlockK, b1_row);
+          }
+        }
+      }
+      if (ok) {
+        // Drain: wait until the MMA warp has consumed every stage this thread filled, so
+        // no bulk copy is still writing shared memory when the CTA exits.
+        const uint32_t filled = it < static_cast<uint32_t>(S) ? it : static_cast<uint32_t>(S);
+        for (uint32_t d = 0; d < filled && ok; ++d) {
+          const uint32_t j = it - filled + d;  // the last `filled` fills
+          ok = mbar_wait(&empty_bar[j % S], (j / S) & 1u, abort_flag);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(kBlockM, BN);
+      uint32_t it = 0;
+      uint32_t tcount = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tcount) {
+        const uint32_t acc = tcount & 1u;
+        const uint32_t acc_ph = (tcount >> 1) & 1u;
+        if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1u, abort_flag)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < kb_total; ++kb, ++it) {
+          const uint32_t s = it % S;
+          const uint32_t ph = (it / S) & 1u;
+          if (!mbar_wait(&full_bar[s], ph, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + s * L::kStageBytes);
+          const uint64_t da = make_smem_desc_sw128(a_addr);
+          const uint64_t db = make_smem_desc_sw128(a_addr + L::kABytes);
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            // advancing 16 bf16 (32 bytes) along K inside the swizzle row: +2 in the
+            // descriptor's 16-byte address units
+            umma_bf16(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
+        }
+        if (ok) umma_commit(&tmem_full[acc]);  // accumulator complete
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (4 warps)
+    const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+    uint32_t tcount = 0;
+    int gcur = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tcount) {
+      const TileCoord c = decode_tile(t, gcur, prefix, seg, n_tiles, p.band, BN);
+      const uint32_t acc = tcount & 1u;
+      const uint32_t acc_ph = (tcount >> 1) & 1u;
+      if (!mbar_wait(&tmem_full[acc], acc_ph, abort_flag)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int r = c.m0 + quarter * 32 + lane;
+      const bool row_ok = r < c.row_end;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+
+      if constexpr (EPI == kEpiStore) {
+        const long long orow = row_ok ? (p.row_map ? p.row_map[r] : r) : 0;
+        __nv_bfloat16* out_row = p.out + orow * p.ldo;
+        const __nv_bfloat16* res_row = p.residual ? p.residual + orow * p.ldr : nullptr;
+#pragma unroll 1
+        for (int ch = 0; ch < BN / 32; ++ch) {
+          const int col0 = c.n0 + ch * 32;
+          if (col0 >= p.N) break;  // uniform across the warp
+          uint32_t v[32];
+          tmem_ld32(t_row + ch * 32, v);
+          tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int col = col0 + q * 8;
+              if (col < p.out_cols) {
+                float f[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[q * 8 + j]);
+                if (p.bias) {
+                  const uint4 b = *reinterpret_cast<const uint4*>(p.bias + col);
+                  const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    f[2 * j] += fminf(fmaxf(bf16_lo(bw[j]), p.bias_lo), p.bias_hi);
+                    f[2 * j + 1] += fminf(fmaxf(bf16_hi(bw[j]), p.bias_lo), p.bias_hi);
+                  }
+                }
+                if (res_row) {
+                  const uint4 rr = *reinterpret_cast<const uint4*>(res_row + col);
+                  const uint32_t rw[4] = {rr.x, rr.y, rr.z, rr.w};
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    f[2 * j] += bf16_lo(rw[j]);
+                    f[2 * j + 1] += bf16_hi(rw[j]);
+                  }
+                }
+                if (p.do_clamp) {
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) f[j] = fminf(fmaxf(f[j], p.clamp_lo), p.clamp_hi);
+                }
+                uint4 o;
+                o.x = pack_bf16x2(f[0], f[1]);
+                o.y = pack_bf16x2(f[2], f[3]);
+                o.z = pack_bf16x2(f[4], f[5]);
+                o.w = pack_bf16x2(f[6], f[7]);
+                *reinterpret_cast<uint4*>(out_row + col) = o;
+              }
+            }
+          }
+        }
+      } else {
+        // SwiGLU: accumulator columns [0, BN/2) hold gate, [BN/2, BN) hold up, for output
+        // columns (n0 / 2) .. (n0 / 2) + BN / 2.
+        __nv_bfloat16* out_row = p.out + static_cast<long long>(row_ok ? r : 0) * p.ldo;
+        const int ocol_base = c.n0 / 2;
+#pragma unroll 1
+        for (int ch = 0; ch < BN / 64; ++ch) {
+          const int ocol0 = ocol_base + ch * 32;
+          if (ocol0 >= p.out_cols) break;  // uniform across the warp
+          uint32_t g[32], u[32];
+          tmem_ld32(t_row + ch * 32, g);
+          tmem_ld32(t_row + BN / 2 + ch * 32, u);
+          tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int col = ocol0 + q * 8;
+              if (col < p.out_cols) {
+                float h[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                  h[j] = silu_f(__uint_as_float(g[q * 8 + j])) * __uint_as_float(u[q * 8 + j]);
+                uint4 o;
+                o.x = pack_bf16x2(h[0], h[1]);
+                o.y = pack_bf16x2(h[2], h[3]);
+                o.z = pack_bf16x2(h[4], h[5]);
+                o.w = pack_bf16x2(h[6], h[7]);
+                *reinterpret_cast<uint4*>(out_row + col) = o;
+              }
+            }
+          }
+        }
+      }
+      // this warp is done reading the accumulator
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+  if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, 1);
+}
+
+}  // namespace cdeep

@@ -1,0 +1,57 @@
+// Internal launch functions shared by the translation units of libcdeep.so.
+#pragma once
+#include <cstddef>
+#include <cuda_runtime.h>
+
+namespace cdeep {
+
+size_t route_workspace_bytes(int T, int E);
+cudaError_t launch_route(const long long* ids, const long long* table, int V, int E, int T,
+                         int* expert_ids, int* counts, int* offsets, int* perm, int* inv_perm,
+                         int* block_hist, cudaStream_t stream);
+
+cudaError_t launch_rmsnorm(const void* x, const void* residual, const void* weight, float eps,
+                           void* sum_out, void* out, const int* dst_rows, int T, int H,
+                           cudaStream_t stream);
+cudaError_t launch_gather_rows(const void* x, const int* src_rows, void* out, int T, int H,
+                               cudaStream_t stream);
+cudaError_t launch_qk_norm_rope(void* qkv, const void* q_w, const void* k_w, const float* cos_t,
+                                const float* sin_t, float eps, int T, int S, int pos0, int hq,
+                                int hkv, int D, cudaStream_t stream);
+
+// One operand pair of the GEMM: row-major bf16 matrices with K contiguous.
+struct GemmOperand {
+  const void* a;   // [M, K], leading dimension lda
+  long long lda;
+  const void* b;   // [groups * n_rows or n_rows, K], leading dimension ldb
+  long long ldb;
+  long long b_rows;      // total rows of b (bounds of the tensor map)
+  int b_group_rows;      // row offset per group, 0 when every group uses the same rows
+  int K;
+};
+
+struct GemmEpilogueArgs {
+  int kind;                // GemmEpilogue
+  void* out;
+  int ldo;
+  int out_cols;
+  const int* row_map;
+  const void* residual;
+  int ldr;
+  const void* bias;
+  float bias_lo, bias_hi;
+  int do_clamp;
+  float clamp_lo, clamp_hi;
+};
+
+// Returns a CD_* status code.
+int launch_gemm(int M, int N, int num_groups, const int* seg_offsets, const GemmOperand& op0,
+                const GemmOperand* op1, const GemmEpilogueArgs& epi, int block_n,
+                cudaStream_t stream);
+
+int* device_status_word();  // per-device word the kernels raise when a bounded wait ran out
+
+extern thread_local char g_cuda_err[256];        // text behind cd_last_cuda_error()
+int cuda_fail(cudaError_t e, const char* what);  // records the text, returns CD_ERR_CUDA
+
+}  // namespace cdeep

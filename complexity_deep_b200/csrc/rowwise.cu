@@ -1,0 +1,247 @@
+// Row-wise, HBM-bound kernels of the block: RMSNorm (optionally fused with the residual add
+// before it and with the scatter of rows into expert-sorted order after it), the row
+// gather used when the MoE layer is called on its own, and the per-head Q/K RMSNorm +
+// rotary embedding applied in place on the fused QKV buffer.
+//
+// Reference semantics:
+//   RMSNorm            complexity_deep/core/normalization.py:29-32  (w * x * rsqrt(mean(x^2) + eps))
+//   residual add       complexity_deep/core/layer.py:174
+//   Q/K norm, RoPE     complexity_deep/core/attention.py:138-155, complexity_deep/core/rotary.py:57-86
+// The reference evaluates these in the activation dtype; here every reduction and product
+// is fp32 and each output is rounded to bf16 once.
+#include <cstdint>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include "kernels.h"
+
+namespace cdeep {
+
+namespace {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float lo_f(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float hi_f(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+constexpr int kNormWarps = 4;
+constexpr int kMaxVec = 16;  // register path: H <= 16 * 256 = 4096, H % 256 == 0
+
+// One warp per row; the row lives in registers between the reduction and the scaling, so
+// x is read from HBM exactly once.
+__global__ void __launch_bounds__(kNormWarps * 32)
+rmsnorm_rows_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+                    const __nv_bfloat16* __restrict__ w, float eps,
+                    __nv_bfloat16* __restrict__ sum_out, __nv_bfloat16* __restrict__ out,
+                    const int* __restrict__ dst_rows, int T, int H) {
+  const int row = blockIdx.x * kNormWarps + (threadIdx.x >> 5);
+  if (row >= T) return;
+  const int lane = threadIdx.x & 31;
+  const int nv = H >> 8;  // uint4 (8 bf16) per lane
+  const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * H);
+  const uint4* rr = res ? reinterpret_cast<const uint4*>(res + static_cast<size_t>(row) * H)
+                        : nullptr;
+  uint4 buf[kMaxVec];
+#pragma unroll
+  for (int v = 0; v < kMaxVec; ++v)
+    if (v < nv) buf[v] = xr[v * 32 + lane];
+  if (rr) {
+#pragma unroll
+    for (int v = 0; v < kMaxVec; ++v)
+      if (v < nv) {
+        const uint4 r = rr[v * 32 + lane];
+        uint32_t* a = reinterpret_cast<uint32_t*>(&buf[v]);
+        const uint32_t b[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) a[j] = pack2(lo_f(a[j]) + lo_f(b[j]), hi_f(a[j]) + hi_f(b[j]));
+      }
+    if (sum_out) {
+      uint4* so = reinterpret_cast<uint4*>(sum_out + static_cast<size_t>(row) * H);
+#pragma unroll
+      for (int v = 0; v < kMaxVec; ++v)
+        if (v < nv) so[v * 32 + lane] = buf[v];
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int v = 0; v < kMaxVec; ++v)
+    if (v < nv) {
+      const uint32_t* a = reinterpret_cast<const uint32_t*>(&buf[v]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float l = lo_f(a[j]), h = hi_f(a[j]);
+        ss += l * l + h * h;
+      }
+    }
+  ss = warp_sum(ss);
+  const float rstd = rsqrtf(ss / static_cast<float>(H) + eps);
+  const int orow = dst_rows ? dst_rows[row] : row;
+  uint4* orw = reinterpret_cast<uint4*>(out + static_cast<size_t>(orow) * H);
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+#pragma unroll
+  for (int v = 0; v < kMaxVec; ++v)
+    if (v < nv) {
+      const uint4 wv = wr[v * 32 + lane];
+      const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+      const uint32_t* a = reinterpret_cast<const uint32_t*>(&buf[v]);
+      uint4 o;
+      uint32_t* oo = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        oo[j] = pack2(lo_f(ww[j]) * (lo_f(a[j]) * rstd), hi_f(ww[j]) * (hi_f(a[j]) * rstd));
+      orw[v * 32 + lane] = o;
+    }
+}
+
+// Any H: one block per row, scalar accesses, the row is re-read from L1/L2 for the scaling.
+__global__ void __launch_bounds__(128)
+rmsnorm_generic_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+                       const __nv_bfloat16* __restrict__ w, float eps,
+                       __nv_bfloat16* __restrict__ sum_out, __nv_bfloat16* __restrict__ out,
+                       const int* __restrict__ dst_rows, int T, int H) {
+  __shared__ float s_part[4];
+  const int row = blockIdx.x;
+  const __nv_bfloat16* xr = x + static_cast<size_t>(row) * H;
+  const __nv_bfloat16* rr = res ? res + static_cast<size_t>(row) * H : nullptr;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    float v = __bfloat162float(xr[c]);
+    if (rr) {
+      const __nv_bfloat16 s = __float2bfloat16_rn(v + __bfloat162float(rr[c]));
+      if (sum_out) sum_out[static_cast<size_t>(row) * H + c] = s;
+      v = __bfloat162float(s);
+    }
+    ss += v * v;
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  const float tot = s_part[0] + s_part[1] + s_part[2] + s_part[3];
+  const float rstd = rsqrtf(tot / static_cast<float>(H) + eps);
+  const int orow = dst_rows ? dst_rows[row] : row;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    float v = __bfloat162float(xr[c]);
+    if (rr) v = __bfloat162float(__float2bfloat16_rn(v + __bfloat162float(rr[c])));
+    out[static_cast<size_t>(orow) * H + c] = __float2bfloat16_rn(__bfloat162float(w[c]) * (v * rstd));
+  }
+}
+
+// out[j, :] = x[src_rows[j], :]
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ src_rows,
+                   __nv_bfloat16* __restrict__ out, int T, int H) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int j = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  if (j >= T) return;
+  const int lane = threadIdx.x & 31;
+  const size_t src = static_cast<size_t>(src_rows[j]) * H;
+  const size_t dst = static_cast<size_t>(j) * H;
+  if ((H & 7) == 0) {
+    const uint4* s = reinterpret_cast<const uint4*>(x + src);
+    uint4* d = reinterpret_cast<uint4*>(out + dst);
+    for (int c = lane; c < (H >> 3); c += 32) d[c] = s[c];
+  } else {
+    for (int c = lane; c < H; c += 32) out[dst + c] = x[src + c];
+  }
+}
+
+// One warp per (token, head) over the q and k heads of the fused [T, (hq + 2 hkv) * D]
+// buffer: y = rmsnorm(head) * norm_w, then rotate-half RoPE with fp32 cos/sin tables
+// [positions, D].  Lane l owns the element pairs (2l', 2l'+1) of the first half together
+// with their partners D/2 further, so the rotation needs no shuffles.
+__global__ void __launch_bounds__(256)
+qk_norm_rope_kernel(__nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ q_w,
+                    const __nv_bfloat16* __restrict__ k_w, const float* __restrict__ cos_t,
+                    const float* __restrict__ sin_t, float eps, int T, int S, int pos0, int hq,
+                    int hkv, int D) {
+  const int heads = hq + hkv;
+  const long long wid = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (wid >= static_cast<long long>(T) * heads) return;
+  const int lane = threadIdx.x & 31;
+  const int t = static_cast<int>(wid / heads);
+  const int h = static_cast<int>(wid - static_cast<long long>(t) * heads);
+  const int ld = (hq + 2 * hkv) * D;
+  __nv_bfloat16* head = qkv + static_cast<size_t>(t) * ld + static_cast<size_t>(h) * D;
+  const __nv_bfloat16* nw = (h < hq) ? q_w : k_w;
+  const int half = D >> 1;
+  const int pos = pos0 + (t % S);
+  const float* cs = cos_t + static_cast<size_t>(pos) * D;
+  const float* sn = sin_t + static_cast<size_t>(pos) * D;
+
+  float ss = 0.f;
+  for (int j = 2 * lane; j < half; j += 64) {
+    const uint32_t a = *reinterpret_cast<const uint32_t*>(head + j);
+    const uint32_t b = *reinterpret_cast<const uint32_t*>(head + half + j);
+    ss += lo_f(a) * lo_f(a) + hi_f(a) * hi_f(a) + lo_f(b) * lo_f(b) + hi_f(b) * hi_f(b);
+  }
+  ss = warp_sum(ss);
+  const float rstd = nw ? rsqrtf(ss / static_cast<float>(D) + eps) : 1.0f;
+  for (int j = 2 * lane; j < half; j += 64) {
+    const uint32_t a = *reinterpret_cast<const uint32_t*>(head + j);
+    const uint32_t b = *reinterpret_cast<const uint32_t*>(head + half + j);
+    float a0 = lo_f(a) * rstd, a1 = hi_f(a) * rstd, b0 = lo_f(b) * rstd, b1 = hi_f(b) * rstd;
+    if (nw) {
+      const uint32_t wa = *reinterpret_cast<const uint32_t*>(nw + j);
+      const uint32_t wb = *reinterpret_cast<const uint32_t*>(nw + half + j);
+      a0 *= lo_f(wa); a1 *= hi_f(wa); b0 *= lo_f(wb); b1 *= hi_f(wb);
+    }
+    // out = x * cos + rotate_half(x) * sin, rotate_half(x) = [-x2, x1]
+    const float o_a0 = a0 * cs[j] - b0 * sn[j];
+    const float o_a1 = a1 * cs[j + 1] - b1 * sn[j + 1];
+    const float o_b0 = b0 * cs[half + j] + a0 * sn[half + j];
+    const float o_b1 = b1 * cs[half + j + 1] + a1 * sn[half + j + 1];
+    *reinterpret_cast<uint32_t*>(head + j) = pack2(o_a0, o_a1);
+    *reinterpret_cast<uint32_t*>(head + half + j) = pack2(o_b0, o_b1);
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_rmsnorm(const void* x, const void* residual, const void* weight, float eps,
+                           void* sum_out, void* out, const int* dst_rows, int T, int H,
+                           cudaStream_t stream) {
+  if (T == 0) return cudaSuccess;
+  auto xb = static_cast<const __nv_bfloat16*>(x);
+  auto rb = static_cast<const __nv_bfloat16*>(residual);
+  auto wb = static_cast<const __nv_bfloat16*>(weight);
+  auto sb = static_cast<__nv_bfloat16*>(sum_out);
+  auto ob = static_cast<__nv_bfloat16*>(out);
+  if ((H & 255) == 0 && H <= kMaxVec * 256) {
+    const int blocks = (T + kNormWarps - 1) / kNormWarps;
+    rmsnorm_rows_kernel<<<blocks, kNormWarps * 32, 0, stream>>>(xb, rb, wb, eps, sb, ob, dst_rows,
+                                                               T, H);
+  } else {
+    rmsnorm_generic_kernel<<<T, 128, 0, stream>>>(xb, rb, wb, eps, sb, ob, dst_rows, T, H);
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gather_rows(const void* x, const int* src_rows, void* out, int T, int H,
+                               cudaStream_t stream) {
+  if (T == 0) return cudaSuccess;
+  const int wpb = 8;
+  gather_rows_kernel<<<(T + wpb - 1) / wpb, wpb * 32, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(x), src_rows, static_cast<__nv_bfloat16*>(out), T, H);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_qk_norm_rope(void* qkv, const void* q_w, const void* k_w, const float* cos_t,
+                                const float* sin_t, float eps, int T, int S, int pos0, int hq,
+                                int hkv, int D, cudaStream_t stream) {
+  if (T == 0) return cudaSuccess;
+  const long long warps = static_cast<long long>(T) * (hq + hkv);
+  const int wpb = 8;
+  const long long blocks = (warps + wpb - 1) / wpb;
+  qk_norm_rope_kernel<<<static_cast<unsigned>(blocks), wpb * 32, 0, stream>>>(
+      static_cast<__nv_bfloat16*>(qkv), static_cast<const __nv_bfloat16*>(q_w),
+      static_cast<const __nv_bfloat16*>(k_w), cos_t, sin_t, eps, T, S, pos0, hq, hkv, D);
+  return cudaGetLastError();
+}
+
+}  // namespace cdeep

@@ -1,0 +1,284 @@
+"""Tensor-level wrappers over the libcdeep C ABI.
+
+PyTorch is used for device memory and streams only: each function checks its arguments,
+allocates outputs with ``torch.empty`` on the caller's device and enqueues the CUDA kernels
+on ``torch.cuda.current_stream()``.  Nothing here computes on the CPU and nothing falls
+back to PyTorch operators.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+
+BF16 = torch.bfloat16
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _need(t: torch.Tensor, name: str, dtype=BF16) -> None:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise RuntimeError(
+            f"{name}: expected a CUDA tensor; the complexity_deep_b200 kernels have no CPU path")
+    if t.dtype != dtype:
+        raise RuntimeError(f"{name}: expected dtype {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name}: expected a contiguous tensor")
+
+
+def status_fetch() -> int:
+    """Synchronises and returns the kernels' status word (0 = ok); raises on a timeout."""
+    lib = _lib.load()
+    st = ctypes.c_int(0)
+    _lib.check(lib.cd_status_fetch(ctypes.byref(st)), "cd_status_fetch")
+    if st.value != 0:
+        raise _lib.CdeepError("a libcdeep kernel gave up on a bounded wait (pipeline error)")
+    return st.value
+
+
+# --------------------------------------------------------------------------- dispatch
+@dataclass
+class Routing:
+    """Routing artefacts of one batch of token ids (all int32, on the device)."""
+    expert_ids: torch.Tensor   # [T]
+    counts: torch.Tensor       # [E]
+    offsets: torch.Tensor      # [E + 1]
+    perm: torch.Tensor         # [T] sorted position -> source row
+    inv_perm: torch.Tensor     # [T] source row -> sorted position
+    num_experts: int
+
+
+def route(token_ids: torch.Tensor, table: torch.Tensor, num_experts: int) -> Routing:
+    lib = _lib.load()
+    ids = token_ids.reshape(-1)
+    _need(ids, "token_ids", torch.int64)
+    _need(table, "token_to_expert", torch.int64)
+    T, V, E = ids.numel(), table.numel(), int(num_experts)
+    dev = ids.device
+    i32 = dict(dtype=torch.int32, device=dev)
+    expert_ids = torch.empty(T, **i32)
+    perm = torch.empty(T, **i32)
+    inv_perm = torch.empty(T, **i32)
+    counts = torch.empty(E, **i32)
+    offsets = torch.empty(E + 1, **i32)
+    ws_bytes = lib.cd_route_workspace_bytes(T, E)
+    ws = torch.empty(max(ws_bytes, 4), dtype=torch.uint8, device=dev)
+    _lib.check(lib.cd_route(ids.data_ptr(), table.data_ptr(), V, E, T, expert_ids.data_ptr(),
+                            counts.data_ptr(), offsets.data_ptr(), perm.data_ptr(),
+                            inv_perm.data_ptr(), ws.data_ptr(), ws.numel(), _stream()),
+               "cd_route")
+    return Routing(expert_ids, counts, offsets, perm, inv_perm, E)
+
+
+# --------------------------------------------------------------------------- row-wise
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float,
+            residual: Optional[torch.Tensor] = None, dst_rows: Optional[torch.Tensor] = None,
+            want_sum: bool = False):
+    """``norm(x (+ residual)) * weight``; returns ``out`` or ``(sum, out)`` when want_sum.
+
+    With ``dst_rows`` row i of the result is written to row ``dst_rows[i]``.
+    """
+    lib = _lib.load()
+    H = x.shape[-1]
+    x2 = x.reshape(-1, H)
+    _need(x2, "x")
+    _need(weight, "weight")
+    T = x2.shape[0]
+    res2 = None
+    if residual is not None:
+        res2 = residual.reshape(-1, H)
+        _need(res2, "residual")
+    if dst_rows is not None:
+        _need(dst_rows, "dst_rows", torch.int32)
+    out = torch.empty_like(x2)
+    s = torch.empty_like(x2) if (want_sum and res2 is not None) else None
+    _lib.check(lib.cd_rmsnorm(x2.data_ptr(), _ptr(res2), weight.data_ptr(), float(eps), _ptr(s),
+                              out.data_ptr(), _ptr(dst_rows), T, H, _stream()), "cd_rmsnorm")
+    out = out.view(x.shape)
+    if want_sum:
+        return (s.view(x.shape) if s is not None else x), out
+    return out
+
+
+def gather_rows(x: torch.Tensor, src_rows: torch.Tensor) -> torch.Tensor:
+    lib = _lib.load()
+    H = x.shape[-1]
+    x2 = x.reshape(-1, H)
+    _need(x2, "x")
+    _need(src_rows, "src_rows", torch.int32)
+    out = torch.empty_like(x2)
+    _lib.check(lib.cd_gather_rows(x2.data_ptr(), src_rows.data_ptr(), out.data_ptr(), x2.shape[0],
+                                  H, _stream()), "cd_gather_rows")
+    return out
+
+
+def qk_norm_rope_(qkv: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Optional[torch.Tensor],
+                  cos: torch.Tensor, sin: torch.Tensor, eps: float, seq_len: int, pos0: int,
+                  hq: int, hkv: int, head_dim: int) -> torch.Tensor:
+    """In-place Q/K RMSNorm + RoPE on the fused projection buffer [T, (hq + 2 hkv) * D]."""
+    lib = _lib.load()
+    _need(qkv, "qkv")
+    _need(cos, "cos", torch.float32)
+    _need(sin, "sin", torch.float32)
+    if q_w is not None:
+        _need(q_w, "q_norm.weight")
+        _need(k_w, "k_norm.weight")
+    T = qkv.shape[0]
+    if qkv.shape[1] != (hq + 2 * hkv) * head_dim:
+        raise RuntimeError("qkv width does not match the head layout")
+    if cos.shape[0] < pos0 + seq_len or cos.shape[1] != head_dim:
+        raise RuntimeError("cos/sin tables too short for the requested positions")
+    _lib.check(lib.cd_qk_norm_rope(qkv.data_ptr(), _ptr(q_w), _ptr(k_w), cos.data_ptr(),
+                                   sin.data_ptr(), float(eps), T, seq_len, pos0, hq, hkv,
+                                   head_dim, _stream()), "cd_qk_norm_rope")
+    return qkv
+
+
+# --------------------------------------------------------------------------- weights
+def choose_block_n(width: int) -> int:
+    """Accumulator-tile width for the SwiGLU up-projection of an expert `width` wide.
+
+    256 (128 gate + 128 up columns per tile) unless padding `width` to a multiple of 128
+    would waste more than 5 % of the tile columns; then 128 (64 + 64).
+    """
+    padded = -(-width // 128) * 128
+    return 256 if (padded - width) / width <= 0.05 else 128
+
+
+def pack_gate_up(gate: torch.Tensor, up: torch.Tensor, block_n: int) -> torch.Tensor:
+    """Interleaves gate and up rows per accumulator tile.
+
+    gate, up: [G, I, H] (one output feature per row, H contiguous).  Result
+    [G, ceil(I / half) * block_n, H] with, for each tile, `half` gate rows then `half` up rows
+    (half = block_n / 2); rows past I are zero.
+    """
+    G, I, H = gate.shape
+    half = block_n // 2
+    chunks = -(-I // half)
+    pad = chunks * half - I
+    if pad:
+        z = gate.new_zeros(G, pad, H)
+        gate = torch.cat([gate, z], dim=1)
+        up = torch.cat([up, z], dim=1)
+    g = gate.reshape(G, chunks, 1, half, H)
+    u = up.reshape(G, chunks, 1, half, H)
+    return torch.cat([g, u], dim=2).reshape(G, chunks * block_n, H).contiguous()
+
+
+# --------------------------------------------------------------------------- GEMMs
+def moe_up(x_sorted: torch.Tensor, seg_offsets: Optional[torch.Tensor], num_groups: int,
+           packed_w: torch.Tensor, width: int, block_n: int) -> torch.Tensor:
+    lib = _lib.load()
+    _need(x_sorted, "x_sorted")
+    _need(packed_w, "packed gate/up weights")
+    T, H = x_sorted.shape
+    rows = lib.cd_gate_up_packed_rows(width, block_n)
+    if tuple(packed_w.shape) != (num_groups, rows, H):
+        raise RuntimeError(f"packed weights have shape {tuple(packed_w.shape)}, expected "
+                           f"{(num_groups, rows, H)}")
+    if seg_offsets is not None:
+        _need(seg_offsets, "seg_offsets", torch.int32)
+    h = torch.empty(T, width, dtype=BF16, device=x_sorted.device)
+    _lib.check(lib.cd_moe_up(x_sorted.data_ptr(), _ptr(seg_offsets), num_groups,
+                             packed_w.data_ptr(), h.data_ptr(), T, H, width, block_n, _stream()),
+               "cd_moe_up")
+    return h
+
+
+def moe_down(h_routed: torch.Tensor, wd_routed: torch.Tensor, h_shared: Optional[torch.Tensor],
+             wd_shared: Optional[torch.Tensor], seg_offsets: Optional[torch.Tensor],
+             num_experts: int, row_map: Optional[torch.Tensor],
+             residual: Optional[torch.Tensor]) -> torch.Tensor:
+    """wd_routed: [E, H, I_e] (feature rows, I_e contiguous); wd_shared: [H, I_s]."""
+    lib = _lib.load()
+    _need(h_routed, "h_routed")
+    _need(wd_routed, "routed down weights")
+    T, I_e = h_routed.shape
+    E, H, I_e2 = wd_routed.shape
+    if E != num_experts or I_e2 != I_e:
+        raise RuntimeError("routed down weights do not match h_routed")
+    I_s = 0
+    if h_shared is not None:
+        _need(h_shared, "h_shared")
+        _need(wd_shared, "shared down weight")
+        I_s = h_shared.shape[1]
+        if tuple(wd_shared.shape) != (H, I_s) or h_shared.shape[0] != T:
+            raise RuntimeError("shared down weight does not match h_shared")
+    if seg_offsets is not None:
+        _need(seg_offsets, "seg_offsets", torch.int32)
+    if row_map is not None:
+        _need(row_map, "row_map", torch.int32)
+    res2 = None
+    if residual is not None:
+        res2 = residual.reshape(-1, H)
+        _need(res2, "residual")
+        if res2.shape[0] != T:
+            raise RuntimeError("residual rows do not match")
+    out = torch.empty(T, H, dtype=BF16, device=h_routed.device)
+    _lib.check(lib.cd_moe_down(h_routed.data_ptr(), I_e, wd_routed.data_ptr(), _ptr(h_shared),
+                               I_s, _ptr(wd_shared), _ptr(seg_offsets), E, _ptr(row_map),
+                               _ptr(res2), out.data_ptr(), T, H, _stream()), "cd_moe_down")
+    return out
+
+
+def mu_qkv(x: torch.Tensor, mu_prev: Optional[torch.Tensor], w: torch.Tensor,
+           w_mu: Optional[torch.Tensor]) -> torch.Tensor:
+    lib = _lib.load()
+    _need(x, "x")
+    _need(w, "qkv weight")
+    T, H = x.shape
+    N = w.shape[0]
+    if mu_prev is not None:
+        _need(mu_prev, "mu_prev")
+        _need(w_mu, "mu qkv weight")
+        if tuple(mu_prev.shape) != (T, H) or tuple(w_mu.shape) != (N, H):
+            raise RuntimeError("mu_prev / mu weights do not match x / qkv weights")
+    out = torch.empty(T, N, dtype=BF16, device=x.device)
+    _lib.check(lib.cd_mu_qkv(x.data_ptr(), _ptr(mu_prev), w.data_ptr(),
+                             _ptr(w_mu) if mu_prev is not None else None, out.data_ptr(), T, H, N,
+                             _stream()), "cd_mu_qkv")
+    return out
+
+
+def mu_proj(h: torch.Tensor, w: torch.Tensor, mu_param: torch.Tensor, mu_min: float,
+            mu_max: float, out_clamp: Optional[Tuple[float, float]] = None) -> torch.Tensor:
+    lib = _lib.load()
+    _need(h, "hidden_states")
+    _need(w, "mu_proj.weight")
+    _need(mu_param, "mu")
+    T, H = h.shape
+    out = torch.empty(T, H, dtype=BF16, device=h.device)
+    lo, hi = out_clamp if out_clamp is not None else (0.0, 0.0)
+    _lib.check(lib.cd_mu_proj(h.data_ptr(), w.data_ptr(), mu_param.data_ptr(), float(mu_min),
+                              float(mu_max), 1 if out_clamp is not None else 0, float(lo),
+                              float(hi), out.data_ptr(), T, H, _stream()), "cd_mu_proj")
+    return out
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = None
+           ) -> torch.Tensor:
+    lib = _lib.load()
+    _need(x, "x")
+    _need(w, "weight")
+    T, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise RuntimeError("weight does not match x")
+    if residual is not None:
+        _need(residual, "residual")
+        if tuple(residual.shape) != (T, N):
+            raise RuntimeError("residual does not match the output")
+    out = torch.empty(T, N, dtype=BF16, device=x.device)
+    _lib.check(lib.cd_linear(x.data_ptr(), w.data_ptr(), _ptr(residual), out.data_ptr(), T, K, N,
+                             _stream()), "cd_linear")
+    return out

@@ -1,0 +1,143 @@
+/*
+ * libcdeep — C ABI of the B200 (sm_100a) kernels for Complexity-Deep's token-routed MoE
+ * layer and mu-guided attention projection.
+ *
+ * The reference (Complexity-ML/complexity-deep) has no FFI: the boundary it exposes is the
+ * nn.Module API of complexity_deep/core and complexity_deep/models.  The Python package in
+ * this repository keeps that API and calls the entry points below through ctypes; each
+ * entry point names the reference code it replaces (path inside the reference project).
+ *
+ * Conventions
+ *   - every function returns a CD_* status (0 = ok) and never throws;
+ *   - all pointers are DEVICE pointers unless the name starts with h_;
+ *   - activations and weights are bf16 (uint16 storage), row-major, contiguous, 16-byte
+ *     aligned; ids and the routing table are int64 as in the reference; routing artefacts
+ *     are int32;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = default stream); kernels are only
+ *     enqueued, nothing synchronises except cd_status_fetch;
+ *   - the library allocates no device memory on these paths: scratch is passed in.
+ */
+#ifndef CDEEP_H_
+#define CDEEP_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CD_OK 0
+#define CD_ERR_INVALID 1      /* bad argument (null pointer, size or alignment rule broken) */
+#define CD_ERR_CUDA 2         /* a CUDA runtime / driver call failed; see cd_last_cuda_error */
+#define CD_ERR_UNSUPPORTED 3  /* shape outside what the kernels implement */
+#define CD_ERR_TIMEOUT 4      /* a kernel gave up on a bounded wait (reported by cd_status_fetch) */
+
+/* ABI version of this header (bumped on any signature change). */
+int cd_version(void);
+/* Static text for a CD_* code. */
+const char* cd_error_string(int status);
+/* Text of the last CUDA error seen by the calling thread's last failing call. */
+const char* cd_last_cuda_error(void);
+/* Synchronises the current device, copies the kernels' status word to *h_status
+ * (0 = every bounded wait completed) and clears it. */
+int cd_status_fetch(int* h_status);
+
+/* ---- dispatch -------------------------------------------------------------------------
+ * Replaces TokenRoutedMLP.forward's lookup and mask loop,
+ * complexity_deep/core/token_routed_mlp.py:149-150 (clamp + table lookup) and :166-170,
+ * :174 (per-expert boolean mask, gather, scatter).  Outputs, all bit-exact with what the
+ * mask loop implies:
+ *   expert_ids[T]  table[clamp(ids, 0, V-1)]
+ *   counts[E]      tokens per expert
+ *   offsets[E+1]   exclusive prefix sum of counts
+ *   perm[T]        sorted position -> source row (rows of expert e in ascending row order)
+ *   inv_perm[T]    source row -> sorted position
+ * ws: scratch of at least cd_route_workspace_bytes(T, E) bytes.  E <= 256. */
+size_t cd_route_workspace_bytes(int T, int E);
+int cd_route(const int64_t* ids, const int64_t* table, int V, int E, int T, int32_t* expert_ids,
+             int32_t* counts, int32_t* offsets, int32_t* perm, int32_t* inv_perm, void* ws,
+             size_t ws_bytes, void* stream);
+
+/* ---- RMSNorm ---------------------------------------------------------------------------
+ * Replaces RMSNorm.forward, complexity_deep/core/normalization.py:29-32, optionally fused
+ * with the residual add in front of it (complexity_deep/core/layer.py:174) and with the
+ * scatter of rows into expert-sorted order behind it (the gather of
+ * token_routed_mlp.py:170).
+ *   h = x (+ residual, rounded to bf16);  sum_out = h (if non-null)
+ *   out[dst_rows ? dst_rows[i] : i, :] = weight * h[i] * rsqrt(mean(h[i]^2) + eps)
+ * residual, sum_out, dst_rows may be NULL. */
+int cd_rmsnorm(const void* x, const void* residual, const void* weight, float eps, void* sum_out,
+               void* out, const int32_t* dst_rows, int T, int H, void* stream);
+
+/* out[j, :] = x[src_rows[j], :] — the gather `flat_x[mask]` of token_routed_mlp.py:170 for
+ * all experts at once, used when the MoE layer is called without the fused norm. */
+int cd_gather_rows(const void* x, const int32_t* src_rows, void* out, int T, int H, void* stream);
+
+/* ---- Q/K RMSNorm + rotary embedding, in place -------------------------------------------
+ * Replaces complexity_deep/core/attention.py:138-155 (q_norm/k_norm, cos/sin slicing,
+ * apply_rotary_pos_emb of complexity_deep/core/rotary.py:64-86) on the fused
+ * [T, (hq + 2*hkv) * D] projection buffer; the V columns are left untouched.  Token t sits
+ * at position pos0 + (t % S).  q_w / k_w ([D] bf16) may both be NULL (use_qk_norm=False).
+ * cos_t / sin_t are fp32 [>= pos0 + S, D].  D % 4 == 0. */
+int cd_qk_norm_rope(void* qkv, const void* q_w, const void* k_w, const float* cos_t,
+                    const float* sin_t, float eps, int T, int S, int pos0, int hq, int hkv, int D,
+                    void* stream);
+
+/* ---- expert up-projection with fused SwiGLU ---------------------------------------------
+ * Replaces gate/up GEMMs and silu(gate)*up of the routed experts
+ * (token_routed_mlp.py:171-173) or, with num_groups = 1 and seg_offsets = NULL, of the
+ * shared expert (:157-160) / the dense SwiGLU (complexity_deep/core/mlp.py:40).
+ *   h[r, :I] = silu(x[r] @ Wg[g]) * (x[r] @ Wu[g])   for rows r of group g
+ * x_sorted: [T, H] rows grouped by expert (seg_offsets[g] .. seg_offsets[g+1]).
+ * packed_w: [num_groups, cd_gate_up_packed_rows(I, block_n), H] — per group, for each tile
+ *   of block_n/2 output columns, block_n/2 gate rows followed by block_n/2 up rows (each
+ *   row = one output feature, H contiguous), zero rows padding the last tile.
+ * h: [T, I].  block_n is 128 or 256.  H % 8 == 0, I % 8 == 0. */
+int cd_gate_up_packed_rows(int I, int block_n);
+int cd_moe_up(const void* x_sorted, const int32_t* seg_offsets, int num_groups,
+              const void* packed_w, void* h, int T, int H, int I, int block_n, void* stream);
+
+/* ---- expert down-projection, combine, un-permute, residual -------------------------------
+ * Replaces the routed down GEMM and scatter (token_routed_mlp.py:174), the shared down GEMM
+ * (:157-160), `routed_out + shared_out` (:177) and the block's residual add
+ * (complexity_deep/core/layer.py:183) with ONE fp32 accumulation per output element:
+ *   out[row_map[r], :] = h_routed[r] @ Wd[g]^T + h_shared[r] @ Sd^T + residual[row_map[r], :]
+ * h_routed [T, I_e], h_shared [T, I_s] (NULL = no shared expert), rows in sorted order;
+ * wd_routed [E * H, I_e] (for expert e rows e*H..: one output feature per row, I_e
+ * contiguous); wd_shared [H, I_s]; row_map = perm (NULL = identity); residual (NULL = none)
+ * and out are [T, H] in ORIGINAL row order.  I_e % 8 == 0, I_s % 8 == 0, H % 8 == 0. */
+int cd_moe_down(const void* h_routed, int I_e, const void* wd_routed, const void* h_shared,
+                int I_s, const void* wd_shared, const int32_t* seg_offsets, int E,
+                const int32_t* row_map, const void* residual, void* out, int T, int H,
+                void* stream);
+
+/* ---- mu-guided QKV -------------------------------------------------------------------------
+ * Replaces complexity_deep/core/attention.py:120-131: torch.cat([x, mu_prev]) against the
+ * re-concatenated weights, three F.linear calls.  One GEMM whose K loop walks x then
+ * mu_prev; nothing is concatenated in memory:
+ *   qkv[t, :N] = x[t] @ w^T + mu_prev[t] @ w_mu^T,   N = q_dim + 2 * kv_dim
+ * w, w_mu: [N, H] = rows of q_proj, k_proj, v_proj (resp. mu_to_q, mu_to_k, mu_to_v) stacked.
+ * mu_prev / w_mu may be NULL (no mu guidance: plain q/k/v projections). */
+int cd_mu_qkv(const void* x, const void* mu_prev, const void* w, const void* w_mu, void* qkv,
+              int T, int H, int N, void* stream);
+
+/* ---- mu projection ------------------------------------------------------------------------
+ * Replaces MuGuidance.forward, complexity_deep/core/layer.py:54-61, and optionally the
+ * model's clamp of the result, complexity_deep/models/modeling.py:199-200:
+ *   out[t, n] = clamp(mu_param[n], mu_min, mu_max) + h[t] @ w[n]      (w = mu_proj.weight [H, H])
+ *   if clamp_out: out = clamp(out, out_lo, out_hi) */
+int cd_mu_proj(const void* h, const void* w, const void* mu_param, float mu_min, float mu_max,
+               int clamp_out, float out_lo, float out_hi, void* out, int T, int H, void* stream);
+
+/* ---- plain projection with optional residual ---------------------------------------------
+ * out[t, :N] = x[t, :K] @ w^T (+ residual[t, :N]);  w = nn.Linear weight [N, K].
+ * Replaces o_proj + residual (complexity_deep/core/attention.py:181 with layer.py:174) and
+ * lm_head (complexity_deep/models/modeling.py:206).  K % 8 == 0, N % 8 == 0. */
+int cd_linear(const void* x, const void* w, const void* residual, void* out, int T, int K, int N,
+              void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CDEEP_H_ */

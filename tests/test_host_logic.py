@@ -1,0 +1,175 @@
+"""Host-side mirror of the reference interface: names, constructor signatures, state_dict
+layout, table construction, weight packing, caches, and the no-fallback rule."""
+import inspect
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN, load_golden
+import complexity_deep_b200 as cd
+from complexity_deep_b200 import ops
+from complexity_deep_b200.core._cache import DerivedCache
+from complexity_deep_b200.core.token_routed_mlp import ROUTING_CACHE
+from complexity_deep_b200.models import (CausalLMOutput, ComplexityConfig, ComplexityModel,
+                                         ModelOutput, count_parameters, create_complexity_model)
+from oracle import complexity_oracle as oracle
+
+
+def _shapes(sd):
+    return {k: (tuple(v.shape), v.dtype) for k, v in sd.items()}
+
+
+def test_public_names():
+    for name in ["RMSNorm", "RotaryEmbedding", "ComplexityAttention", "SwiGLU", "TokenRoutedMLP",
+                 "TransformerBlock", "MuGuidance", "ComplexityConfig", "ComplexityModel",
+                 "create_complexity_model", "count_parameters"]:
+        assert hasattr(cd, name)
+    assert CausalLMOutput().logits is None and ModelOutput().last_hidden_state is None
+
+
+def test_constructor_signatures():
+    sig = lambda c: list(inspect.signature(c.__init__).parameters)[1:]
+    assert sig(cd.TokenRoutedMLP) == ["hidden_size", "intermediate_size", "num_experts",
+                                      "vocab_size", "shared_expert", "token_frequencies"]
+    assert sig(cd.ComplexityAttention) == ["hidden_size", "num_attention_heads",
+                                           "num_key_value_heads", "max_position_embeddings",
+                                           "rope_theta", "attention_dropout", "use_qk_norm"]
+    assert sig(cd.TransformerBlock) == [
+        "hidden_size", "intermediate_size", "num_attention_heads", "num_key_value_heads",
+        "max_position_embeddings", "rms_norm_eps", "rope_theta", "attention_dropout",
+        "use_token_routed_mlp", "num_experts", "vocab_size", "shared_expert", "token_frequencies",
+        "use_qk_norm", "use_mu_guidance"]
+    assert sig(cd.MuGuidance) == ["hidden_size", "mu_min", "mu_max"]
+    assert sig(cd.RMSNorm) == ["hidden_size", "eps"]
+    fwd = list(inspect.signature(cd.TransformerBlock.forward).parameters)[1:]
+    assert fwd == ["hidden_states", "attention_mask", "past_key_value", "use_cache", "token_ids",
+                   "mu_prev"]
+    fwd = list(inspect.signature(ComplexityModel.forward).parameters)[1:]
+    assert fwd == ["input_ids", "attention_mask", "labels", "past_key_values", "use_cache"]
+
+
+def test_state_dict_layout_matches_reference_checkpoints():
+    g = load_golden("model_tiny.pt")
+    model = ComplexityModel(ComplexityConfig.from_dict(g["config"]))
+    assert _shapes(model.state_dict()) == _shapes(g["state"])
+    missing, unexpected = model.load_state_dict(g["state"], strict=True)
+    assert not missing and not unexpected
+    assert model.lm_head.weight is model.embed_tokens.weight
+
+    g = load_golden("moe_layer.pt")
+    mlp = cd.TokenRoutedMLP(**g["config"], shared_expert=True)
+    assert _shapes(mlp.state_dict()) == _shapes(g["state"])
+    g = load_golden("attention.pt")
+    assert _shapes(cd.ComplexityAttention(64, 4, 2).state_dict()) == _shapes(g["state"])
+    g = load_golden("block.pt")
+    blk = cd.TransformerBlock(64, 128, 4, 2, num_experts=4, vocab_size=256)
+    assert _shapes(blk.state_dict()) == _shapes(g["state"])
+
+
+def test_init_statistics_follow_reference_rules():
+    torch.manual_seed(0)
+    cfg = ComplexityConfig(vocab_size=512, hidden_size=128, intermediate_size=256,
+                           num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2)
+    m = ComplexityModel(cfg)
+    rstd = 0.02 / (2 * 4) ** 0.5
+    l0 = m.layers[0]
+    assert abs(l0.self_attn.q_proj.weight.std().item() - 0.02) < 2e-3
+    assert abs(l0.mu_guidance.mu_proj.weight.std().item() - 0.02) < 2e-3   # re-drawn, not zero
+    assert abs(l0.self_attn.o_proj.weight.std().item() - rstd) < 1e-3
+    assert abs(l0.mlp.down_proj_w.std().item() - rstd) < 1e-3
+    assert abs(l0.mlp.shared_down.weight.std().item() - rstd) < 1e-3
+    assert abs(l0.mlp.gate_proj_w.std().item() - 0.02) < 2e-3
+    assert torch.all(m.mu_init == 0) and torch.all(l0.mu_guidance.mu == 1.0)
+    assert torch.equal(l0.mlp.token_to_expert, torch.arange(512) % 4)
+
+
+def test_token_mapping_bit_exact_with_reference_tables():
+    g = np.load(os.path.join(GOLDEN, "routing.npz"))
+    p = oracle.zipf_probabilities(32000, 1.1).float()
+    t8 = cd.TokenRoutedMLP._build_token_mapping(32000, 8, p)
+    assert t8.dtype == torch.int64
+    assert np.array_equal(t8.numpy(), g["table_e8"].astype(np.int64))
+    t4 = cd.TokenRoutedMLP._build_token_mapping(32000, 4, p)
+    assert np.array_equal(t4.numpy(), g["table_e4"].astype(np.int64))
+    # ties (equal frequencies) follow the reference's argsort + first-minimum rule
+    f = torch.tensor([0.25, 0.25, 0.25, 0.25, 0.1, 0.1, 0.0, 0.0])
+    assert np.array_equal(cd.TokenRoutedMLP._build_token_mapping(8, 3, f).numpy(),
+                          oracle.build_token_mapping(8, 3, f))
+    with pytest.raises(ValueError):
+        cd.TokenRoutedMLP._build_token_mapping(8, 3, torch.ones(7))
+
+
+def test_config_presets_and_serialisation():
+    c = ComplexityConfig.complexity_1b()
+    assert (c.hidden_size, c.intermediate_size, c.num_hidden_layers, c.num_attention_heads,
+            c.num_key_value_heads, c.num_experts, c.vocab_size) == (2048, 5632, 24, 16, 8, 8, 100000)
+    d = c.to_dict()
+    d["unknown_key"] = 1
+    assert ComplexityConfig.from_dict(d) == c
+    assert ComplexityConfig().num_hidden_layers == 12 and ComplexityConfig().eos_token_id == 0
+    n = count_parameters(ComplexityConfig(vocab_size=32000, hidden_size=768, num_hidden_layers=18))
+    assert n["total"] == n["embedding"] + 18 * n["per_layer"] + 768
+    with pytest.raises(ValueError):
+        create_complexity_model("nope")
+    m = create_complexity_model("tiny", vocab_size=128, num_hidden_layers=1, bogus=3)
+    assert len(m.layers) == 1 and m.config.vocab_size == 128
+
+
+def test_pack_gate_up_layout():
+    G, I, H = 2, 40, 8
+    gate = torch.arange(G * I * H, dtype=torch.float32).view(G, I, H)
+    up = -gate
+    packed = ops.pack_gate_up(gate, up, 128)          # half = 64 -> one tile, 24 zero rows
+    assert packed.shape == (G, 128, H)
+    assert torch.equal(packed[:, :40], gate) and torch.equal(packed[:, 64:104], up)
+    assert torch.all(packed[:, 40:64] == 0) and torch.all(packed[:, 104:] == 0)
+    gate2 = torch.randn(1, 200, 8)
+    packed2 = ops.pack_gate_up(gate2, 2 * gate2, 256)  # half = 128 -> two tiles
+    assert packed2.shape == (1, 512, 8)
+    assert torch.equal(packed2[0, 256:256 + 72], gate2[0, 128:])
+    assert torch.equal(packed2[0, 384:384 + 72], 2 * gate2[0, 128:])
+    assert ops.choose_block_n(5632) == 256 and ops.choose_block_n(704) == 128
+    assert ops.choose_block_n(2816) == 256 and ops.choose_block_n(512) == 256
+
+
+def test_derived_cache_tracks_in_place_mutation():
+    cache = DerivedCache()
+    w = torch.ones(4)
+    calls = []
+    make = lambda: (calls.append(1), w * 2)[1]
+    a = cache.get("x", (w,), make)
+    b = cache.get("x", (w,), make)
+    assert a is b and len(calls) == 1
+    w.mul_(3)                                  # what the reference's ablation scripts do
+    c = cache.get("x", (w,), make)
+    assert len(calls) == 2 and torch.equal(c, torch.full((4,), 6.0))
+    w2 = w.clone()
+    cache.get("x", (w2,), make)
+    assert len(calls) == 3
+
+
+def test_no_cpu_fallback():
+    mlp = cd.TokenRoutedMLP(64, 128, 4, 256)
+    x = torch.randn(1, 4, 64)
+    ids = torch.randint(0, 256, (1, 4))
+    with pytest.raises(RuntimeError, match="no CPU path|CUDA"):
+        mlp(x, ids)
+    with pytest.raises(RuntimeError):
+        cd.RMSNorm(64)(x)
+    with pytest.raises(RuntimeError):
+        cd.MuGuidance(64)(x)
+    ROUTING_CACHE.clear()
+
+
+def test_table_validation():
+    mlp = cd.TokenRoutedMLP(64, 128, 4, 256)
+    mlp.token_to_expert[3] = 7
+    with pytest.raises(ValueError, match="outside"):
+        mlp._table_signature()
+    mlp.token_to_expert[3] = 1
+    sig = mlp._table_signature()
+    assert sig == mlp._table_signature()
+    mlp.token_to_expert.zero_()               # ablation: in-place edit must change the signature
+    assert mlp._table_signature() != sig
