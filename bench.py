@@ -1,0 +1,319 @@
+#!/usr/bin/env python
+"""Prefill throughput of the 1B-class Complexity model (bf16) on B200 — the metric of
+BASELINE.json — through the drop-in ``ComplexityModel`` API of this repository.
+
+    python bench.py --gpus 1 --steps 10 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+    python bench.py --impl reference ...      # CPU arm: the oracle port on the host cores
+
+One step = one forward pass to logits over this rank's share of the global batch
+(32 sequences x 2048 tokens, split data-parallel across ranks; no collective on the data
+path).  Rank 0 prints ONE JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "prefill tokens/s (1B bf16)"
+UNIT = "tokens/s"
+WORKLOAD = "1B-class prefill: hidden 2048, 24 layers, 16Q/8KV (D 128), intermediate 5632, " \
+           "8 experts + shared, mu guidance, vocab 32000, batch 32 x seq 2048 Zipf(1.1) ids"
+MODEL = dict(vocab_size=32000, hidden_size=2048, intermediate_size=5632, num_hidden_layers=24,
+             num_attention_heads=16, num_key_value_heads=8, num_experts=8)
+GLOBAL_BATCH, SEQ_LEN = 32, 2048
+
+
+def shard_batch(global_batch: int, world: int, rank: int):
+    """Contiguous split of the batch rows across ranks (sizes differ by at most one)."""
+    base, extra = divmod(global_batch, world)
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
+
+
+def flops_per_token(cfg: dict, seq_len: int) -> dict:
+    """Algorithmic FLOPs per token of each GEMM entry point (per layer unless noted)."""
+    H, V, L = cfg["hidden_size"], cfg["vocab_size"], cfg["num_hidden_layers"]
+    I_e = cfg["intermediate_size"] // cfg["num_experts"]
+    D = H // cfg["num_attention_heads"]
+    q_dim, kv_dim = cfg["num_attention_heads"] * D, cfg["num_key_value_heads"] * D
+    return {
+        "mu_qkv": 2 * 2 * H * (q_dim + 2 * kv_dim),
+        "linear_o_proj": 2 * q_dim * H,
+        "moe_up_routed": 4 * H * I_e,
+        "moe_up_shared": 4 * H * I_e,
+        "moe_down": 2 * H * (2 * I_e),
+        "mu_proj": 2 * H * H,
+        "linear_lm_head": 2 * H * V,          # once per token, not per layer
+        "attention": 4 * seq_len * q_dim // 2,
+        "layers": L,
+    }
+
+
+def peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return {"bf16_tflops": d["bf16_tflops"], "bf16_tflops_sustained": d.get("bf16_tflops_sustained"),
+                "hbm_gbs": d["hbm_gbs"], "source": "measured"}
+    return {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0,
+            "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        rows = [r for r in self.rows if len(r) == 6 and r[0].isdigit()]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i] == "Active" for r in rows)]
+        return {"sm_mhz": statistics.median(int(r[0]) for r in rows),
+                "sm_max_mhz": int(rows[0][1]), "samples": len(rows), "reasons": reasons}
+
+
+# ------------------------------------------------------------------------------- our arm
+def build_model(device):
+    from complexity_deep_b200 import TokenRoutedMLP
+    from complexity_deep_b200.models import ComplexityConfig, ComplexityModel
+    from oracle.complexity_oracle import zipf_probabilities  # input distribution only
+    torch.manual_seed(0)
+    with torch.device(device):
+        model = ComplexityModel(ComplexityConfig(**MODEL))
+    model = model.to(dtype=torch.bfloat16).eval()
+    table = TokenRoutedMLP._build_token_mapping(
+        MODEL["vocab_size"], MODEL["num_experts"], zipf_probabilities(MODEL["vocab_size"], 1.1).float())
+    with torch.no_grad():
+        for layer in model.layers:
+            layer.mlp.token_to_expert.copy_(table)
+    return model
+
+
+def run_ours(args):
+    from complexity_deep_b200 import ops
+    from oracle.complexity_oracle import zipf_token_ids  # input distribution only
+    rank = int(os.environ.get("RANK", 0))
+    local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    model = build_model(dev)
+    batch = args.batch or GLOBAL_BATCH
+    lo, hi = shard_batch(batch, world, rank)
+    n_local = hi - lo
+    steps_total = args.warmup + args.steps
+    # a different id batch per step, all drawn up front on the host (seeded), pinned
+    host_ids = [zipf_token_ids(MODEL["vocab_size"], 1.1, batch * SEQ_LEN, seed=s)
+                .view(batch, SEQ_LEN)[lo:hi].contiguous().pin_memory() for s in range(steps_total)]
+    dev_ids = [h.to(dev) for h in host_ids]
+    host_next = torch.empty(n_local, dtype=torch.int64).pin_memory()
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    @torch.no_grad()
+    def step_device(i):
+        return model(dev_ids[i]).logits
+
+    @torch.no_grad()
+    def step_e2e(i):
+        ids = host_ids[i].to(dev, non_blocking=True)
+        logits = model(ids).logits
+        host_next.copy_(logits[:, -1, :].argmax(-1), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return host_next
+
+    def timed(step_fn, instrument):
+        for i in range(args.warmup):
+            step_fn(i)
+        barrier()
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        ops.PROFILE.reset(enabled=instrument)
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for i in range(args.warmup, steps_total):
+            step_fn(i)
+        t1.record()
+        barrier()
+        ms = torch.tensor([t0.elapsed_time(t1)], device=dev)
+        if dist is not None:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        clocks = sampler.stop()
+        prof = ops.PROFILE.collect()
+        ops.PROFILE.reset(enabled=False)
+        return float(ms.item()), clocks, prof
+
+    ms_dev, clocks, prof = timed(step_device, instrument=True)
+    ms_e2e, clocks_e2e, _ = timed(step_e2e, instrument=False)
+    ops.status_fetch()
+
+    tokens_per_step = batch * SEQ_LEN
+    value = tokens_per_step * args.steps / (ms_dev / 1e3)
+    e2e = tokens_per_step * args.steps / (ms_e2e / 1e3)
+
+    # roofline of the dominant GEMM entry point, from the events recorded in the timed region
+    pk = peaks()
+    fl = flops_per_token(MODEL, SEQ_LEN)
+    local_tokens = n_local * SEQ_LEN
+    kernels = {}
+    for name, (launches, total_ms, kernel_launches) in prof.items():
+        entry = {"launches": launches, "ms_total": round(total_ms, 3)}
+        if name in fl:
+            flop = fl[name] * local_tokens
+            tf = flop / (total_ms / launches / 1e3) / 1e12
+            entry.update(tflops=round(tf, 1), frac=round(tf / pk["bf16_tflops"], 4))
+        kernels[name] = entry
+    gemm_names = [n for n in kernels if n in fl]
+    dom = max(gemm_names, key=lambda n: kernels[n]["ms_total"]) if gemm_names else None
+    roofline = None
+    if dom:
+        k = kernels[dom]
+        roofline = {"bound": "tensor", "kernel": "gemm_bf16_sm100_kernel", "entry": dom, "achieved": k["tflops"], "peak": pk["bf16_tflops"],
+                    "peak_source": pk["source"] + " burst", "unit": "TFLOP/s", "frac": k["frac"],
+                    "flop_per_launch": fl[dom] * local_tokens,
+                    "ms_per_launch": round(k["ms_total"] / k["launches"], 4), "traffic": None}
+    gpu_launches = sum(v[2] for v in prof.values())
+
+    line = {
+        "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_dev / args.steps, 3),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "impl": "b200",
+        "config": {"workload": WORKLOAD, "global_batch": batch, "seq_len": SEQ_LEN,
+                   "parallelism": f"dp{world}", "tokens_per_gpu_per_step": local_tokens,
+                   "l2": "no flush: per-step working set (3.2 GB weights, 268 MB per activation) >> 126 MB L2; new ids each step"},
+        "e2e": {"value": round(e2e, 1), "unit": UNIT, "ms_per_step": round(ms_e2e / args.steps, 3),
+                "h2d_bytes_per_step": n_local * SEQ_LEN * 8, "d2h_bytes_per_step": n_local * 8,
+                "result": "next-token argmax of the last position of every sequence"},
+        "gpu_launches": gpu_launches,
+        "clocks": clocks, "clocks_e2e": clocks_e2e,
+        "roofline": roofline, "kernels": kernels,
+        "model_flops_utilisation": round(
+            (sum(fl[k] for k in ("mu_qkv", "linear_o_proj", "moe_up_routed", "moe_up_shared",
+                                 "moe_down", "mu_proj", "attention")) * fl["layers"]
+             + fl["linear_lm_head"]) * value / world / 1e12 / pk["bf16_tflops"], 4),
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(sample_tokens=args.cpu_tokens, steps=1, warmup=0)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------------------- CPU arm
+def cpu_baseline(sample_tokens: int, steps: int, warmup: int) -> dict:
+    """Times the oracle port (a restatement of the reference's PyTorch forward) on the host
+    cores, fp32, on one sequence of `sample_tokens` tokens of the same workload."""
+    from oracle import complexity_oracle as oracle
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    cfg = dict(MODEL)
+    p = oracle.zipf_probabilities(cfg["vocab_size"], 1.1).float()
+    from complexity_deep_b200 import TokenRoutedMLP  # host-side table builder (bit-exact, fast)
+    cfg["token_to_expert"] = TokenRoutedMLP._build_token_mapping(cfg["vocab_size"],
+                                                                 cfg["num_experts"], p)
+    sd = oracle.random_model_state(cfg, seed=0, dtype=torch.float32)
+    times = []
+    with torch.no_grad():
+        for i in range(warmup + steps):
+            ids = oracle.zipf_token_ids(cfg["vocab_size"], 1.1, sample_tokens, seed=i).view(1, -1)
+            t = time.perf_counter()
+            oracle.model_forward(sd, cfg, ids)
+            if i >= warmup:
+                times.append(time.perf_counter() - t)
+    total = sum(times)
+    return {"value": round(sample_tokens * len(times) / total, 1), "unit": UNIT, "cores": cores,
+            "kind": "port", "dtype": "f32", "seconds_per_step": round(total / len(times), 3),
+            "sample": f"1 sequence x {sample_tokens} tokens of the same model (all 24 layers + lm_head), "
+                      f"oracle port of the reference's PyTorch forward, {cores} threads"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", 0))
+    if rank != 0:
+        return
+    base = cpu_baseline(sample_tokens=args.cpu_tokens, steps=args.steps, warmup=args.warmup)
+    line = {
+        "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(base["seconds_per_step"] * 1e3, 1), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "impl": "reference",
+        "config": {"workload": WORKLOAD, "global_batch": GLOBAL_BATCH, "seq_len": SEQ_LEN,
+                   "parallelism": "host cores"},
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=8)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--batch", type=int, default=0, help="global batch override (debug only)")
+    ap.add_argument("--cpu-tokens", type=int, default=1024,
+                    help="tokens of the bounded CPU sample (one sequence)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "b200":
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

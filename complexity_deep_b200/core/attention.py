@@ -99,14 +99,16 @@ class ComplexityAttention(nn.Module):
             v = torch.cat([past_key_value[1], v], dim=2)
         new_kv = (k, v) if use_cache else None
 
-        attn = F.scaled_dot_product_attention(
-            q, k, v,
-            attn_mask=attention_mask,
-            dropout_p=self.attention_dropout if self.training else 0.0,
-            is_causal=(attention_mask is None),
-            enable_gqa=self.num_kv_groups > 1,
-        )
-        return attn.transpose(1, 2).reshape(B * S, hq * D).contiguous(), new_kv
+        with ops._Span("sdpa", kernels=0):  # PyTorch operator, timed for the breakdown only
+            attn = F.scaled_dot_product_attention(
+                q, k, v,
+                attn_mask=attention_mask,
+                dropout_p=self.attention_dropout if self.training else 0.0,
+                is_causal=(attention_mask is None),
+                enable_gqa=self.num_kv_groups > 1,
+            )
+            attn = attn.transpose(1, 2).reshape(B * S, hq * D).contiguous()
+        return attn, new_kv
 
     def forward(
         self,
@@ -119,7 +121,7 @@ class ComplexityAttention(nn.Module):
         B, S, H = hidden_states.shape
         attn, new_kv = self._attend(hidden_states, attention_mask, past_key_value, use_cache,
                                     mu_prev)
-        return ops.linear(attn, self.o_proj.weight).view(B, S, H), new_kv
+        return ops.linear(attn, self.o_proj.weight, tag="linear_o_proj").view(B, S, H), new_kv
 
     def forward_with_residual(self, hidden_states, residual, attention_mask=None,
                               past_key_value=None, use_cache=False, mu_prev=None):
@@ -127,5 +129,5 @@ class ComplexityAttention(nn.Module):
         B, S, H = hidden_states.shape
         attn, new_kv = self._attend(hidden_states, attention_mask, past_key_value, use_cache,
                                     mu_prev)
-        out = ops.linear(attn, self.o_proj.weight, residual.reshape(B * S, H))
+        out = ops.linear(attn, self.o_proj.weight, residual.reshape(B * S, H), tag="linear_o_proj")
         return out.view(B, S, H), new_kv

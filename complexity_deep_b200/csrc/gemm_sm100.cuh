@@ -229,6 +229,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
         }
       }
     }
+    __syncwarp();
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
@@ -267,6 +268,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
         if (ok) umma_commit(&tmem_full[acc]);  // accumulator complete
       }
     }
+    __syncwarp();
   } else {
     // ------------------------------------------------------------ epilogue (4 warps)
     const int quarter = warp & 3;  // TMEM lane quarter this warp may read
@@ -381,6 +383,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
+    __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }

@@ -125,7 +125,7 @@ class ComplexityModel(nn.Module):
                 new_kvs.append(new_kv)
 
         normed = ops.rmsnorm(hidden.reshape(B * S, H).contiguous(), self.norm.weight, self.norm.eps)
-        logits = ops.linear(normed, self.lm_head.weight).view(B, S, -1)
+        logits = ops.linear(normed, self.lm_head.weight, tag="linear_lm_head").view(B, S, -1)
 
         loss = None
         if labels is not None:

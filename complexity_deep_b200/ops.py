@@ -36,6 +36,55 @@ def _need(t: torch.Tensor, name: str, dtype=BF16) -> None:
         raise RuntimeError(f"{name}: expected a contiguous tensor")
 
 
+class _Profile:
+    """Optional CUDA-event timing of the GEMM entry points (used by bench.py).
+
+    Disabled by default: then `span` costs one attribute check.  When enabled, every call of
+    an instrumented entry point records an event before and after its launch on the current
+    stream; `collect` synchronises and returns per-entry launch counts and device time.
+    """
+
+    def __init__(self) -> None:
+        self.enabled = False
+        self.events = []
+        self.kernel_launches = 0
+
+    def reset(self, enabled: bool) -> None:
+        self.enabled = enabled
+        self.events = []
+        self.kernel_launches = 0
+
+    def collect(self):
+        """name -> (calls, total_ms, kernels launched)."""
+        torch.cuda.synchronize()
+        out = {}
+        for name, a, b, n in self.events:
+            c, ms, k = out.get(name, (0, 0.0, 0))
+            out[name] = (c + 1, ms + a.elapsed_time(b), k + n)
+        return out
+
+
+PROFILE = _Profile()
+
+
+class _Span:
+    def __init__(self, name: str, kernels: int = 1) -> None:
+        self.name, self.kernels = name, kernels
+
+    def __enter__(self):
+        if PROFILE.enabled:
+            self.start = torch.cuda.Event(enable_timing=True)
+            self.start.record()
+        return self
+
+    def __exit__(self, *exc):
+        if PROFILE.enabled:
+            end = torch.cuda.Event(enable_timing=True)
+            end.record()
+            PROFILE.events.append((self.name, self.start, end, self.kernels))
+        return False
+
+
 def status_fetch() -> int:
     """Synchronises and returns the kernels' status word (0 = ok); raises on a timeout."""
     lib = _lib.load()
@@ -73,10 +122,11 @@ def route(token_ids: torch.Tensor, table: torch.Tensor, num_experts: int) -> Rou
     offsets = torch.empty(E + 1, **i32)
     ws_bytes = lib.cd_route_workspace_bytes(T, E)
     ws = torch.empty(max(ws_bytes, 4), dtype=torch.uint8, device=dev)
-    _lib.check(lib.cd_route(ids.data_ptr(), table.data_ptr(), V, E, T, expert_ids.data_ptr(),
-                            counts.data_ptr(), offsets.data_ptr(), perm.data_ptr(),
-                            inv_perm.data_ptr(), ws.data_ptr(), ws.numel(), _stream()),
-               "cd_route")
+    with _Span("route", 2):
+        _lib.check(lib.cd_route(ids.data_ptr(), table.data_ptr(), V, E, T, expert_ids.data_ptr(),
+                                counts.data_ptr(), offsets.data_ptr(), perm.data_ptr(),
+                                inv_perm.data_ptr(), ws.data_ptr(), ws.numel(), _stream()),
+                   "cd_route")
     return Routing(expert_ids, counts, offsets, perm, inv_perm, E)
 
 
@@ -102,8 +152,10 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float,
         _need(dst_rows, "dst_rows", torch.int32)
     out = torch.empty_like(x2)
     s = torch.empty_like(x2) if (want_sum and res2 is not None) else None
-    _lib.check(lib.cd_rmsnorm(x2.data_ptr(), _ptr(res2), weight.data_ptr(), float(eps), _ptr(s),
-                              out.data_ptr(), _ptr(dst_rows), T, H, _stream()), "cd_rmsnorm")
+    with _Span("rmsnorm"):
+        _lib.check(lib.cd_rmsnorm(x2.data_ptr(), _ptr(res2), weight.data_ptr(), float(eps),
+                                  _ptr(s), out.data_ptr(), _ptr(dst_rows), T, H, _stream()),
+                   "cd_rmsnorm")
     out = out.view(x.shape)
     if want_sum:
         return (s.view(x.shape) if s is not None else x), out
@@ -117,8 +169,9 @@ def gather_rows(x: torch.Tensor, src_rows: torch.Tensor) -> torch.Tensor:
     _need(x2, "x")
     _need(src_rows, "src_rows", torch.int32)
     out = torch.empty_like(x2)
-    _lib.check(lib.cd_gather_rows(x2.data_ptr(), src_rows.data_ptr(), out.data_ptr(), x2.shape[0],
-                                  H, _stream()), "cd_gather_rows")
+    with _Span("gather_rows"):
+        _lib.check(lib.cd_gather_rows(x2.data_ptr(), src_rows.data_ptr(), out.data_ptr(),
+                                      x2.shape[0], H, _stream()), "cd_gather_rows")
     return out
 
 
@@ -138,9 +191,10 @@ def qk_norm_rope_(qkv: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Optional[
         raise RuntimeError("qkv width does not match the head layout")
     if cos.shape[0] < pos0 + seq_len or cos.shape[1] != head_dim:
         raise RuntimeError("cos/sin tables too short for the requested positions")
-    _lib.check(lib.cd_qk_norm_rope(qkv.data_ptr(), _ptr(q_w), _ptr(k_w), cos.data_ptr(),
-                                   sin.data_ptr(), float(eps), T, seq_len, pos0, hq, hkv,
-                                   head_dim, _stream()), "cd_qk_norm_rope")
+    with _Span("qk_norm_rope"):
+        _lib.check(lib.cd_qk_norm_rope(qkv.data_ptr(), _ptr(q_w), _ptr(k_w), cos.data_ptr(),
+                                       sin.data_ptr(), float(eps), T, seq_len, pos0, hq, hkv,
+                                       head_dim, _stream()), "cd_qk_norm_rope")
     return qkv
 
 
@@ -189,9 +243,10 @@ def moe_up(x_sorted: torch.Tensor, seg_offsets: Optional[torch.Tensor], num_grou
     if seg_offsets is not None:
         _need(seg_offsets, "seg_offsets", torch.int32)
     h = torch.empty(T, width, dtype=BF16, device=x_sorted.device)
-    _lib.check(lib.cd_moe_up(x_sorted.data_ptr(), _ptr(seg_offsets), num_groups,
-                             packed_w.data_ptr(), h.data_ptr(), T, H, width, block_n, _stream()),
-               "cd_moe_up")
+    with _Span("moe_up_routed" if seg_offsets is not None else "moe_up_shared"):
+        _lib.check(lib.cd_moe_up(x_sorted.data_ptr(), _ptr(seg_offsets), num_groups,
+                                 packed_w.data_ptr(), h.data_ptr(), T, H, width, block_n,
+                                 _stream()), "cd_moe_up")
     return h
 
 
@@ -225,9 +280,10 @@ def moe_down(h_routed: torch.Tensor, wd_routed: torch.Tensor, h_shared: Optional
         if res2.shape[0] != T:
             raise RuntimeError("residual rows do not match")
     out = torch.empty(T, H, dtype=BF16, device=h_routed.device)
-    _lib.check(lib.cd_moe_down(h_routed.data_ptr(), I_e, wd_routed.data_ptr(), _ptr(h_shared),
-                               I_s, _ptr(wd_shared), _ptr(seg_offsets), E, _ptr(row_map),
-                               _ptr(res2), out.data_ptr(), T, H, _stream()), "cd_moe_down")
+    with _Span("moe_down"):
+        _lib.check(lib.cd_moe_down(h_routed.data_ptr(), I_e, wd_routed.data_ptr(), _ptr(h_shared),
+                                   I_s, _ptr(wd_shared), _ptr(seg_offsets), E, _ptr(row_map),
+                                   _ptr(res2), out.data_ptr(), T, H, _stream()), "cd_moe_down")
     return out
 
 
@@ -244,9 +300,10 @@ def mu_qkv(x: torch.Tensor, mu_prev: Optional[torch.Tensor], w: torch.Tensor,
         if tuple(mu_prev.shape) != (T, H) or tuple(w_mu.shape) != (N, H):
             raise RuntimeError("mu_prev / mu weights do not match x / qkv weights")
     out = torch.empty(T, N, dtype=BF16, device=x.device)
-    _lib.check(lib.cd_mu_qkv(x.data_ptr(), _ptr(mu_prev), w.data_ptr(),
-                             _ptr(w_mu) if mu_prev is not None else None, out.data_ptr(), T, H, N,
-                             _stream()), "cd_mu_qkv")
+    with _Span("mu_qkv"):
+        _lib.check(lib.cd_mu_qkv(x.data_ptr(), _ptr(mu_prev), w.data_ptr(),
+                                 _ptr(w_mu) if mu_prev is not None else None, out.data_ptr(), T,
+                                 H, N, _stream()), "cd_mu_qkv")
     return out
 
 
@@ -259,14 +316,15 @@ def mu_proj(h: torch.Tensor, w: torch.Tensor, mu_param: torch.Tensor, mu_min: fl
     T, H = h.shape
     out = torch.empty(T, H, dtype=BF16, device=h.device)
     lo, hi = out_clamp if out_clamp is not None else (0.0, 0.0)
-    _lib.check(lib.cd_mu_proj(h.data_ptr(), w.data_ptr(), mu_param.data_ptr(), float(mu_min),
-                              float(mu_max), 1 if out_clamp is not None else 0, float(lo),
-                              float(hi), out.data_ptr(), T, H, _stream()), "cd_mu_proj")
+    with _Span("mu_proj"):
+        _lib.check(lib.cd_mu_proj(h.data_ptr(), w.data_ptr(), mu_param.data_ptr(), float(mu_min),
+                                  float(mu_max), 1 if out_clamp is not None else 0, float(lo),
+                                  float(hi), out.data_ptr(), T, H, _stream()), "cd_mu_proj")
     return out
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = None
-           ) -> torch.Tensor:
+def linear(x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = None,
+           tag: str = "linear") -> torch.Tensor:
     lib = _lib.load()
     _need(x, "x")
     _need(w, "weight")
@@ -279,6 +337,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = 
         if tuple(residual.shape) != (T, N):
             raise RuntimeError("residual does not match the output")
     out = torch.empty(T, N, dtype=BF16, device=x.device)
-    _lib.check(lib.cd_linear(x.data_ptr(), w.data_ptr(), _ptr(residual), out.data_ptr(), T, K, N,
-                             _stream()), "cd_linear")
+    with _Span(tag):
+        _lib.check(lib.cd_linear(x.data_ptr(), w.data_ptr(), _ptr(residual), out.data_ptr(), T, K,
+                                 N, _stream()), "cd_linear")
     return out

@@ -1,0 +1,175 @@
+"""tcgen05 GEMM entry points through the C ABI vs fp32 oracle arithmetic on the same
+bf16-rounded inputs.
+
+Tolerance (stated by the path's specification): max|y - ref| / max|ref| <= 2e-2 and
+mean|y - ref| <= 2e-3 for outputs of unit scale; for outputs of another scale the mean bound
+is taken relative to rms(ref).  The kernels accumulate in fp32 and round once (twice where
+the SwiGLU intermediate h is stored in bf16), so the observed errors sit well inside."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import complexity_oracle as oracle
+
+pytestmark = pytest.mark.gpu
+BF = torch.bfloat16
+
+
+def _rand(g, *shape, scale=1.0):
+    return (torch.randn(*shape, generator=g) * scale).to(BF)
+
+
+def _close(got, ref, max_rel=2e-2, mean_rel=2e-3):
+    got, ref = got.float().cpu(), ref.float().cpu()
+    mr, ma = oracle.error_metrics(got, ref)
+    rms = float(ref.double().pow(2).mean().sqrt())
+    assert torch.isfinite(got).all()
+    assert mr <= max_rel and ma <= mean_rel * max(rms, 1e-30), (mr, ma, rms)
+
+
+def _fetch():
+    from complexity_deep_b200 import ops
+    ops.status_fetch()
+
+
+@pytest.mark.parametrize("T,K,N", [(128, 64, 256), (128, 64, 128), (128, 128, 256), (256, 512, 512),
+                                   (100, 64, 8), (1, 72, 40), (333, 200, 264), (1000, 768, 1024),
+                                   (4096, 2048, 2048), (129, 1032, 520)])
+@pytest.mark.parametrize("with_res", [False, True])
+def test_linear(T, K, N, with_res):
+    from complexity_deep_b200 import ops
+    g = torch.Generator().manual_seed(T + K + N)
+    x, w = _rand(g, T, K), _rand(g, N, K, scale=0.05)
+    res = _rand(g, T, N) if with_res else None
+    out = ops.linear(x.cuda(), w.cuda(), res.cuda() if with_res else None)
+    _fetch()
+    ref = x.float() @ w.float().t()
+    if with_res:
+        ref = ref + res.float()
+    _close(out, ref)
+
+
+def test_linear_many_tiles_persistent_schedule():
+    """More tiles than SMs and more k-blocks than pipeline stages: exercises barrier phase
+    wrap-around, both TMEM accumulators and the band schedule."""
+    from complexity_deep_b200 import ops
+    g = torch.Generator().manual_seed(5)
+    T, K, N = 128 * 40 + 17, 64 * 13, 256 * 9 + 64
+    x, w = _rand(g, T, K), _rand(g, N, K, scale=0.05)
+    out = ops.linear(x.cuda(), w.cuda())
+    _fetch()
+    ref = (x.cuda().float() @ w.cuda().float().t())      # fp32 reference on the device
+    _close(out, ref)
+    out2 = ops.linear(x.cuda(), w.cuda())
+    assert torch.equal(out, out2)                        # deterministic
+
+
+@pytest.mark.parametrize("T,H,N", [(64, 64, 128), (300, 256, 384), (2048, 768, 1280)])
+def test_mu_qkv_k_concat(T, H, N):
+    from complexity_deep_b200 import ops
+    g = torch.Generator().manual_seed(7)
+    x, mu = _rand(g, T, H), _rand(g, T, H)
+    w, wm = _rand(g, N, H, scale=0.05), _rand(g, N, H, scale=0.05)
+    out = ops.mu_qkv(x.cuda(), mu.cuda(), w.cuda(), wm.cuda())
+    _fetch()
+    # reference arithmetic: cat([x, mu]) @ cat([W, W_mu], dim=1)^T  (attention.py:121-127)
+    ref = F.linear(torch.cat([x, mu], -1).float(), torch.cat([w, wm], 1).float())
+    _close(out, ref)
+    out_nomu = ops.mu_qkv(x.cuda(), None, w.cuda(), None)
+    _close(out_nomu, x.float() @ w.float().t())
+
+
+@pytest.mark.parametrize("T,H", [(40, 64), (513, 768)])
+def test_mu_proj_bias_and_clamp(T, H):
+    from complexity_deep_b200 import ops
+    g = torch.Generator().manual_seed(9)
+    h, w = _rand(g, T, H), _rand(g, H, H, scale=0.05)
+    mu = (torch.randn(H, generator=g) * 1.5 + 1.0).to(BF)
+    ref = torch.clamp(mu.float(), 0.0, 2.0) + h.float() @ w.float().t()     # layer.py:61
+    out = ops.mu_proj(h.cuda(), w.cuda(), mu.cuda(), 0.0, 2.0)
+    _fetch()
+    _close(out, ref)
+    out_c = ops.mu_proj(h.cuda(), w.cuda(), mu.cuda(), 0.0, 2.0, out_clamp=(-2.0, 2.0))
+    _close(out_c, ref.clamp(-2.0, 2.0))                                     # modeling.py:200
+    assert out_c.float().abs().max() <= 2.0
+
+
+def _swiglu_ref(x, gate, up):
+    return F.silu(x.float() @ gate.float().t()) * (x.float() @ up.float().t())
+
+
+@pytest.mark.parametrize("T,H,I,bn", [(128, 64, 128, 256), (200, 128, 64, 128), (77, 256, 40, 128),
+                                      (1000, 768, 512, 256), (512, 2048, 704, 128),
+                                      (512, 2048, 704, 256), (300, 512, 200, 256)])
+def test_moe_up_dense(T, H, I, bn):
+    from complexity_deep_b200 import ops
+    g = torch.Generator().manual_seed(11)
+    x = _rand(g, T, H)
+    gate, up = _rand(g, I, H, scale=0.05), _rand(g, I, H, scale=0.05)
+    packed = ops.pack_gate_up(gate[None].cuda(), up[None].cuda(), bn)
+    h = ops.moe_up(x.cuda(), None, 1, packed, I, bn)
+    _fetch()
+    _close(h, _swiglu_ref(x, gate, up))
+
+
+def _segments(g, T, E, empty=()):
+    w = torch.rand(E, generator=g) + 0.1
+    for e in empty:
+        w[e] = 0
+    counts = torch.floor(w / w.sum() * T).long()
+    live = [e for e in range(E) if e not in empty]
+    counts[live[0]] += T - counts.sum()
+    return torch.cat([torch.zeros(1, dtype=torch.long), counts.cumsum(0)]).to(torch.int32)
+
+
+@pytest.mark.parametrize("T,H,I,E,bn,empty", [(300, 64, 64, 4, 128, ()), (1000, 128, 136, 8, 256, (2,)),
+                                              (4096, 768, 512, 4, 256, ()), (517, 256, 72, 32, 128, (0, 31)),
+                                              (129, 64, 64, 4, 128, (1, 2, 3))])
+def test_moe_up_grouped_ragged(T, H, I, E, bn, empty):
+    from complexity_deep_b200 import ops
+    g = torch.Generator().manual_seed(13)
+    x = _rand(g, T, H)
+    gate, up = _rand(g, E, I, H, scale=0.05), _rand(g, E, I, H, scale=0.05)
+    seg = _segments(g, T, E, empty)
+    packed = ops.pack_gate_up(gate.cuda(), up.cuda(), bn)
+    h = ops.moe_up(x.cuda(), seg.cuda(), E, packed, I, bn)
+    _fetch()
+    ref = torch.empty(T, I)
+    for e in range(E):
+        lo, hi = int(seg[e]), int(seg[e + 1])
+        ref[lo:hi] = _swiglu_ref(x[lo:hi], gate[e], up[e])
+    _close(h, ref)
+
+
+@pytest.mark.parametrize("T,H,Ie,Is,E,shared,perm,res", [
+    (300, 64, 64, 64, 4, True, True, True), (1000, 256, 136, 72, 8, True, True, False),
+    (500, 128, 64, 0, 4, False, False, False), (2048, 768, 512, 512, 4, True, True, True),
+    (130, 264, 40, 200, 3, True, True, True)])
+def test_moe_down_combine_unpermute_residual(T, H, Ie, Is, E, shared, perm, res):
+    from complexity_deep_b200 import ops
+    g = torch.Generator().manual_seed(17)
+    hr = _rand(g, T, Ie)
+    wd = _rand(g, E, H, Ie, scale=0.05)
+    hs = _rand(g, T, Is) if shared else None
+    ws = _rand(g, H, Is, scale=0.05) if shared else None
+    seg = _segments(g, T, E, (1,) if E > 3 else ())
+    pm = torch.randperm(T, generator=g).to(torch.int32) if perm else None
+    rs = _rand(g, T, H) if res else None
+    out = ops.moe_down(hr.cuda(), wd.cuda(), hs.cuda() if shared else None,
+                       ws.cuda() if shared else None, seg.cuda(), E,
+                       pm.cuda() if perm else None, rs.cuda() if res else None)
+    _fetch()
+    acc = torch.empty(T, H)
+    for e in range(E):
+        lo, hi = int(seg[e]), int(seg[e + 1])
+        acc[lo:hi] = hr[lo:hi].float() @ wd[e].float().t()
+    if shared:
+        acc += hs.float() @ ws.float().t()
+    ref = torch.empty(T, H)
+    if perm:
+        ref[pm.long()] = acc
+    else:
+        ref = acc
+    if res:
+        ref = ref + rs.float()
+    _close(out, ref)
