@@ -22,6 +22,9 @@ SIGNATURES = {
     "cd_route_workspace_bytes": (c_size_t, [c_int, c_int]),
     "cd_route": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
                          c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "cd_route_static_max_tokens": (c_int, [c_int]),
+    "cd_route_static": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
+                                c_void_p, c_void_p, c_void_p, c_void_p]),
     "cd_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
                            c_int, c_int, c_void_p]),
     "cd_gather_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),

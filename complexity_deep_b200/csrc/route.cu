@@ -13,7 +13,10 @@
 //                       contiguous slice of its block with match/ballot, in row order.
 // Scratch: the block histograms, ceil(T / kTokPerBlock) * E int32.
 #include <cstdint>
+#include <cstdio>
+#include <mutex>
 #include <cuda_runtime.h>
+#include "../../include/cdeep.h"
 #include "kernels.h"
 
 namespace cdeep {
@@ -141,4 +144,74 @@ cudaError_t launch_route(const long long* ids, const long long* table, int V, in
   return cudaGetLastError();
 }
 
+// ---------------------------------------------------------------------------------------
+// Dispatch without any allocation by the caller or the library.
+//
+// Some hosts of this library cannot allocate device memory at the point where they route a
+// batch: a serving loop that runs under a fixed memory budget and must not touch the
+// allocator once it is warm, or a plugin that only receives input and output buffers from
+// its framework and has no handle to an allocator.  For them the block histograms of the
+// dispatch live in a fixed array that is part of the library image; every GPU that loads
+// the library holds these 512 KiB until the process exits.
+namespace {
+
+constexpr int kStaticScratchInts = 131072;  // 512 KiB: ceil(T / 2048) * E must fit
+static __device__ __align__(256) int g_route_scratch[kStaticScratchInts];
+
+constexpr int kStaticMaxDevices = 64;
+int* g_scratch_ptr[kStaticMaxDevices] = {nullptr};
+std::mutex g_scratch_mu;
+
+// In host code `g_route_scratch` is only a handle for the runtime, not a device address;
+// the address on the CURRENT device is looked up once per device and cached.
+cudaError_t static_scratch_for_current_device(int** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= kStaticMaxDevices) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lk(g_scratch_mu);
+  if (!g_scratch_ptr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_route_scratch);
+    if (e != cudaSuccess) return e;
+    g_scratch_ptr[dev] = static_cast<int*>(p);
+  }
+  *out = g_scratch_ptr[dev];
+  return cudaSuccess;
+}
+
+}  // namespace
 }  // namespace cdeep
+
+extern "C" int cd_route_static_max_tokens(int E) {
+  if (E < 1 || E > 256) return 0;
+  const long long blocks = cdeep::kStaticScratchInts / E;
+  const long long t = blocks * cdeep::kTokPerBlock;
+  return t > 0x7fffffffLL ? 0x7fffffff : static_cast<int>(t);
+}
+
+extern "C" int cd_route_static(const int64_t* ids, const int64_t* table, int V, int E, int T,
+                               int32_t* expert_ids, int32_t* counts, int32_t* offsets,
+                               int32_t* perm, int32_t* inv_perm, void* stream) {
+  using namespace cdeep;
+  if (T < 0 || V < 1 || E < 1 || E > 256) return CD_ERR_INVALID;
+  if (!table || !counts || !offsets) return CD_ERR_INVALID;
+  if (T > 0 && (!ids || !expert_ids || !perm || !inv_perm)) return CD_ERR_INVALID;
+  const long long blocks = (static_cast<long long>(T) + kTokPerBlock - 1) / kTokPerBlock;
+  if ((blocks > 0 ? blocks : 1) * E > kStaticScratchInts) {
+    snprintf(g_cuda_err, sizeof(g_cuda_err),
+             "cd_route_static: T=%d with E=%d needs %lld scratch ints, the built-in array holds %d "
+             "(use cd_route with caller-provided scratch)",
+             T, E, (blocks > 0 ? blocks : 1) * E, kStaticScratchInts);
+    return CD_ERR_UNSUPPORTED;
+  }
+  int* scratch = nullptr;
+  cudaError_t e = static_scratch_for_current_device(&scratch);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(route scratch)");
+  // Every histogram slot that route_rank reads is written by route_lookup_hist in this same
+  // call, so nothing left over from an earlier call has to be cleared.
+  e = launch_route(reinterpret_cast<const long long*>(ids),
+                   reinterpret_cast<const long long*>(table), V, E, T, expert_ids, counts,
+                   offsets, perm, inv_perm, scratch, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? CD_OK : cuda_fail(e, "route launch");
+}

@@ -59,6 +59,26 @@ int cd_route(const int64_t* ids, const int64_t* table, int V, int E, int T, int3
              int32_t* counts, int32_t* offsets, int32_t* perm, int32_t* inv_perm, void* ws,
              size_t ws_bytes, void* stream);
 
+/* ---- dispatch for callers that cannot allocate ---------------------------------------------
+ * (No counterpart in the reference.)  Same computation and outputs as cd_route, but the
+ * scratch is a fixed 512 KiB array inside the library instead of a caller buffer, and the
+ * call allocates nothing — no cudaMalloc/cudaFree, no allocating library routine.  Meant for
+ * hosts that must not touch a device allocator where they route a batch: a serving loop
+ * pinned to a fixed memory budget, or a framework plugin that is handed only input and
+ * output buffers.
+ *   - Limit: ceil(T / 2048) * E <= 131072; cd_route_static_max_tokens(E) gives the largest T.
+ *     Larger requests return CD_ERR_UNSUPPORTED (text in cd_last_cuda_error) — use cd_route.
+ *   - The first call on each device looks up the array's device address (with that device
+ *     current); make that first call before starting any stream capture.
+ *   - All calls on a device share the one array.  It keeps the previous call's contents, which
+ *     is harmless (each call overwrites every slot it later reads), but two calls whose
+ *     kernels overlap on the GPU (different streams, no ordering) race on it: order them.
+ *   - Every GPU that loads the library holds the array until the process exits. */
+int cd_route_static_max_tokens(int E);
+int cd_route_static(const int64_t* ids, const int64_t* table, int V, int E, int T,
+                    int32_t* expert_ids, int32_t* counts, int32_t* offsets, int32_t* perm,
+                    int32_t* inv_perm, void* stream);
+
 /* ---- RMSNorm ---------------------------------------------------------------------------
  * Replaces RMSNorm.forward, complexity_deep/core/normalization.py:29-32, optionally fused
  * with the residual add in front of it (complexity_deep/core/layer.py:174) and with the
