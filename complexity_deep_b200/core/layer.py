@@ -25,6 +25,27 @@ from .normalization import RMSNorm
 from .token_routed_mlp import TokenRoutedMLP
 
 
+class MuClampRequest:
+    """Set by ComplexityModel.forward around its layer loop: asks each block to apply the
+    model's clamp of mu (complexity_deep/models/modeling.py:199-200) in the mu_proj GEMM's
+    epilogue instead of a separate elementwise pass.  A block honours it only when nobody
+    hooks the block or its mu_guidance (their hooks must see the unclamped value), and
+    reports back through `applied`."""
+    current = None
+
+    def __init__(self, lo: float, hi: float) -> None:
+        self.range = (lo, hi)
+        self.applied = False
+
+    def __enter__(self):
+        self.previous, MuClampRequest.current = MuClampRequest.current, self
+        return self
+
+    def __exit__(self, *exc):
+        MuClampRequest.current = self.previous
+        return False
+
+
 def _has_hooks(m: nn.Module) -> bool:
     return bool(m._forward_hooks or m._forward_pre_hooks or m._backward_hooks
                 or getattr(m, "_forward_hooks_with_kwargs", None)
@@ -127,7 +148,18 @@ class TransformerBlock(nn.Module):
                 hidden_states = self.mlp(hidden_states)
             hidden_states = residual + hidden_states
 
-        mu_contextual = self.mu_guidance(hidden_states) if self.mu_guidance is not None else None
+        mu_contextual = None
+        if self.mu_guidance is not None:
+            req = MuClampRequest.current
+            if req is not None and not _has_hooks(self) and not _has_hooks(self.mu_guidance):
+                mg = self.mu_guidance
+                shape = hidden_states.shape
+                mu_contextual = ops.mu_proj(
+                    hidden_states.reshape(-1, shape[-1]).contiguous(), mg.mu_proj.weight, mg.mu,
+                    mg.mu_min, mg.mu_max, out_clamp=req.range).view(shape)
+                req.applied = True
+            else:
+                mu_contextual = self.mu_guidance(hidden_states)
         return hidden_states, new_kv, mu_contextual
 
     def _forward_fused(self, hidden_states, attention_mask, past_key_value, use_cache, token_ids,

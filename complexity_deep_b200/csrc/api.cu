@@ -58,7 +58,7 @@ size_t cd_route_workspace_bytes(int T, int E) {
 int cd_route(const int64_t* ids, const int64_t* table, int V, int E, int T, int32_t* expert_ids,
              int32_t* counts, int32_t* offsets, int32_t* perm, int32_t* inv_perm, void* ws,
              size_t ws_bytes, void* stream) {
-  if (T < 0 || V < 1 || E < 1 || E > kMaxGroups) return CD_ERR_INVALID;
+  if (T < 0 || V < 1 || E < 1 || E > 256) return CD_ERR_INVALID;
   if (!table || !counts || !offsets || !ws) return CD_ERR_INVALID;
   if (T > 0 && (!ids || !expert_ids || !perm || !inv_perm)) return CD_ERR_INVALID;
   if (ws_bytes < route_workspace_bytes(T, E)) return CD_ERR_INVALID;

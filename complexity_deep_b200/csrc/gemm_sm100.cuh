@@ -31,7 +31,9 @@ namespace cdeep {
 constexpr int kBlockM = 128;       // rows per tile = TMEM lanes
 constexpr int kBlockK = 64;        // bf16 elements per k-block = one 128-byte swizzle row
 constexpr int kUmmaK = 16;         // K of one tcgen05.mma for 16-bit inputs
-constexpr int kMaxGroups = 256;
+constexpr int kMaxGroups = 128;
+constexpr int kEpiCols = 64;          // output columns per epilogue sub-tile (128 bytes of bf16)
+constexpr int kEpiStageBytes = 4096;  // 32 rows x 128 bytes, per warp and buffer
 constexpr int kGemmThreads = 192;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
 
 enum GemmEpilogue : int {
@@ -69,8 +71,10 @@ struct GemmSmem {
   static constexpr int kBBytes = BN * kBlockK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTileBytes = kStages * kStageBytes;
-  // after the tiles: barriers, TMEM base, abort flag, schedule tables
-  static constexpr int kBarOff = kTileBytes;
+  // after the tiles: epilogue staging (4 warps x 2 buffers), barriers, TMEM base, abort
+  // flag, schedule tables
+  static constexpr int kEpiOff = kTileBytes;
+  static constexpr int kBarOff = kEpiOff + 4 * 2 * kEpiStageBytes;
   static constexpr int kNumBars = 2 * kStages + 4;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
   static constexpr int kPrefixOff = kMiscOff + 16;
@@ -109,6 +113,17 @@ __device__ __forceinline__ TileCoord decode_tile(int t, int& gcur, const int* pr
   c.n0 = n_idx * bn;
   c.row_end = hi;
   return c;
+}
+
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+__device__ __forceinline__ uint4 ld_nc_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
 }
 
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + __expf(-g)); }
@@ -271,7 +286,18 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
     __syncwarp();
   } else {
     // ------------------------------------------------------------ epilogue (4 warps)
+    // A thread owns one accumulator row (TMEM lane), but rows are 32 different cache lines:
+    // results are therefore staged through a per-warp shared-memory buffer (32 rows x 64
+    // bf16 columns = 4 KB, 16-byte chunks XOR-swizzled by row so both access patterns are
+    // conflict-free) and leave in a coalesced pattern: 8 lanes cover the 128 bytes of one
+    // row, a warp instruction covers 4 rows.  The residual enters the same way, fetched with
+    // cp.async one and two sub-tiles ahead — the first two before the accumulator is even
+    // complete — so its latency stays off the critical path.
     const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+    uint8_t* stage0 = smem + L::kEpiOff + (warp - 2) * (2 * kEpiStageBytes);
+    const int crow_l = lane >> 3;   // row within a group of 4 rows (coalesced phase)
+    const int cchunk = lane & 7;    // 16-byte chunk within the 128-byte row
+    const uint32_t own_off = static_cast<uint32_t>(lane) * 128u;  // this lane's row (owner phase)
     uint32_t tcount = 0;
     int gcur = 0;
     bool ok = true;
@@ -279,98 +305,148 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
       const TileCoord c = decode_tile(t, gcur, prefix, seg, n_tiles, p.band, BN);
       const uint32_t acc = tcount & 1u;
       const uint32_t acc_ph = (tcount >> 1) & 1u;
+      const int r = c.m0 + quarter * 32 + lane;
+      const bool row_ok = r < c.row_end;
+      int orow = 0;
+      if constexpr (EPI == kEpiStore) {
+        orow = row_ok ? (p.row_map ? p.row_map[r] : r) : 0;
+      } else {
+        orow = row_ok ? r : 0;
+      }
+      // destination rows in the coalesced mapping: it * 4 + lane / 8
+      int crow[8];
+      uint32_t cvalid = 0;
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        crow[it] = __shfl_sync(0xffffffffu, orow, it * 4 + crow_l);
+        cvalid |= (__shfl_sync(0xffffffffu, row_ok ? 1 : 0, it * 4 + crow_l) ? 1u : 0u) << it;
+      }
+      // output columns of this tile and the number of 64-column sub-tiles
+      const int ocol_base = (EPI == kEpiStore) ? c.n0 : c.n0 / 2;
+      const int ocol_span = (EPI == kEpiStore) ? BN : BN / 2;
+      const int ocols = min(ocol_span, p.out_cols - ocol_base);
+      const int nsub = (ocols + kEpiCols - 1) / kEpiCols;
+      const bool has_res = (EPI == kEpiStore) && p.residual != nullptr;
+
+      auto fetch_residual = [&](int sub) {
+        uint8_t* buf = stage0 + (sub & 1) * kEpiStageBytes;
+        const int col = ocol_base + sub * kEpiCols + cchunk * 8;
+        if (col < p.out_cols) {
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            if ((cvalid >> it) & 1u) {
+              const int rr = it * 4 + crow_l;
+              cp_async_16(buf + rr * 128 + ((cchunk ^ (rr & 7)) << 4),
+                          p.residual + static_cast<long long>(crow[it]) * p.ldr + col);
+            }
+          }
+        }
+        cp_async_commit();
+      };
+      if (has_res) {
+        fetch_residual(0);
+        if (nsub > 1) fetch_residual(1);
+      }
+
       if (!mbar_wait(&tmem_full[acc], acc_ph, abort_flag)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      const int r = c.m0 + quarter * 32 + lane;
-      const bool row_ok = r < c.row_end;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
 
-      if constexpr (EPI == kEpiStore) {
-        const long long orow = row_ok ? (p.row_map ? p.row_map[r] : r) : 0;
-        __nv_bfloat16* out_row = p.out + orow * p.ldo;
-        const __nv_bfloat16* res_row = p.residual ? p.residual + orow * p.ldr : nullptr;
 #pragma unroll 1
-        for (int ch = 0; ch < BN / 32; ++ch) {
-          const int col0 = c.n0 + ch * 32;
-          if (col0 >= p.N) break;  // uniform across the warp
-          uint32_t v[32];
-          tmem_ld32(t_row + ch * 32, v);
+      for (int sub = 0; sub < nsub; ++sub) {
+        uint8_t* buf = stage0 + (sub & 1) * kEpiStageBytes;
+        const int col0 = ocol_base + sub * kEpiCols;
+        if constexpr (EPI == kEpiStore) {
+          uint32_t v[64];
+          tmem_ld32(t_row + sub * 64, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+          tmem_ld32(t_row + sub * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+          if (has_res) {
+            if (sub + 1 < nsub) cp_async_wait<1>(); else cp_async_wait<0>();
+            __syncwarp();
+          }
           tmem_ld_wait();
-          if (row_ok) {
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const int col = col0 + q * 8;
+            float f[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[q * 8 + j]);
+            uint8_t* slot = buf + own_off + ((q ^ (lane & 7)) << 4);
+            if (col < p.out_cols) {
+              if (p.bias) {
+                const uint4 b = *reinterpret_cast<const uint4*>(p.bias + col);
+                const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  f[2 * j] += fminf(fmaxf(bf16_lo(bw[j]), p.bias_lo), p.bias_hi);
+                  f[2 * j + 1] += fminf(fmaxf(bf16_hi(bw[j]), p.bias_lo), p.bias_hi);
+                }
+              }
+              if (has_res && row_ok) {
+                const uint4 rr = *reinterpret_cast<const uint4*>(slot);
+                const uint32_t rw[4] = {rr.x, rr.y, rr.z, rr.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  f[2 * j] += bf16_lo(rw[j]);
+                  f[2 * j + 1] += bf16_hi(rw[j]);
+                }
+              }
+              if (p.do_clamp) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] = fminf(fmaxf(f[j], p.clamp_lo), p.clamp_hi);
+              }
+            }
+            uint4 o;
+            o.x = pack_bf16x2(f[0], f[1]);
+            o.y = pack_bf16x2(f[2], f[3]);
+            o.z = pack_bf16x2(f[4], f[5]);
+            o.w = pack_bf16x2(f[6], f[7]);
+            *reinterpret_cast<uint4*>(slot) = o;
+          }
+        } else {
+          // SwiGLU: accumulator columns [0, BN/2) hold gate, [BN/2, BN) hold up, for output
+          // columns (n0 / 2) .. (n0 / 2) + BN / 2; 32 output columns per TMEM round trip.
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            uint32_t g[32], u[32];
+            tmem_ld32(t_row + sub * 64 + half * 32, g);
+            tmem_ld32(t_row + BN / 2 + sub * 64 + half * 32, u);
+            tmem_ld_wait();
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-              const int col = col0 + q * 8;
-              if (col < p.out_cols) {
-                float f[8];
+              float h[8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[q * 8 + j]);
-                if (p.bias) {
-                  const uint4 b = *reinterpret_cast<const uint4*>(p.bias + col);
-                  const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+              for (int j = 0; j < 8; ++j)
+                h[j] = silu_f(__uint_as_float(g[q * 8 + j])) * __uint_as_float(u[q * 8 + j]);
+              uint4 o;
+              o.x = pack_bf16x2(h[0], h[1]);
+              o.y = pack_bf16x2(h[2], h[3]);
+              o.z = pack_bf16x2(h[4], h[5]);
+              o.w = pack_bf16x2(h[6], h[7]);
+              *reinterpret_cast<uint4*>(buf + own_off + (((half * 4 + q) ^ (lane & 7)) << 4)) = o;
+            }
+          }
+        }
+        __syncwarp();
+        // coalesced copy-out: 4 rows x 128 bytes per warp instruction
+        {
+          const int col = col0 + cchunk * 8;
+          if (col < p.out_cols) {
 #pragma unroll
-                  for (int j = 0; j < 4; ++j) {
-                    f[2 * j] += fminf(fmaxf(bf16_lo(bw[j]), p.bias_lo), p.bias_hi);
-                    f[2 * j + 1] += fminf(fmaxf(bf16_hi(bw[j]), p.bias_lo), p.bias_hi);
-                  }
-                }
-                if (res_row) {
-                  const uint4 rr = *reinterpret_cast<const uint4*>(res_row + col);
-                  const uint32_t rw[4] = {rr.x, rr.y, rr.z, rr.w};
-#pragma unroll
-                  for (int j = 0; j < 4; ++j) {
-                    f[2 * j] += bf16_lo(rw[j]);
-                    f[2 * j + 1] += bf16_hi(rw[j]);
-                  }
-                }
-                if (p.do_clamp) {
-#pragma unroll
-                  for (int j = 0; j < 8; ++j) f[j] = fminf(fmaxf(f[j], p.clamp_lo), p.clamp_hi);
-                }
-                uint4 o;
-                o.x = pack_bf16x2(f[0], f[1]);
-                o.y = pack_bf16x2(f[2], f[3]);
-                o.z = pack_bf16x2(f[4], f[5]);
-                o.w = pack_bf16x2(f[6], f[7]);
-                *reinterpret_cast<uint4*>(out_row + col) = o;
+            for (int it = 0; it < 8; ++it) {
+              if ((cvalid >> it) & 1u) {
+                const int rr = it * 4 + crow_l;
+                const uint4 o = *reinterpret_cast<const uint4*>(buf + rr * 128 + ((cchunk ^ (rr & 7)) << 4));
+                *reinterpret_cast<uint4*>(p.out + static_cast<long long>(crow[it]) * p.ldo + col) = o;
               }
             }
           }
         }
-      } else {
-        // SwiGLU: accumulator columns [0, BN/2) hold gate, [BN/2, BN) hold up, for output
-        // columns (n0 / 2) .. (n0 / 2) + BN / 2.
-        __nv_bfloat16* out_row = p.out + static_cast<long long>(row_ok ? r : 0) * p.ldo;
-        const int ocol_base = c.n0 / 2;
-#pragma unroll 1
-        for (int ch = 0; ch < BN / 64; ++ch) {
-          const int ocol0 = ocol_base + ch * 32;
-          if (ocol0 >= p.out_cols) break;  // uniform across the warp
-          uint32_t g[32], u[32];
-          tmem_ld32(t_row + ch * 32, g);
-          tmem_ld32(t_row + BN / 2 + ch * 32, u);
-          tmem_ld_wait();
-          if (row_ok) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const int col = ocol0 + q * 8;
-              if (col < p.out_cols) {
-                float h[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                  h[j] = silu_f(__uint_as_float(g[q * 8 + j])) * __uint_as_float(u[q * 8 + j]);
-                uint4 o;
-                o.x = pack_bf16x2(h[0], h[1]);
-                o.y = pack_bf16x2(h[2], h[3]);
-                o.z = pack_bf16x2(h[4], h[5]);
-                o.w = pack_bf16x2(h[6], h[7]);
-                *reinterpret_cast<uint4*>(out_row + col) = o;
-              }
-            }
-          }
-        }
+        __syncwarp();  // the buffer may be refilled from here on
+        if (has_res && sub + 2 < nsub) fetch_residual(sub + 2);
       }
       // this warp is done reading the accumulator
       tc_fence_before();

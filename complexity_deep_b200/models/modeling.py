@@ -20,7 +20,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .. import ops
-from ..core.layer import TransformerBlock
+from ..core.layer import MuClampRequest, TransformerBlock
 from ..core.normalization import RMSNorm
 from .config import ComplexityConfig
 
@@ -115,14 +115,17 @@ class ComplexityModel(nn.Module):
         mu_prev = self.mu_init.expand(B, S, -1) if self.config.use_mu_guidance else None
         new_kvs: Optional[KVCache] = [] if use_cache else None
 
-        for i, layer in enumerate(self.layers):
-            past = past_key_values[i] if past_key_values is not None else None
-            hidden, new_kv, mu = layer(hidden, attention_mask=attention_mask, past_key_value=past,
-                                       use_cache=use_cache, token_ids=input_ids, mu_prev=mu_prev)
-            if mu is not None:
-                mu_prev = torch.clamp(mu, -2.0, 2.0)
-            if use_cache:
-                new_kvs.append(new_kv)
+        with MuClampRequest(-2.0, 2.0) as clamp:
+            for i, layer in enumerate(self.layers):
+                past = past_key_values[i] if past_key_values is not None else None
+                clamp.applied = False
+                hidden, new_kv, mu = layer(hidden, attention_mask=attention_mask,
+                                           past_key_value=past, use_cache=use_cache,
+                                           token_ids=input_ids, mu_prev=mu_prev)
+                if mu is not None:  # clamp fused into the block's mu_proj epilogue when allowed
+                    mu_prev = mu if clamp.applied else torch.clamp(mu, -2.0, 2.0)
+                if use_cache:
+                    new_kvs.append(new_kv)
 
         normed = ops.rmsnorm(hidden.reshape(B * S, H).contiguous(), self.norm.weight, self.norm.eps)
         logits = ops.linear(normed, self.lm_head.weight, tag="linear_lm_head").view(B, S, -1)

@@ -69,7 +69,8 @@ def test_gather_rows_bit_exact():
 
 @pytest.mark.parametrize("hq,hkv,D,S,pos0,norm", [(4, 2, 64, 12, 0, True), (16, 8, 128, 40, 0, True),
                                                   (4, 2, 64, 1, 12, True), (12, 4, 64, 9, 5, False),
-                                                  (2, 1, 32, 7, 3, True)])
+                                                  (2, 1, 32, 7, 3, True), (2, 1, 24, 5, 0, True),
+                                                  (2, 2, 256, 3, 1, True)])
 def test_qk_norm_rope(hq, hkv, D, S, pos0, norm):
     from complexity_deep_b200 import ops
     g = torch.Generator().manual_seed(3)

@@ -130,7 +130,8 @@ def test_pack_gate_up_layout():
     assert packed2.shape == (1, 512, 8)
     assert torch.equal(packed2[0, 256:256 + 72], gate2[0, 128:])
     assert torch.equal(packed2[0, 384:384 + 72], 2 * gate2[0, 128:])
-    assert ops.choose_block_n(5632) == 256 and ops.choose_block_n(704) == 128
+    assert ops.choose_block_n(5632) == 256 and ops.choose_block_n(704) == 256
+    assert ops.choose_block_n(64) == 128 and ops.choose_block_n(48) == 128
     assert ops.choose_block_n(2816) == 256 and ops.choose_block_n(512) == 256
 
 
