@@ -42,6 +42,14 @@ def shard_batch(global_batch: int, world: int, rank: int):
     return lo, lo + base + (1 if rank < extra else 0)
 
 
+def aggregate_ms(local_ms: float, dist=None, device=None) -> float:
+    """Step time of the whole job: the MAX over ranks of the device-measured time."""
+    t = torch.tensor([local_ms], dtype=torch.float64, device=device)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
 def flops_per_token(cfg: dict, seq_len: int) -> dict:
     """Algorithmic FLOPs per token of each GEMM entry point (per layer unless noted)."""
     H, V, L = cfg["hidden_size"], cfg["vocab_size"], cfg["num_hidden_layers"]
@@ -181,13 +189,11 @@ def run_ours(args):
             step_fn(i)
         t1.record()
         barrier()
-        ms = torch.tensor([t0.elapsed_time(t1)], device=dev)
-        if dist is not None:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        ms = aggregate_ms(t0.elapsed_time(t1), dist, dev)
         clocks = sampler.stop()
         prof = ops.PROFILE.collect()
         ops.PROFILE.reset(enabled=False)
-        return float(ms.item()), clocks, prof
+        return ms, clocks, prof
 
     ms_dev, clocks, prof = timed(step_device, instrument=True)
     ms_e2e, clocks_e2e, _ = timed(step_e2e, instrument=False)
