@@ -35,6 +35,8 @@ SIGNATURES = {
                           c_int, c_void_p]),
     "cd_moe_down": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
                             c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "cd_moe_combine": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                               c_int, c_int, c_void_p]),
     "cd_mu_qkv": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                           c_void_p]),
     "cd_mu_proj": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_float, c_int, c_float, c_float,

@@ -165,6 +165,31 @@ int cd_moe_down(const void* h_routed, int I_e, const void* wd_routed, const void
                      H > 128 ? 256 : 128, as_stream(stream));
 }
 
+int cd_moe_combine(const void* h_shared, int I_s, const void* wd_shared, const void* routed_sorted,
+                   const int32_t* row_map, const void* residual, void* out, int T, int H,
+                   void* stream) {
+  if (T < 0 || H < 8 || (H & 7) || I_s < 8 || (I_s & 7)) return CD_ERR_INVALID;
+  if (!h_shared || !wd_shared) return CD_ERR_INVALID;
+  GemmOperand op0{};
+  op0.a = h_shared;
+  op0.lda = I_s;
+  op0.b = wd_shared;
+  op0.ldb = I_s;
+  op0.b_rows = H;
+  op0.K = I_s;
+  GemmEpilogueArgs epi{};
+  epi.kind = kEpiStore;
+  epi.out = out;
+  epi.ldo = H;
+  epi.out_cols = H;
+  epi.row_map = row_map;
+  epi.residual = residual;
+  epi.ldr = H;
+  epi.residual2 = routed_sorted;
+  epi.ldr2 = H;
+  return launch_gemm(T, H, 1, nullptr, op0, nullptr, epi, H > 128 ? 256 : 128, as_stream(stream));
+}
+
 int cd_mu_qkv(const void* x, const void* mu_prev, const void* w, const void* w_mu, void* qkv,
               int T, int H, int N, void* stream) {
   if (T < 0 || H < 8 || (H & 7) || N < 8 || (N & 7)) return CD_ERR_INVALID;

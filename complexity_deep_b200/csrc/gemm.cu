@@ -126,7 +126,8 @@ int launch_gemm(int M, int N, int num_groups, const int* seg_offsets, const Gemm
     return CD_ERR_INVALID;
   auto aligned16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
   if (!op0.a || !op0.b || !epi.out || !aligned16(op0.a) || !aligned16(op0.b) ||
-      !aligned16(epi.out) || !aligned16(epi.residual) || !aligned16(epi.bias))
+      !aligned16(epi.out) || !aligned16(epi.residual) || !aligned16(epi.residual2) ||
+      !aligned16(epi.bias) || (epi.residual2 && (epi.ldr2 & 7)))
     return CD_ERR_INVALID;
   if (op1 && (!op1->a || !op1->b || !aligned16(op1->a) || !aligned16(op1->b)))
     return CD_ERR_INVALID;
@@ -170,6 +171,8 @@ int launch_gemm(int M, int N, int num_groups, const int* seg_offsets, const Gemm
   p.row_map = epi.row_map;
   p.residual = static_cast<const __nv_bfloat16*>(epi.residual);
   p.ldr = epi.ldr;
+  p.residual2 = static_cast<const __nv_bfloat16*>(epi.residual2);
+  p.ldr2 = epi.ldr2;
   p.bias = static_cast<const __nv_bfloat16*>(epi.bias);
   p.bias_lo = epi.bias_lo;
   p.bias_hi = epi.bias_hi;

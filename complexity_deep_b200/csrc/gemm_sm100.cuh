@@ -57,6 +57,8 @@ struct GemmParams {
   const int* row_map;      // sorted row -> destination row (nullptr = identity)
   const __nv_bfloat16* residual;  // indexed like out (nullptr = none)
   int ldr;
+  const __nv_bfloat16* residual2;  // second addend, indexed by the tile row itself (nullptr = none)
+  int ldr2;
   const __nv_bfloat16* bias;      // per output column, clamped to [bias_lo, bias_hi] (nullptr = none)
   float bias_lo, bias_hi;
   int do_clamp;            // clamp the result to [clamp_lo, clamp_hi]
@@ -347,6 +349,14 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
         fetch_residual(0);
         if (nsub > 1) fetch_residual(1);
       }
+      const __nv_bfloat16* res2_row = nullptr;
+      if constexpr (EPI == kEpiStore) {
+        if (p.residual2 && row_ok) {
+          // read lane-per-row (uncoalesced): pull the row's bytes into L2 ahead of time
+          res2_row = p.residual2 + static_cast<long long>(r) * p.ldr2;
+          for (int cc = 0; cc < ocols; cc += 64) prefetch_l2(res2_row + ocol_base + cc);
+        }
+      }
 
       if (!mbar_wait(&tmem_full[acc], acc_ph, abort_flag)) {
         ok = false;
@@ -360,6 +370,12 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
         uint8_t* buf = stage0 + (sub & 1) * kEpiStageBytes;
         const int col0 = ocol_base + sub * kEpiCols;
         if constexpr (EPI == kEpiStore) {
+          uint4 r2[8];
+          if (res2_row) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              if (col0 + q * 8 < p.out_cols) r2[q] = ld_nc_v4(res2_row + col0 + q * 8);
+          }
           uint32_t v[64];
           tmem_ld32(t_row + sub * 64, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
           tmem_ld32(t_row + sub * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
@@ -388,6 +404,14 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
               if (has_res && row_ok) {
                 const uint4 rr = *reinterpret_cast<const uint4*>(slot);
                 const uint32_t rw[4] = {rr.x, rr.y, rr.z, rr.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  f[2 * j] += bf16_lo(rw[j]);
+                  f[2 * j + 1] += bf16_hi(rw[j]);
+                }
+              }
+              if (res2_row) {
+                const uint32_t rw[4] = {r2[q].x, r2[q].y, r2[q].z, r2[q].w};
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                   f[2 * j] += bf16_lo(rw[j]);

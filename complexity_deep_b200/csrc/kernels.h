@@ -38,6 +38,8 @@ struct GemmEpilogueArgs {
   const int* row_map;
   const void* residual;
   int ldr;
+  const void* residual2;   // indexed by the un-mapped row
+  int ldr2;
   const void* bias;
   float bias_lo, bias_hi;
   int do_clamp;

@@ -289,6 +289,35 @@ def moe_down(h_routed: torch.Tensor, wd_routed: torch.Tensor, h_shared: Optional
     return out
 
 
+def moe_combine(h_shared: torch.Tensor, wd_shared: torch.Tensor,
+                routed_sorted: Optional[torch.Tensor], row_map: Optional[torch.Tensor],
+                residual: Optional[torch.Tensor]) -> torch.Tensor:
+    """Shared down projection + routed part (sorted order, from the expert GPUs) + residual."""
+    lib = _lib.load()
+    _need(h_shared, "h_shared")
+    _need(wd_shared, "shared down weight")
+    T, I_s = h_shared.shape
+    H = wd_shared.shape[0]
+    if wd_shared.shape[1] != I_s:
+        raise RuntimeError("shared down weight does not match h_shared")
+    if routed_sorted is not None:
+        _need(routed_sorted, "routed_sorted")
+        if tuple(routed_sorted.shape) != (T, H):
+            raise RuntimeError("routed_sorted does not match")
+    if row_map is not None:
+        _need(row_map, "row_map", torch.int32)
+    res2 = None
+    if residual is not None:
+        res2 = residual.reshape(-1, H)
+        _need(res2, "residual")
+    out = torch.empty(T, H, dtype=BF16, device=h_shared.device)
+    with _Span("moe_combine"):
+        _lib.check(lib.cd_moe_combine(h_shared.data_ptr(), I_s, wd_shared.data_ptr(),
+                                      _ptr(routed_sorted), _ptr(row_map), _ptr(res2),
+                                      out.data_ptr(), T, H, _stream()), "cd_moe_combine")
+    return out
+
+
 def mu_qkv(x: torch.Tensor, mu_prev: Optional[torch.Tensor], w: torch.Tensor,
            w_mu: Optional[torch.Tensor]) -> torch.Tensor:
     lib = _lib.load()

@@ -132,6 +132,18 @@ int cd_moe_down(const void* h_routed, int I_e, const void* wd_routed, const void
                 const int32_t* row_map, const void* residual, void* out, int T, int H,
                 void* stream);
 
+/* ---- expert-parallel combine ---------------------------------------------------------------
+ * Home-GPU half of the layer when the routed experts live on other GPUs: the shared expert's
+ * down projection (token_routed_mlp.py:157-160) plus `routed_out + shared_out` (:177) and the
+ * block's residual add (complexity_deep/core/layer.py:183), where the routed part arrives
+ * from the expert GPUs (already down-projected there with cd_moe_down, h_shared = NULL):
+ *   out[row_map[r], :] = h_shared[r] @ Sd^T + routed_sorted[r, :] + residual[row_map[r], :]
+ * h_shared [T, I_s] and routed_sorted [T, H] in sorted order (routed_sorted may be NULL);
+ * row_map / residual as in cd_moe_down. */
+int cd_moe_combine(const void* h_shared, int I_s, const void* wd_shared, const void* routed_sorted,
+                   const int32_t* row_map, const void* residual, void* out, int T, int H,
+                   void* stream);
+
 /* ---- mu-guided QKV -------------------------------------------------------------------------
  * Replaces complexity_deep/core/attention.py:120-131: torch.cat([x, mu_prev]) against the
  * re-concatenated weights, three F.linear calls.  One GEMM whose K loop walks x then

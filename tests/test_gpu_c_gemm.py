@@ -173,3 +173,29 @@ def test_moe_down_combine_unpermute_residual(T, H, Ie, Is, E, shared, perm, res)
     if res:
         ref = ref + rs.float()
     _close(out, ref)
+
+
+@pytest.mark.parametrize("T,H,Is,perm,res,routed", [(300, 64, 64, True, True, True),
+                                                    (1000, 256, 200, True, False, True),
+                                                    (513, 768, 512, False, True, False)])
+def test_moe_combine_shared_plus_routed_partial(T, H, Is, perm, res, routed):
+    from complexity_deep_b200 import ops
+    g = torch.Generator().manual_seed(19)
+    hs, ws = _rand(g, T, Is), _rand(g, H, Is, scale=0.05)
+    yr = _rand(g, T, H) if routed else None
+    pm = torch.randperm(T, generator=g).to(torch.int32) if perm else None
+    rs = _rand(g, T, H) if res else None
+    out = ops.moe_combine(hs.cuda(), ws.cuda(), yr.cuda() if routed else None,
+                          pm.cuda() if perm else None, rs.cuda() if res else None)
+    _fetch()
+    acc = hs.float() @ ws.float().t()
+    if routed:
+        acc = acc + yr.float()
+    ref = torch.empty(T, H)
+    if perm:
+        ref[pm.long()] = acc
+    else:
+        ref = acc
+    if res:
+        ref = ref + rs.float()
+    _close(out, ref)

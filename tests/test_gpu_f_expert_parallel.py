@@ -1,0 +1,79 @@
+"""Expert-parallel MoE layer on 2 GPUs (one process per GPU, NCCL all-to-all) vs the oracle
+of the UNSHARDED layer on each rank's own tokens.  Tolerance as for the single-GPU layer:
+max|y - ref| / max|ref| <= 2e-2, mean|y - ref| <= 2e-3 * max(1, rms(ref)).  Skipped when the
+box has a single GPU; the exchange arithmetic itself is covered on CPU ranks."""
+import os
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from conftest import ROOT
+
+pytestmark = pytest.mark.gpu
+BF = torch.bfloat16
+
+
+def _rank_main(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank),
+                      WORLD_SIZE=str(world))
+    sys.path.insert(0, ROOT)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world,
+                            device_id=torch.device("cuda", rank))
+    try:
+        import complexity_deep_b200 as cd
+        from complexity_deep_b200 import ops
+        from complexity_deep_b200.expert_parallel import ExpertParallelMoE
+        from oracle import complexity_oracle as oracle
+        H, E, I_e, V, T = 256, 8, 136, 1000, 900 + 77 * rank
+        g = torch.Generator().manual_seed(0)                      # same weights on every rank
+        table = torch.from_numpy(oracle.build_token_mapping(
+            V, E, oracle.zipf_probabilities(V, 1.0).float()))
+        mlp = cd.TokenRoutedMLP(H, I_e * E, E, V, True, None)
+        sd = {}
+        with torch.no_grad():
+            for name, prm in mlp.named_parameters():
+                w = (torch.randn(prm.shape, generator=g) * 0.05).to(BF)
+                prm.copy_(w)
+                sd[name] = w.float()
+            mlp.token_to_expert.copy_(table)
+        sd["token_to_expert"] = table
+        mlp = mlp.to(device="cuda", dtype=BF).eval()
+        ep = ExpertParallelMoE(mlp)
+        gi = torch.Generator().manual_seed(100 + rank)            # different tokens per rank
+        x = torch.randn(1, T, H, generator=gi).to(BF)
+        ids = oracle.zipf_token_ids(V, 1.0, T, seed=100 + rank).view(1, T)
+        res = torch.randn(T, H, generator=gi).to(BF)
+        y = ep(x.cuda(), ids.cuda())
+        routing = mlp.routing(ids.cuda())
+        xs = ops.gather_rows(x.cuda().view(T, H), routing.perm)
+        y_res = ep.forward_sorted(xs, routing, res.cuda())
+        y_local = mlp(x.cuda(), ids.cuda())                       # unsharded kernels, same rank
+        ops.status_fetch()
+        ref = oracle.token_routed_mlp(sd, "", x.float(), ids)
+        m1 = oracle.error_metrics(y.float().cpu(), ref)
+        m2 = oracle.error_metrics(y_res.float().cpu(), ref[0] + res.float())
+        m3 = oracle.error_metrics(y.float().cpu(), y_local.float().cpu())
+        rms = float(ref.pow(2).mean().sqrt())
+        out[rank] = (m1, m2, m3, rms, int(ep.plan_for(routing)[0].received))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_expert_parallel_layer_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_rank_main, args=(2, 29655, out), nprocs=2, join=True)
+    total = 0
+    for rank in range(2):
+        (mr1, ma1), (mr2, ma2), (mr3, ma3), rms, received = out[rank]
+        assert mr1 <= 2e-2 and ma1 <= 2e-3 * max(1.0, rms), (rank, mr1, ma1, rms)
+        assert mr2 <= 2e-2 and ma2 <= 2e-3 * max(1.0, rms), (rank, mr2, ma2, rms)
+        assert mr3 <= 2e-2                                        # sharded vs unsharded kernels
+        total += received
+    assert total == 900 + 977                                     # every row visited one expert

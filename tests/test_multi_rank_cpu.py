@@ -50,3 +50,59 @@ def test_shard_batch_uneven():
     parts = [bench.shard_batch(10, 4, r) for r in range(4)]
     assert parts == [(0, 3), (3, 6), (6, 8), (8, 10)]
     assert [bench.shard_batch(32, 8, r) for r in range(8)] == [(4 * r, 4 * r + 4) for r in range(8)]
+
+
+# ----------------------------------------------------------------------------- expert parallel
+def _ep_exchange_job(rank, world):
+    """The exchange arithmetic of the expert-parallel layer, run for real over gloo with CPU
+    tensors: every row must reach the rank that owns its expert, arrive grouped by expert
+    after `gather_idx`, and come home to its original position."""
+    import numpy as np
+    from complexity_deep_b200.expert_parallel import exchange_plan
+    from oracle import complexity_oracle as oracle
+    E, El, V, T = 8, 4, 200, 300 + 50 * rank
+    table = oracle.build_token_mapping(V, E, oracle.zipf_probabilities(V, 1.0).float())
+    ids = oracle.zipf_token_ids(V, 1.0, T, seed=10 + rank).numpy()
+    eid, counts, offsets, perm, inv = oracle.route(ids, table, E)
+    all_counts = [torch.empty(E, dtype=torch.int32) for _ in range(world)]
+    dist.all_gather(all_counts, torch.from_numpy(counts))
+    plan = exchange_plan(torch.stack(all_counts).numpy(), rank, El)
+    assert sum(plan.in_splits) == T
+    # payload: (home rank, original row, expert id) per row, in expert-sorted order
+    rows = torch.tensor([[rank, int(r), int(eid[r])] for r in perm], dtype=torch.int64)
+    recv = torch.empty(plan.received, 3, dtype=torch.int64)
+    dist.all_to_all_single(recv, rows, plan.out_splits, plan.in_splits)
+    grouped = recv[torch.from_numpy(plan.gather_idx).long()]
+    # every received row belongs to one of my experts, grouped by expert in segment order
+    for e in range(El):
+        seg = grouped[plan.seg_offsets[e]:plan.seg_offsets[e + 1]]
+        assert bool((seg[:, 2] == rank * El + e).all())
+        assert bool((seg[1:, 0] >= seg[:-1, 0]).all())             # source-minor order
+    # "expert output" = payload tagged; scatter back to receive order with the same map
+    back = torch.empty_like(grouped)
+    back[torch.from_numpy(plan.gather_idx).long()] = grouped + torch.tensor([0, 0, 100])
+    home = torch.empty(T, 3, dtype=torch.int64)
+    dist.all_to_all_single(home, back, plan.in_splits, plan.out_splits)
+    assert bool((home[:, 0] == rank).all())
+    assert home[:, 1].tolist() == perm.tolist()                    # sorted order preserved
+    assert home[:, 2].tolist() == [int(eid[r]) + 100 for r in perm]
+    return plan.received
+
+
+def test_expert_parallel_exchange_plan_two_ranks():
+    got = run_ranks(_ep_exchange_job, port=29612)
+    assert sum(got) == 300 + 350                                   # nothing lost, nothing padded
+
+
+def test_exchange_plan_rejects_uneven_split_and_handles_empty():
+    import numpy as np
+    import pytest
+    from complexity_deep_b200.expert_parallel import exchange_plan
+    with pytest.raises(ValueError):
+        exchange_plan(np.zeros((2, 6)), 0, 4)
+    plan = exchange_plan(np.array([[0, 0, 5, 0], [0, 0, 0, 2]]), 0, 2)   # rank 0 receives nothing
+    assert plan.received == 0 and plan.out_splits == [0, 0] and plan.in_splits == [0, 5]
+    assert plan.seg_offsets.tolist() == [0, 0, 0]
+    plan1 = exchange_plan(np.array([[0, 0, 5, 0], [0, 0, 0, 2]]), 1, 2)
+    assert plan1.received == 7 and plan1.seg_offsets.tolist() == [0, 5, 7]
+    assert plan1.gather_idx.tolist() == [0, 1, 2, 3, 4, 5, 6]
