@@ -302,6 +302,127 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+
+# ------------------------------------------------------------------------------- layer modes
+LAYER_CONFIGS = {
+    # BASELINE.json config 2: isolated token-routed MLP layer on one GPU
+    "moe_layer": dict(T=16384, H=2048, E=8, I_e=5632, I_s=5632, V=32000, zipf=1.1, qkv=None),
+    # BASELINE.json config 5: expert-parallel layer incl. fused mu-QKV (32 Q / 8 KV heads, D 128)
+    "ep_layer": dict(T=65536, H=4096, E=32, I_e=2816, I_s=11008, V=100000, zipf=1.0, qkv=6144),
+}
+
+
+def run_layer(args):
+    """MoE-layer TFLOP/s: the isolated layer (1 GPU) or the expert-parallel layer (N GPUs, the
+    T tokens split across ranks, experts sharded E/N per rank, NCCL all-to-all both ways)."""
+    import torch.nn as nn
+    from complexity_deep_b200 import TokenRoutedMLP, ops
+    from complexity_deep_b200.expert_parallel import ExpertParallelMoE
+    from oracle.complexity_oracle import zipf_probabilities, zipf_token_ids  # inputs only
+    cfg = LAYER_CONFIGS[args.workload]
+    rank = int(os.environ.get("RANK", 0))
+    local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1 or args.workload == "ep_layer":
+        import torch.distributed as dist
+        if not dist.is_initialized():
+            if "MASTER_ADDR" not in os.environ:
+                os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT="29577")
+            dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    T, H, E, I_e, I_s, V = (cfg[k] for k in ("T", "H", "E", "I_e", "I_s", "V"))
+    lo, hi = shard_batch(T, world, rank)
+    t_loc = hi - lo
+    torch.manual_seed(0)                                   # same weights on every rank
+    p = zipf_probabilities(V, cfg["zipf"]).float()
+    with torch.device(dev):
+        mlp = TokenRoutedMLP(H, I_e * E, E, V, True, None)
+        if I_s != I_e:   # shared expert wider than one routed expert: swap the three Linears
+            mlp.shared_gate, mlp.shared_up = nn.Linear(H, I_s, bias=False), nn.Linear(H, I_s, bias=False)
+            mlp.shared_down = nn.Linear(I_s, H, bias=False)
+        for lin in (mlp.shared_gate, mlp.shared_up, mlp.shared_down):
+            nn.init.normal_(lin.weight, 0.0, 0.02)
+    mlp = mlp.to(torch.bfloat16).eval()
+    with torch.no_grad():
+        mlp.token_to_expert.copy_(TokenRoutedMLP._build_token_mapping(V, E, p))
+    ep = ExpertParallelMoE(mlp) if args.workload == "ep_layer" else None
+    steps_total = args.warmup + args.steps
+    gen = torch.Generator(device=dev).manual_seed(1 + rank)
+    x = torch.randn(t_loc, H, device=dev, generator=gen).to(torch.bfloat16)
+    ids = [zipf_token_ids(V, cfg["zipf"], T, seed=s)[lo:hi].to(dev) for s in range(steps_total)]
+    w_qkv = w_mu = mu_prev = None
+    if cfg["qkv"]:
+        w_qkv = (torch.randn(cfg["qkv"], H, device=dev, generator=gen) * 0.02).to(torch.bfloat16)
+        w_mu = (torch.randn(cfg["qkv"], H, device=dev, generator=gen) * 0.02).to(torch.bfloat16)
+        mu_prev = torch.randn(t_loc, H, device=dev, generator=gen).to(torch.bfloat16)
+
+    @torch.no_grad()
+    def step(i):
+        if w_qkv is not None:
+            ops.mu_qkv(x, mu_prev, w_qkv, w_mu)
+        if ep is not None:
+            return ep.forward(x.view(1, t_loc, H), ids[i].view(1, t_loc))
+        return mlp(x.view(1, t_loc, H), ids[i].view(1, t_loc))
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ops.PROFILE.reset(enabled=True)
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for i in range(args.warmup, steps_total):
+        step(i)
+    t1.record()
+    barrier()
+    ms = aggregate_ms(t0.elapsed_time(t1), dist, dev)
+    clocks = sampler.stop()
+    prof = ops.PROFILE.collect()
+    ops.PROFILE.reset(enabled=False)
+    ops.status_fetch()
+    flop = 6 * T * H * I_e + 6 * T * H * I_s + (2 * T * 2 * H * cfg["qkv"] if cfg["qkv"] else 0)
+    tflops = flop * args.steps / (ms / 1e3) / 1e12
+    pk = peaks()
+    received = None
+    if ep is not None:
+        rows = torch.tensor([ep.plan_for(mlp.routing(ids[-1].view(1, t_loc)))[0].received],
+                            device=dev)
+        gathered = [torch.empty_like(rows) for _ in range(world)]
+        dist.all_gather(gathered, rows)
+        received = [int(r) for r in gathered]
+    line = {
+        "metric": "MoE-layer TFLOP/s (bf16)", "value": round(tflops, 1), "unit": "TFLOP/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "b200",
+        "config": {"workload": args.workload, **{k: v for k, v in cfg.items()},
+                   "parallelism": (f"ep{world}: {E // world} experts per GPU, tokens dp{world}"
+                                   if ep is not None else "1 GPU"),
+                   "tokens_per_gpu": t_loc, "flop_per_step": flop},
+        "tokens_per_s": round(T * args.steps / (ms / 1e3), 1),
+        "frac_of_peak": round(tflops / world / pk["bf16_tflops"], 4),
+        "peak": pk["bf16_tflops"], "peak_source": pk["source"] + " burst, per GPU",
+        "rows_received_per_gpu": received, "clocks": clocks,
+        "gpu_launches": sum(v[2] for v in prof.values()),
+        "kernels": {k: {"launches": v[0], "ms_total": round(v[1], 3)} for k, v in prof.items()},
+    }
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -312,11 +433,15 @@ def main():
     ap.add_argument("--cpu-tokens", type=int, default=1024,
                     help="tokens of the bounded CPU sample (one sequence)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="prefill_1b", choices=["prefill_1b"] + list(LAYER_CONFIGS),
+                    help="prefill_1b is the headline; the layer modes report MoE-layer TFLOP/s")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "b200":
         args.warmup = 3
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload != "prefill_1b":
+        run_layer(args)
     else:
         run_ours(args)
 
