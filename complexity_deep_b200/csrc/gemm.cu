@@ -1,5 +1,6 @@
 // Host side of the tcgen05 GEMM: tensor-map encoding, shape checks, launch.
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <cuda.h>
@@ -51,7 +52,7 @@ bool make_map(CUtensorMap* m, const void* base, long long rows, long long cols, 
 
 struct DeviceInfo {
   int sm_count = 0;
-  bool attr_set[2][2] = {{false, false}, {false, false}};
+  bool attr_set[2][2][2] = {};  // [BN 128/256][epilogue][CTA group 1/2]
   int* status = nullptr;
 };
 constexpr int kMaxDevices = 64;
@@ -60,20 +61,55 @@ std::mutex g_mu;
 
 __device__ int g_status_word;  // raised by a kernel whose bounded wait ran out
 
-template <int BN, int EPI>
+template <int BN, int EPI, int CG>
 cudaError_t launch_one(int grid, const CUtensorMap& a0, const CUtensorMap& b0,
                        const CUtensorMap& a1, const CUtensorMap& b1, const GemmParams& p,
                        DeviceInfo& di, cudaStream_t stream) {
   constexpr int bi = (BN == 256) ? 1 : 0;
-  auto kern = gemm_bf16_sm100_kernel<BN, EPI>;
-  if (!di.attr_set[bi][EPI]) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         GemmSmem<BN>::kDynamic);
+  auto kern = gemm_bf16_sm100_kernel<BN, EPI, CG>;
+  constexpr int smem = GemmSmem<BN, CG>::kDynamic;
+  if (!di.attr_set[bi][EPI][CG - 1]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    di.attr_set[bi][EPI] = true;
+    di.attr_set[bi][EPI][CG - 1] = true;
   }
-  kern<<<grid, kGemmThreads, GemmSmem<BN>::kDynamic, stream>>>(a0, b0, a1, b1, p);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+  cfg.blockDim = dim3(kGemmThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CG;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, a0, b0, a1, b1, p);
+}
+
+template <int CG>
+cudaError_t launch_any(int block_n, int kind, int grid, const CUtensorMap& a0,
+                       const CUtensorMap& b0, const CUtensorMap& a1, const CUtensorMap& b1,
+                       const GemmParams& p, DeviceInfo& di, cudaStream_t stream) {
+  if (block_n == 256)
+    return kind == kEpiSwiGLU ? launch_one<256, kEpiSwiGLU, CG>(grid, a0, b0, a1, b1, p, di, stream)
+                              : launch_one<256, kEpiStore, CG>(grid, a0, b0, a1, b1, p, di, stream);
+  return kind == kEpiSwiGLU ? launch_one<128, kEpiSwiGLU, CG>(grid, a0, b0, a1, b1, p, di, stream)
+                            : launch_one<128, kEpiStore, CG>(grid, a0, b0, a1, b1, p, di, stream);
+}
+
+// CTA pairs (256-row tiles) pay off once there are enough rows to keep every pair busy; small
+// row counts keep 128-row tiles so more SMs get a tile.  CDEEP_CTA_GROUP=1|2 forces a choice
+// (tuning aid).
+int choose_cta_group(int M, int block_n, int sm_count) {
+  static const int forced = [] {
+    const char* e = getenv("CDEEP_CTA_GROUP");
+    return e ? atoi(e) : 0;
+  }();
+  if (forced == 1 || forced == 2) return forced;
+  if (block_n != 256) return 1;
+  return M >= 2 * kBlockM * (sm_count / 2) ? 2 : 1;
 }
 
 }  // namespace
@@ -137,15 +173,17 @@ int launch_gemm(int M, int N, int num_groups, const int* seg_offsets, const Gemm
   DeviceInfo* di = device_info(&st);
   if (!di) return st;
 
+  const int cg = choose_cta_group(M, block_n, di->sm_count);
+  const int b_box = block_n / cg;
   CUtensorMap a0, b0, a1, b1;
   if (!make_map(&a0, op0.a, M, op0.K, op0.lda, kBlockM) ||
-      !make_map(&b0, op0.b, op0.b_rows, op0.K, op0.ldb, block_n)) {
+      !make_map(&b0, op0.b, op0.b_rows, op0.K, op0.ldb, b_box)) {
     snprintf(g_cuda_err, sizeof(g_cuda_err), "cuTensorMapEncodeTiled failed (operand 0)");
     return CD_ERR_CUDA;
   }
   if (op1) {
     if (!make_map(&a1, op1->a, M, op1->K, op1->lda, kBlockM) ||
-        !make_map(&b1, op1->b, op1->b_rows, op1->K, op1->ldb, block_n)) {
+        !make_map(&b1, op1->b, op1->b_rows, op1->K, op1->ldb, b_box)) {
       snprintf(g_cuda_err, sizeof(g_cuda_err), "cuTensorMapEncodeTiled failed (operand 1)");
       return CD_ERR_CUDA;
     }
@@ -183,23 +221,18 @@ int launch_gemm(int M, int N, int num_groups, const int* seg_offsets, const Gemm
 
   // Upper bound of the tile count without reading the segment sizes (they live on the
   // device): every group adds at most one partial m-tile.
+  const int tile_m = kBlockM * cg;
   const long long n_tiles = (N + block_n - 1) / block_n;
-  const long long m_tiles_max = (M + kBlockM - 1) / kBlockM + (num_groups > 1 ? num_groups : 0);
-  long long grid = m_tiles_max * n_tiles;
-  if (grid > di->sm_count) grid = di->sm_count;
-  if (grid < 1) grid = 1;
+  const long long m_tiles_max = (M + tile_m - 1) / tile_m + (num_groups > 1 ? num_groups : 0);
+  long long units = m_tiles_max * n_tiles;           // CTAs (cg = 1) or CTA pairs (cg = 2)
+  if (units > di->sm_count / cg) units = di->sm_count / cg;
+  if (units < 1) units = 1;
+  const int grid = static_cast<int>(units) * cg;
 
   cudaError_t e;
   std::lock_guard<std::mutex> lk(g_mu);
-  if (block_n == 256) {
-    e = (epi.kind == kEpiSwiGLU)
-            ? launch_one<256, kEpiSwiGLU>(static_cast<int>(grid), a0, b0, a1, b1, p, *di, stream)
-            : launch_one<256, kEpiStore>(static_cast<int>(grid), a0, b0, a1, b1, p, *di, stream);
-  } else {
-    e = (epi.kind == kEpiSwiGLU)
-            ? launch_one<128, kEpiSwiGLU>(static_cast<int>(grid), a0, b0, a1, b1, p, *di, stream)
-            : launch_one<128, kEpiStore>(static_cast<int>(grid), a0, b0, a1, b1, p, *di, stream);
-  }
+  e = (cg == 2) ? launch_any<2>(block_n, epi.kind, grid, a0, b0, a1, b1, p, *di, stream)
+                : launch_any<1>(block_n, epi.kind, grid, a0, b0, a1, b1, p, *di, stream);
   if (e != cudaSuccess) return cuda_fail(e, "gemm launch");
   return CD_OK;
 }

@@ -66,12 +66,14 @@ struct GemmParams {
   int* status;             // device word; set non-zero when a bounded wait ran out
 };
 
-template <int BN>
+// CG = 1: one CTA per 128-row tile.  CG = 2: a CTA pair per 256-row tile (cta_group::2); each
+// CTA stages its 128 rows of A and its BN / 2 rows of B.
+template <int BN, int CG>
 struct GemmSmem {
-  static constexpr int kStages = (BN == 256) ? 4 : 6;
   static constexpr int kABytes = kBlockM * kBlockK * 2;
-  static constexpr int kBBytes = BN * kBlockK * 2;
+  static constexpr int kBBytes = (BN / CG) * kBlockK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = (kStageBytes > 32768) ? 4 : 6;
   static constexpr int kTileBytes = kStages * kStageBytes;
   // after the tiles: epilogue staging (4 warps x 2 buffers), barriers, TMEM base, abort
   // flag, schedule tables
@@ -97,11 +99,11 @@ struct TileCoord {
 // share a small set of B tiles while the A band stays in L2.
 __device__ __forceinline__ TileCoord decode_tile(int t, int& gcur, const int* prefix,
                                                  const int* seg, int n_tiles, int band,
-                                                 int bn) {
+                                                 int bn, int block_m) {
   while (t >= prefix[gcur + 1]) ++gcur;
   const int local = t - prefix[gcur];
   const int lo = seg[gcur], hi = seg[gcur + 1];
-  const int m_tiles = (hi - lo + kBlockM - 1) / kBlockM;
+  const int m_tiles = (hi - lo + block_m - 1) / block_m;
   const int per_band = band * n_tiles;
   const int b = local / per_band;
   const int within = local - b * per_band;
@@ -111,7 +113,7 @@ __device__ __forceinline__ TileCoord decode_tile(int t, int& gcur, const int* pr
   const int m_idx = m_first + (within - n_idx * bh);
   TileCoord c;
   c.group = gcur;
-  c.m0 = lo + m_idx * kBlockM;
+  c.m0 = lo + m_idx * block_m;
   c.n0 = n_idx * bn;
   c.row_end = hi;
   return c;
@@ -137,14 +139,18 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
 
-template <int BN, int EPI>
+template <int BN, int EPI, int CG>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
                        const __grid_constant__ CUtensorMap tmB0,
                        const __grid_constant__ CUtensorMap tmA1,
                        const __grid_constant__ CUtensorMap tmB1, const GemmParams p) {
-  using L = GemmSmem<BN>;
+  using L = GemmSmem<BN, CG>;
   constexpr int S = L::kStages;
+  constexpr int kTileM = kBlockM * CG;             // rows per tile (per CTA pair when CG = 2)
+  const uint32_t crank = (CG == 2) ? cluster_ctarank() : 0u;  // 0 = leader
+  const int tile0 = blockIdx.x / CG;               // both CTAs of a pair walk the same tiles
+  const int tstride = gridDim.x / CG;
   constexpr uint32_t kTmemCols = 2 * BN;  // two accumulators of BN fp32 columns
   static_assert(kTmemCols == 256 || kTmemCols == 512, "TMEM allocation must be a power of two");
 
@@ -175,7 +181,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full[a], 1);
-      mbar_init(&tmem_empty[a], 4);  // one arrival per epilogue warp
+      mbar_init(&tmem_empty[a], 4 * CG);  // one arrival per epilogue warp (of both CTAs)
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -186,8 +192,13 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
       tma_prefetch_desc(&tmB1);
     }
   } else if (warp == 1) {
-    tmem_alloc(tmem_base_slot, kTmemCols);
-    tmem_relinquish();
+    if constexpr (CG == 2) {
+      tmem_alloc_pair(tmem_base_slot, kTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_base_slot, kTmemCols);
+      tmem_relinquish();
+    }
   } else if (warp == 2 && lane == 0) {
     int acc = 0;
     prefix[0] = 0;
@@ -196,12 +207,13 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
       const int hi = p.seg_offsets ? p.seg_offsets[g + 1] : p.M;
       seg[g] = lo;
       seg[g + 1] = hi;
-      acc += ((hi - lo + kBlockM - 1) / kBlockM) * n_tiles;
+      acc += ((hi - lo + kTileM - 1) / kTileM) * n_tiles;
       prefix[g + 1] = acc;
     }
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (CG == 2) cluster_sync_all();  // the peer's barriers exist before anyone signals them
   tc_fence_after();
 
   const uint32_t tmem_base = *tmem_base_slot;
@@ -213,10 +225,11 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
       uint32_t it = 0;
       int gcur = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        const TileCoord c = decode_tile(t, gcur, prefix, seg, n_tiles, p.band, BN);
-        const int b0_row = c.group * p.b0_group_rows + c.n0;
-        const int b1_row = c.group * p.b1_group_rows + c.n0;
+      for (int t = tile0; t < total_tiles && ok; t += tstride) {
+        const TileCoord c = decode_tile(t, gcur, prefix, seg, n_tiles, p.band, BN, kTileM);
+        const int a_row = c.m0 + static_cast<int>(crank) * kBlockM;
+        const int b0_row = c.group * p.b0_group_rows + c.n0 + static_cast<int>(crank) * (BN / CG);
+        const int b1_row = c.group * p.b1_group_rows + c.n0 + static_cast<int>(crank) * (BN / CG);
         for (int kb = 0; kb < kb_total; ++kb, ++it) {
           const uint32_t s = it % S;
           const uint32_t ph = (it / S) & 1u;
@@ -226,13 +239,26 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
           }
           uint8_t* a_dst = smem + s * L::kStageBytes;
           uint8_t* b_dst = a_dst + L::kABytes;
-          mbar_arrive_expect_tx(&full_bar[s], L::kStageBytes);
-          if (kb < kb0) {
-            tma_load_2d(a_dst, &tmA0, &full_bar[s], kb * kBlockK, c.m0);
-            tma_load_2d(b_dst, &tmB0, &full_bar[s], kb * kBlockK, b0_row);
+          if constexpr (CG == 2) {
+            // the leader's barrier collects the bytes of both CTAs
+            if (crank == 0) mbar_arrive_expect_tx(&full_bar[s], 2 * L::kStageBytes);
+            const uint32_t bar = map_to_cta(smem_u32(&full_bar[s]), 0);
+            if (kb < kb0) {
+              tma_load_2d_pair(a_dst, &tmA0, bar, kb * kBlockK, a_row);
+              tma_load_2d_pair(b_dst, &tmB0, bar, kb * kBlockK, b0_row);
+            } else {
+              tma_load_2d_pair(a_dst, &tmA1, bar, (kb - kb0) * kBlockK, a_row);
+              tma_load_2d_pair(b_dst, &tmB1, bar, (kb - kb0) * kBlockK, b1_row);
+            }
           } else {
-            tma_load_2d(a_dst, &tmA1, &full_bar[s], (kb - kb0) * kBlockK, c.m0);
-            tma_load_2d(b_dst, &tmB1, &full_bar[s], (kb - kb0) * kBlockK, b1_row);
+            mbar_arrive_expect_tx(&full_bar[s], L::kStageBytes);
+            if (kb < kb0) {
+              tma_load_2d(a_dst, &tmA0, &full_bar[s], kb * kBlockK, a_row);
+              tma_load_2d(b_dst, &tmB0, &full_bar[s], kb * kBlockK, b0_row);
+            } else {
+              tma_load_2d(a_dst, &tmA1, &full_bar[s], (kb - kb0) * kBlockK, a_row);
+              tma_load_2d(b_dst, &tmB1, &full_bar[s], (kb - kb0) * kBlockK, b1_row);
+            }
           }
         }
       }
@@ -249,12 +275,12 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(kBlockM, BN);
+    if (lane == 0 && crank == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(kTileM, BN);
       uint32_t it = 0;
       uint32_t tcount = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tcount) {
+      for (int t = tile0; t < total_tiles && ok; t += tstride, ++tcount) {
         const uint32_t acc = tcount & 1u;
         const uint32_t acc_ph = (tcount >> 1) & 1u;
         if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1u, abort_flag)) {
@@ -278,11 +304,17 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
           for (int k = 0; k < kBlockK / kUmmaK; ++k) {
             // advancing 16 bf16 (32 bytes) along K inside the swizzle row: +2 in the
             // descriptor's 16-byte address units
-            umma_bf16(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            if constexpr (CG == 2)
+              umma_bf16_pair(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            else
+              umma_bf16(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
           }
-          umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
+          // frees the stage (in both CTAs of a pair) once these MMAs have read it
+          if constexpr (CG == 2) umma_commit_pair(&empty_bar[s]); else umma_commit(&empty_bar[s]);
         }
-        if (ok) umma_commit(&tmem_full[acc]);  // accumulator complete
+        if (ok) {  // accumulator complete
+          if constexpr (CG == 2) umma_commit_pair(&tmem_full[acc]); else umma_commit(&tmem_full[acc]);
+        }
       }
     }
     __syncwarp();
@@ -303,11 +335,11 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
     uint32_t tcount = 0;
     int gcur = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tcount) {
-      const TileCoord c = decode_tile(t, gcur, prefix, seg, n_tiles, p.band, BN);
+    for (int t = tile0; t < total_tiles && ok; t += tstride, ++tcount) {
+      const TileCoord c = decode_tile(t, gcur, prefix, seg, n_tiles, p.band, BN, kTileM);
       const uint32_t acc = tcount & 1u;
       const uint32_t acc_ph = (tcount >> 1) & 1u;
-      const int r = c.m0 + quarter * 32 + lane;
+      const int r = c.m0 + static_cast<int>(crank) * kBlockM + quarter * 32 + lane;
       const bool row_ok = r < c.row_end;
       int orow = 0;
       if constexpr (EPI == kEpiStore) {
@@ -475,17 +507,23 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
       // this warp is done reading the accumulator
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      if (lane == 0) {
+        if constexpr (CG == 2)
+          mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc]), 0));  // the leader's barrier
+        else
+          mbar_arrive(&tmem_empty[acc]);
+      }
     }
   }
 
   // ---------------------------------------------------------------- teardown
   tc_fence_before();
   __syncthreads();
+  if constexpr (CG == 2) cluster_sync_all();  // the leader's MMAs read the peer's memory until here
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();
-    tmem_dealloc(tmem_base, kTmemCols);
+    if constexpr (CG == 2) tmem_dealloc_pair(tmem_base, kTmemCols); else tmem_dealloc(tmem_base, kTmemCols);
   }
   if (threadIdx.x == 0 && *abort_flag && p.status) atomicExch(p.status, 1);
 }
