@@ -33,6 +33,9 @@ WORKLOAD = "1B-class prefill: hidden 2048, 24 layers, 16Q/8KV (D 128), intermedi
 MODEL = dict(vocab_size=32000, hidden_size=2048, intermediate_size=5632, num_hidden_layers=24,
              num_attention_heads=16, num_key_value_heads=8, num_experts=8)
 GLOBAL_BATCH, SEQ_LEN = 32, 2048
+# DRAM traffic of one cd_mu_qkv launch per token, from the ncu capture summarised in
+# profiles/gemm_bf16_sm100_1b_layer_small_case.md (719 MB at 24 576 tokens)
+MU_QKV_DRAM_BYTES_PER_TOKEN = 719.15e6 / 24576
 
 
 def shard_batch(global_batch: int, world: int, rank: int):
@@ -223,7 +226,11 @@ def run_ours(args):
         roofline = {"bound": "tensor", "kernel": "gemm_bf16_sm100_kernel", "entry": dom, "achieved": k["tflops"], "peak": pk["bf16_tflops"],
                     "peak_source": pk["source"] + " burst", "unit": "TFLOP/s", "frac": k["frac"],
                     "flop_per_launch": fl[dom] * local_tokens,
-                    "ms_per_launch": round(k["ms_total"] / k["launches"], 4), "traffic": None}
+                    "ms_per_launch": round(k["ms_total"] / k["launches"], 4),
+                    "traffic": (round(MU_QKV_DRAM_BYTES_PER_TOKEN * local_tokens)
+                                if dom == "mu_qkv" else None),
+                    "traffic_source": "ncu dram__bytes_read+write of cd_mu_qkv at 24576 tokens "
+                                      "(719 MB), scaled per token; profiles/"}
     gpu_launches = sum(v[2] for v in prof.values())
 
     line = {
@@ -423,6 +430,111 @@ def run_layer(args):
         dist.destroy_process_group()
 
 
+def run_decode(args):
+    """BASELINE.json config 4: 1B-class decode, concurrent sequences with a prefilled KV cache
+    of 4096 tokens (values N(0,1) bf16), one new Zipf token per sequence per step, an all-zero
+    additive mask so the new token attends to the whole cache.  The batch (256 sequences) is
+    split data-parallel; reports decode tokens/s and the weight-streaming rate of the GEMM
+    entry points (HBM-bound at this M)."""
+    from complexity_deep_b200 import ops
+    from complexity_deep_b200.core.attention import _KVBuffer
+    from oracle.complexity_oracle import zipf_token_ids  # input distribution only
+    rank = int(os.environ.get("RANK", 0))
+    local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    model = build_model(dev)
+    batch = args.batch or 256
+    lo, hi = shard_batch(batch, world, rank)
+    B, P = hi - lo, args.cache_len
+    cfg = MODEL
+    D = cfg["hidden_size"] // cfg["num_attention_heads"]
+    hkv, L = cfg["num_key_value_heads"], cfg["num_hidden_layers"]
+    steps_total = args.warmup + args.steps
+    gen = torch.Generator(device=dev).manual_seed(1 + rank)
+
+    def cache_tensor():
+        # a cache as a prefill through this model would leave it: a view of a buffer with room
+        # to grow, so decode steps append in place
+        buf = torch.empty(B, hkv, P + steps_total + 8, D, dtype=torch.bfloat16, device=dev)
+        buf.normal_(0.0, 1.0, generator=gen)
+        view = buf[:, :, :P]
+        view._cd_kv = _KVBuffer(buf, P)
+        return view
+
+    past = [(cache_tensor(), cache_tensor()) for _ in range(L)]
+    ids = zipf_token_ids(cfg["vocab_size"], 1.1, batch * steps_total, seed=0).view(steps_total, batch)
+    ids = ids[:, lo:hi].contiguous().to(dev)
+
+    @torch.no_grad()
+    def step(i, past):
+        kv_len = past[0][0].shape[2] + 1
+        mask = torch.zeros(B, 1, 1, kv_len, dtype=torch.bfloat16, device=dev)
+        out = model(ids[i].view(B, 1), attention_mask=mask, past_key_values=past, use_cache=True)
+        return out.logits, out.past_key_values
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        _, past = step(i, past)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ops.PROFILE.reset(enabled=True)
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for i in range(args.warmup, steps_total):
+        _, past = step(i, past)
+    t1.record()
+    barrier()
+    ms = aggregate_ms(t0.elapsed_time(t1), dist, dev)
+    clocks = sampler.stop()
+    prof = ops.PROFILE.collect()
+    ops.PROFILE.reset(enabled=False)
+    ops.status_fetch()
+    H, V, E = cfg["hidden_size"], cfg["vocab_size"], cfg["num_experts"]
+    I_e = cfg["intermediate_size"] // E
+    nqkv = (cfg["num_attention_heads"] + 2 * hkv) * D
+    weight_bytes = {  # bf16 weights one launch streams
+        "mu_qkv": 2 * 2 * H * nqkv, "linear_o_proj": 2 * H * H, "moe_up_routed": 2 * 2 * E * H * I_e,
+        "moe_up_shared": 2 * 2 * H * I_e, "moe_down": 2 * (E + 1) * H * I_e, "mu_proj": 2 * H * H,
+        "linear_lm_head": 2 * H * V}
+    pk = peaks()
+    kernels = {}
+    for name, (launches, total_ms, _) in prof.items():
+        entry = {"launches": launches, "us_per_launch": round(total_ms / launches * 1e3, 2)}
+        if name in weight_bytes:
+            gbs = weight_bytes[name] / (total_ms / launches / 1e3) / 1e9
+            entry.update(weight_gbs=round(gbs, 1), frac_of_hbm=round(gbs / pk["hbm_gbs"], 4))
+        kernels[name] = entry
+    cache_bytes = 2 * L * B * hkv * (P + steps_total / 2) * D * 2
+    line = {
+        "metric": "decode tokens/s (1B bf16)", "value": round(batch * args.steps / (ms / 1e3), 1),
+        "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms / args.steps, 3), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "b200",
+        "config": {"workload": f"1B-class decode, {batch} sequences, KV cache {P} tokens, zero additive mask",
+                   "parallelism": f"dp{world}", "sequences_per_gpu": B},
+        "hbm_floor_ms": {"weights": round(sum(weight_bytes[k] * (L if k != "linear_lm_head" else 1)
+                                              for k in weight_bytes) / pk["hbm_gbs"] / 1e6, 3),
+                         "kv_cache": round(cache_bytes / pk["hbm_gbs"] / 1e6, 3)},
+        "clocks": clocks, "gpu_launches": sum(v[2] for v in prof.values()), "kernels": kernels,
+    }
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -433,13 +545,16 @@ def main():
     ap.add_argument("--cpu-tokens", type=int, default=1024,
                     help="tokens of the bounded CPU sample (one sequence)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="prefill_1b", choices=["prefill_1b"] + list(LAYER_CONFIGS),
+    ap.add_argument("--cache-len", type=int, default=4096, help="decode_1b: prefilled KV tokens")
+    ap.add_argument("--workload", default="prefill_1b", choices=["prefill_1b", "decode_1b"] + list(LAYER_CONFIGS),
                     help="prefill_1b is the headline; the layer modes report MoE-layer TFLOP/s")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "b200":
         args.warmup = 3
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "decode_1b":
+        run_decode(args)
     elif args.workload != "prefill_1b":
         run_layer(args)
     else:

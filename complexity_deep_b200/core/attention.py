@@ -26,6 +26,39 @@ from ._cache import DerivedCache
 from .rotary import RotaryEmbedding
 
 
+class _KVBuffer:
+    """Backing store of a KV cache that grows in place.
+
+    The reference appends with ``torch.cat([past, new], dim=2)`` (attention.py:158-161), which
+    copies the whole cache on every decode step.  Here the tensor handed back to the caller is
+    a view ``buf[:, :, :used]`` of a larger buffer; when that same tensor comes back as
+    ``past_key_value`` and nobody has appended to it since (``used`` still equals its length),
+    the new rows are written behind it and a longer view is returned — same values as the
+    concatenation, without the copy.  Any other tensor (a user-built cache, a cache that was
+    already extended by another branch) is copied once into a fresh buffer.
+    """
+
+    def __init__(self, buf: torch.Tensor, used: int) -> None:
+        self.buf, self.used = buf, used
+
+
+def _kv_append(past: torch.Tensor, new: torch.Tensor) -> torch.Tensor:
+    P, S = past.shape[2], new.shape[2]
+    holder = getattr(past, "_cd_kv", None)
+    if (holder is None or holder.used != P or holder.buf.shape[2] < P + S
+            or holder.buf.dtype != new.dtype or holder.buf.device != new.device):
+        B, Hk, _, D = past.shape
+        cap = P + S + max(256, (P + S) // 8)
+        buf = torch.empty(B, Hk, cap, D, dtype=new.dtype, device=new.device)
+        buf[:, :, :P].copy_(past)
+        holder = _KVBuffer(buf, P)
+    holder.buf[:, :, P:P + S].copy_(new)
+    holder.used = P + S
+    out = holder.buf[:, :, :P + S]
+    out._cd_kv = holder
+    return out
+
+
 class ComplexityAttention(nn.Module):
     def __init__(
         self,
@@ -95,8 +128,8 @@ class ComplexityAttention(nn.Module):
         k = qkv[:, hq * D: (hq + hkv) * D].view(B, S, hkv, D).transpose(1, 2)
         v = qkv[:, (hq + hkv) * D:].view(B, S, hkv, D).transpose(1, 2)
         if past_key_value is not None:
-            k = torch.cat([past_key_value[0], k], dim=2)
-            v = torch.cat([past_key_value[1], v], dim=2)
+            k = _kv_append(past_key_value[0], k)
+            v = _kv_append(past_key_value[1], v)
         new_kv = (k, v) if use_cache else None
 
         with ops._Span("sdpa", kernels=0):  # PyTorch operator, timed for the breakdown only

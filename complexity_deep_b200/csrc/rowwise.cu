@@ -201,9 +201,12 @@ qk_norm_rope_kernel(__nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __rest
   }
 }
 
-// Vector form for D % 16 == 0 with D/16 a power of two <= 32 (D = 16 ... 512): a head is
-// handled by D/16 adjacent lanes, each owning 8 consecutive columns of the first half and the
-// 8 partner columns D/2 further (16-byte accesses), so a warp covers 32 / (D/16) heads.
+// Vector form for D % 16 == 0 with D/16 a power of two <= 32 (D = 16 ... 512).  One warp per
+// token: a head is handled by D/16 adjacent lanes (each owns 8 consecutive columns of the
+// first half and the 8 partner columns D/2 further, 16-byte accesses), the warp's 32 / (D/16)
+// lane groups take adjacent heads, and every lane walks over heads with the SAME column
+// chunk, so the cos/sin values of the token's position are loaded once and reused for all
+// its heads.
 __global__ void __launch_bounds__(256)
 qk_norm_rope_vec_kernel(__nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ q_w,
                         const __nv_bfloat16* __restrict__ k_w, const float* __restrict__ cos_t,
@@ -211,68 +214,105 @@ qk_norm_rope_vec_kernel(__nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __
                         int hkv, int D) {
   const int heads = hq + hkv;
   const int half = D >> 1;
-  const int lph = half >> 3;  // lanes per head
-  const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  const long long inst = gid / lph;
-  const int j = static_cast<int>(gid - inst * lph) * 8;
-  const bool active = inst < static_cast<long long>(T) * heads;
-  const int t = active ? static_cast<int>(inst / heads) : 0;
-  const int h = active ? static_cast<int>(inst - static_cast<long long>(t) * heads) : 0;
-  const int ld = (hq + 2 * hkv) * D;
-  __nv_bfloat16* head = qkv + static_cast<size_t>(t) * ld + static_cast<size_t>(h) * D;
-  const __nv_bfloat16* nw = (h < hq) ? q_w : k_w;
-
-  uint4 a = make_uint4(0, 0, 0, 0), b = make_uint4(0, 0, 0, 0);
-  if (active) {
-    a = *reinterpret_cast<const uint4*>(head + j);
-    b = *reinterpret_cast<const uint4*>(head + half + j);
-  }
-  const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
-  float x1[8], x2[8];
-  float ss = 0.f;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    x1[2 * i] = lo_f(aw[i]); x1[2 * i + 1] = hi_f(aw[i]);
-    x2[2 * i] = lo_f(bw[i]); x2[2 * i + 1] = hi_f(bw[i]);
-    ss += x1[2 * i] * x1[2 * i] + x1[2 * i + 1] * x1[2 * i + 1] + x2[2 * i] * x2[2 * i] +
-          x2[2 * i + 1] * x2[2 * i + 1];
-  }
-  for (int o = lph >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-  if (!active) return;
-  if (nw) {
-    const float rstd = rsqrtf(ss / static_cast<float>(D) + eps);
-    const uint4 wa = *reinterpret_cast<const uint4*>(nw + j);
-    const uint4 wb = *reinterpret_cast<const uint4*>(nw + half + j);
-    const uint32_t wwa[4] = {wa.x, wa.y, wa.z, wa.w}, wwb[4] = {wb.x, wb.y, wb.z, wb.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      x1[2 * i] *= rstd * lo_f(wwa[i]); x1[2 * i + 1] *= rstd * hi_f(wwa[i]);
-      x2[2 * i] *= rstd * lo_f(wwb[i]); x2[2 * i + 1] *= rstd * hi_f(wwb[i]);
-    }
-  }
+  const int lph = half >> 3;        // lanes per head
+  const int groups = 32 / lph;      // heads handled side by side by one warp
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= T) return;               // whole warps leave together
+  const int lane = threadIdx.x & 31;
+  const int g = lane / lph;
+  const int j = (lane - g * lph) * 8;
   const int pos = pos0 + (t % S);
-  const float4* c1 = reinterpret_cast<const float4*>(cos_t + static_cast<size_t>(pos) * D + j);
-  const float4* s1 = reinterpret_cast<const float4*>(sin_t + static_cast<size_t>(pos) * D + j);
-  const float4* c2 = reinterpret_cast<const float4*>(cos_t + static_cast<size_t>(pos) * D + half + j);
-  const float4* s2 = reinterpret_cast<const float4*>(sin_t + static_cast<size_t>(pos) * D + half + j);
-  float o1[8], o2[8];
+  float c1[8], s1[8], c2[8], s2[8];
+  {
+    const float* cs = cos_t + static_cast<size_t>(pos) * D;
+    const float* sn = sin_t + static_cast<size_t>(pos) * D;
 #pragma unroll
-  for (int v = 0; v < 2; ++v) {
-    const float4 ca = __ldg(c1 + v), sa = __ldg(s1 + v), cb = __ldg(c2 + v), sb = __ldg(s2 + v);
-    const float cav[4] = {ca.x, ca.y, ca.z, ca.w}, sav[4] = {sa.x, sa.y, sa.z, sa.w};
-    const float cbv[4] = {cb.x, cb.y, cb.z, cb.w}, sbv[4] = {sb.x, sb.y, sb.z, sb.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int e = v * 4 + i;
-      o1[e] = x1[e] * cav[i] - x2[e] * sav[i];   // x * cos + rotate_half(x) * sin, first half
-      o2[e] = x2[e] * cbv[i] + x1[e] * sbv[i];   // second half
+    for (int v = 0; v < 2; ++v) {
+      const float4 a = __ldg(reinterpret_cast<const float4*>(cs + j) + v);
+      const float4 b = __ldg(reinterpret_cast<const float4*>(sn + j) + v);
+      const float4 c = __ldg(reinterpret_cast<const float4*>(cs + half + j) + v);
+      const float4 d = __ldg(reinterpret_cast<const float4*>(sn + half + j) + v);
+      c1[4 * v] = a.x; c1[4 * v + 1] = a.y; c1[4 * v + 2] = a.z; c1[4 * v + 3] = a.w;
+      s1[4 * v] = b.x; s1[4 * v + 1] = b.y; s1[4 * v + 2] = b.z; s1[4 * v + 3] = b.w;
+      c2[4 * v] = c.x; c2[4 * v + 1] = c.y; c2[4 * v + 2] = c.z; c2[4 * v + 3] = c.w;
+      s2[4 * v] = d.x; s2[4 * v + 1] = d.y; s2[4 * v + 2] = d.z; s2[4 * v + 3] = d.w;
     }
   }
-  uint4 oa, ob;
-  oa.x = pack2(o1[0], o1[1]); oa.y = pack2(o1[2], o1[3]); oa.z = pack2(o1[4], o1[5]); oa.w = pack2(o1[6], o1[7]);
-  ob.x = pack2(o2[0], o2[1]); ob.y = pack2(o2[2], o2[3]); ob.z = pack2(o2[4], o2[5]); ob.w = pack2(o2[6], o2[7]);
-  *reinterpret_cast<uint4*>(head + j) = oa;
-  *reinterpret_cast<uint4*>(head + half + j) = ob;
+  // norm weights of this lane's columns (q and k heads use different weights)
+  float wq1[8], wq2[8], wk1[8], wk2[8];
+  if (q_w) {
+    const uint4 a = *reinterpret_cast<const uint4*>(q_w + j);
+    const uint4 b = *reinterpret_cast<const uint4*>(q_w + half + j);
+    const uint4 c = *reinterpret_cast<const uint4*>(k_w + j);
+    const uint4 d = *reinterpret_cast<const uint4*>(k_w + half + j);
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+    const uint32_t cw[4] = {c.x, c.y, c.z, c.w}, dw[4] = {d.x, d.y, d.z, d.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      wq1[2 * i] = lo_f(aw[i]); wq1[2 * i + 1] = hi_f(aw[i]);
+      wq2[2 * i] = lo_f(bw[i]); wq2[2 * i + 1] = hi_f(bw[i]);
+      wk1[2 * i] = lo_f(cw[i]); wk1[2 * i + 1] = hi_f(cw[i]);
+      wk2[2 * i] = lo_f(dw[i]); wk2[2 * i + 1] = hi_f(dw[i]);
+    }
+  }
+  const int ld = (hq + 2 * hkv) * D;
+  __nv_bfloat16* row = qkv + static_cast<size_t>(t) * ld;
+  // All loads of the token are issued before any arithmetic (up to kMaxIter heads per lane
+  // group) so enough bytes are in flight to cover HBM latency.
+  constexpr int kMaxIter = 8;
+  for (int hb = 0; hb < heads; hb += groups * kMaxIter) {   // uniform trip count across the warp
+    uint4 a[kMaxIter], b[kMaxIter];
+#pragma unroll
+    for (int i = 0; i < kMaxIter; ++i) {
+      const int h = hb + i * groups + g;
+      a[i] = make_uint4(0, 0, 0, 0);
+      b[i] = make_uint4(0, 0, 0, 0);
+      if (h < heads) {
+        a[i] = *reinterpret_cast<const uint4*>(row + static_cast<size_t>(h) * D + j);
+        b[i] = *reinterpret_cast<const uint4*>(row + static_cast<size_t>(h) * D + half + j);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < kMaxIter; ++i) {
+      const int h = hb + i * groups + g;
+      if (hb + i * groups >= heads) break;                  // uniform
+      const bool active = h < heads;
+      const uint32_t aw[4] = {a[i].x, a[i].y, a[i].z, a[i].w};
+      const uint32_t bw[4] = {b[i].x, b[i].y, b[i].z, b[i].w};
+      float x1[8], x2[8];
+      float ss = 0.f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        x1[2 * e] = lo_f(aw[e]); x1[2 * e + 1] = hi_f(aw[e]);
+        x2[2 * e] = lo_f(bw[e]); x2[2 * e + 1] = hi_f(bw[e]);
+        ss += x1[2 * e] * x1[2 * e] + x1[2 * e + 1] * x1[2 * e + 1] + x2[2 * e] * x2[2 * e] +
+              x2[2 * e + 1] * x2[2 * e + 1];
+      }
+      for (int o = lph >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if (!active) continue;
+      if (q_w) {
+        const float rstd = rsqrtf(ss / static_cast<float>(D) + eps);
+        const bool is_q = h < hq;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          x1[e] *= rstd * (is_q ? wq1[e] : wk1[e]);
+          x2[e] *= rstd * (is_q ? wq2[e] : wk2[e]);
+        }
+      }
+      float o1[8], o2[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        o1[e] = x1[e] * c1[e] - x2[e] * s1[e];   // x * cos + rotate_half(x) * sin, first half
+        o2[e] = x2[e] * c2[e] + x1[e] * s2[e];   // second half
+      }
+      uint4 oa, ob;
+      oa.x = pack2(o1[0], o1[1]); oa.y = pack2(o1[2], o1[3]); oa.z = pack2(o1[4], o1[5]); oa.w = pack2(o1[6], o1[7]);
+      ob.x = pack2(o2[0], o2[1]); ob.y = pack2(o2[2], o2[3]); ob.z = pack2(o2[4], o2[5]); ob.w = pack2(o2[6], o2[7]);
+      __nv_bfloat16* head = row + static_cast<size_t>(h) * D;
+      *reinterpret_cast<uint4*>(head + j) = oa;
+      *reinterpret_cast<uint4*>(head + half + j) = ob;
+    }
+  }
 }
 
 }  // namespace
@@ -316,8 +356,7 @@ cudaError_t launch_qk_norm_rope(void* qkv, const void* q_w, const void* k_w, con
                        (reinterpret_cast<uintptr_t>(q_w) & 15) == 0 &&
                        (reinterpret_cast<uintptr_t>(k_w) & 15) == 0;
   if ((D & 15) == 0 && lph >= 1 && lph <= 32 && (lph & (lph - 1)) == 0 && aligned) {
-    const long long threads = static_cast<long long>(T) * (hq + hkv) * lph;
-    const long long nblocks = (threads + 255) / 256;
+    const int nblocks = (T + 7) / 8;  // one warp per token, 8 warps per block
     qk_norm_rope_vec_kernel<<<static_cast<unsigned>(nblocks), 256, 0, stream>>>(
         static_cast<__nv_bfloat16*>(qkv), static_cast<const __nv_bfloat16*>(q_w),
         static_cast<const __nv_bfloat16*>(k_w), cos_t, sin_t, eps, T, S, pos0, hq, hkv, D);

@@ -174,3 +174,22 @@ def test_table_validation():
     assert sig == mlp._table_signature()
     mlp.token_to_expert.zero_()               # ablation: in-place edit must change the signature
     assert mlp._table_signature() != sig
+
+
+def test_kv_cache_append_in_place_semantics():
+    """The growing KV view equals torch.cat, reuses its buffer on a linear decode, and falls
+    back to a copy when the same past is extended twice (branching)."""
+    from complexity_deep_b200.core.attention import _kv_append
+    g = torch.Generator().manual_seed(0)
+    past = torch.randn(2, 2, 5, 4, generator=g)
+    n1, n2, n3 = (torch.randn(2, 2, 1, 4, generator=g) for _ in range(3))
+    a = _kv_append(past, n1)
+    assert torch.equal(a, torch.cat([past, n1], 2))
+    b = _kv_append(a, n2)
+    assert torch.equal(b, torch.cat([past, n1, n2], 2))
+    assert b._cd_kv.buf.data_ptr() == a._cd_kv.buf.data_ptr()      # no copy on the second step
+    assert torch.equal(a, torch.cat([past, n1], 2))                # the shorter view is intact
+    c = _kv_append(a, n3)                                          # branch from the older view
+    assert torch.equal(c, torch.cat([past, n1, n3], 2))
+    assert torch.equal(b, torch.cat([past, n1, n2], 2))            # first branch not clobbered
+    assert c._cd_kv.buf.data_ptr() != b._cd_kv.buf.data_ptr()
