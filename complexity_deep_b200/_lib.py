@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_char_p, c_float, c_int, c_size_t, c_void_p
+from ctypes import c_char_p, c_float, c_int, c_longlong, c_size_t, c_void_p
 
 LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libcdeep.so")
 
@@ -30,6 +30,11 @@ SIGNATURES = {
     "cd_gather_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "cd_qk_norm_rope": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int,
                                 c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "cd_decode_attention_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
+    "cd_decode_attention": (c_int, [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong,
+                                    c_longlong, c_longlong, c_void_p, c_longlong, c_float, c_int,
+                                    c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_size_t,
+                                    c_void_p]),
     "cd_gate_up_packed_rows": (c_int, [c_int, c_int]),
     "cd_moe_up": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
                           c_int, c_void_p]),

@@ -142,19 +142,19 @@ class TokenRoutedMLP(nn.Module):
                                     self.num_experts)
 
     # ------------------------------------------------------------------ packed weights
-    def _packed_routed(self):
+    def _packed_routed(self, rows: Optional[int] = None):
         g, u = self.gate_proj_w, self.up_proj_w
-        bn = ops.choose_block_n(self.expert_intermediate_size)
+        bn = ops.choose_block_n(self.expert_intermediate_size, rows)
         packed = self._derived.get(
-            "routed_gate_up", (g, u),
+            f"routed_gate_up_{bn}", (g, u),
             lambda: ops.pack_gate_up(g.detach().transpose(1, 2), u.detach().transpose(1, 2), bn))
         return packed, bn
 
-    def _packed_shared(self):
+    def _packed_shared(self, rows: Optional[int] = None):
         g, u = self.shared_gate.weight, self.shared_up.weight
-        bn = ops.choose_block_n(g.shape[0])
+        bn = ops.choose_block_n(g.shape[0], rows)
         packed = self._derived.get(
-            "shared_gate_up", (g, u),
+            f"shared_gate_up_{bn}", (g, u),
             lambda: ops.pack_gate_up(g.detach()[None], u.detach()[None], bn))
         return packed, bn
 
@@ -168,12 +168,13 @@ class TokenRoutedMLP(nn.Module):
                        residual: Optional[torch.Tensor]) -> torch.Tensor:
         """MoE on rows already grouped by expert; returns rows in ORIGINAL order,
         ``out[perm[j]] = shared(x_j) + expert(x_j) (+ residual[perm[j]])``."""
-        packed_r, bn_r = self._packed_routed()
+        rows = x_sorted.shape[0]
+        packed_r, bn_r = self._packed_routed(rows)
         h_r = ops.moe_up(x_sorted, routing.offsets, self.num_experts, packed_r,
                          self.expert_intermediate_size, bn_r)
         h_s = wd_s = None
         if self.use_shared_expert:
-            packed_s, bn_s = self._packed_shared()
+            packed_s, bn_s = self._packed_shared(rows)
             h_s = ops.moe_up(x_sorted, None, 1, packed_s, self.shared_gate.weight.shape[0], bn_s)
             wd_s = self.shared_down.weight.detach()
         return ops.moe_down(h_r, self._down_routed(), h_s, wd_s, routing.offsets,

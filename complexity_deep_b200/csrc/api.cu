@@ -100,8 +100,31 @@ int cd_qk_norm_rope(void* qkv, const void* q_w, const void* k_w, const float* co
   return e == cudaSuccess ? CD_OK : cuda_fail(e, "qk_norm_rope launch");
 }
 
+size_t cd_decode_attention_workspace_bytes(int B, int hq, int hkv, int L, int D) {
+  if (B < 1 || hq < 1 || hkv < 1 || L < 1 || D < 1 || hq % hkv) return 0;
+  return decode_attention_workspace_bytes(B, hq, hkv, L, D);
+}
+
+int cd_decode_attention(const void* q, long long q_stride_b, const void* k, const void* v,
+                        long long kv_stride_b, long long kv_stride_h, long long kv_stride_t,
+                        const void* mask, long long mask_stride_b, float scale, int B, int hq,
+                        int hkv, int L, int D, void* out, void* ws, size_t ws_bytes, void* stream) {
+  if (B < 1 || hq < 1 || hkv < 1 || L < 1 || hq % hkv) return CD_ERR_INVALID;
+  if (D != 64 && D != 128) return CD_ERR_UNSUPPORTED;
+  if (hq / hkv > 4) return CD_ERR_UNSUPPORTED;
+  if (!q || !k || !v || !out || !ws) return CD_ERR_INVALID;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out)) return CD_ERR_INVALID;
+  if ((q_stride_b & 7) || (kv_stride_b & 7) || (kv_stride_h & 7) || (kv_stride_t & 7))
+    return CD_ERR_INVALID;
+  if (ws_bytes < decode_attention_workspace_bytes(B, hq, hkv, L, D)) return CD_ERR_INVALID;
+  cudaError_t e = launch_decode_attention(q, q_stride_b, k, v, kv_stride_b, kv_stride_h,
+                                          kv_stride_t, mask, mask_stride_b, scale, B, hq, hkv, L,
+                                          D, out, ws, as_stream(stream));
+  return e == cudaSuccess ? CD_OK : cuda_fail(e, "decode attention launch");
+}
+
 int cd_gate_up_packed_rows(int I, int block_n) {
-  if (I < 1 || (block_n != 128 && block_n != 256)) return 0;
+  if (I < 1 || (block_n != 32 && block_n != 64 && block_n != 128 && block_n != 256)) return 0;
   const int half = block_n / 2;
   return ((I + half - 1) / half) * block_n;
 }
@@ -162,7 +185,7 @@ int cd_moe_down(const void* h_routed, int I_e, const void* wd_routed, const void
   epi.residual = residual;
   epi.ldr = H;
   return launch_gemm(T, H, E, seg_offsets, op0, h_shared ? &op1 : nullptr, epi,
-                     H > 128 ? 256 : 128, as_stream(stream));
+                     choose_store_block_n(T, H, current_sm_count()), as_stream(stream));
 }
 
 int cd_moe_combine(const void* h_shared, int I_s, const void* wd_shared, const void* routed_sorted,
@@ -187,7 +210,8 @@ int cd_moe_combine(const void* h_shared, int I_s, const void* wd_shared, const v
   epi.ldr = H;
   epi.residual2 = routed_sorted;
   epi.ldr2 = H;
-  return launch_gemm(T, H, 1, nullptr, op0, nullptr, epi, H > 128 ? 256 : 128, as_stream(stream));
+  return launch_gemm(T, H, 1, nullptr, op0, nullptr, epi,
+                     choose_store_block_n(T, H, current_sm_count()), as_stream(stream));
 }
 
 int cd_mu_qkv(const void* x, const void* mu_prev, const void* w, const void* w_mu, void* qkv,
@@ -215,8 +239,8 @@ int cd_mu_qkv(const void* x, const void* mu_prev, const void* w, const void* w_m
   epi.out = qkv;
   epi.ldo = N;
   epi.out_cols = N;
-  return launch_gemm(T, N, 1, nullptr, op0, mu_prev ? &op1 : nullptr, epi, N > 128 ? 256 : 128,
-                     as_stream(stream));
+  return launch_gemm(T, N, 1, nullptr, op0, mu_prev ? &op1 : nullptr, epi,
+                     choose_store_block_n(T, N, current_sm_count()), as_stream(stream));
 }
 
 int cd_mu_proj(const void* h, const void* w, const void* mu_param, float mu_min, float mu_max,
@@ -240,7 +264,8 @@ int cd_mu_proj(const void* h, const void* w, const void* mu_param, float mu_min,
   epi.do_clamp = clamp_out;
   epi.clamp_lo = out_lo;
   epi.clamp_hi = out_hi;
-  return launch_gemm(T, H, 1, nullptr, op0, nullptr, epi, H > 128 ? 256 : 128, as_stream(stream));
+  return launch_gemm(T, H, 1, nullptr, op0, nullptr, epi,
+                     choose_store_block_n(T, H, current_sm_count()), as_stream(stream));
 }
 
 int cd_linear(const void* x, const void* w, const void* residual, void* out, int T, int K, int N,
@@ -260,7 +285,8 @@ int cd_linear(const void* x, const void* w, const void* residual, void* out, int
   epi.out_cols = N;
   epi.residual = residual;
   epi.ldr = N;
-  return launch_gemm(T, N, 1, nullptr, op0, nullptr, epi, N > 128 ? 256 : 128, as_stream(stream));
+  return launch_gemm(T, N, 1, nullptr, op0, nullptr, epi,
+                     choose_store_block_n(T, N, current_sm_count()), as_stream(stream));
 }
 
 }  // extern "C"

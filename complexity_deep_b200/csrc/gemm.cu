@@ -52,7 +52,7 @@ bool make_map(CUtensorMap* m, const void* base, long long rows, long long cols, 
 
 struct DeviceInfo {
   int sm_count = 0;
-  bool attr_set[2][2][2] = {};  // [BN 128/256][epilogue][CTA group 1/2]
+  bool attr_set[4][2][2] = {};  // [BN 32/64/128/256][epilogue][CTA group 1/2]
   int* status = nullptr;
 };
 constexpr int kMaxDevices = 64;
@@ -65,7 +65,7 @@ template <int BN, int EPI, int CG>
 cudaError_t launch_one(int grid, const CUtensorMap& a0, const CUtensorMap& b0,
                        const CUtensorMap& a1, const CUtensorMap& b1, const GemmParams& p,
                        DeviceInfo& di, cudaStream_t stream) {
-  constexpr int bi = (BN == 256) ? 1 : 0;
+  constexpr int bi = (BN == 256) ? 3 : (BN == 128) ? 2 : (BN == 64) ? 1 : 0;
   auto kern = gemm_bf16_sm100_kernel<BN, EPI, CG>;
   constexpr int smem = GemmSmem<BN, CG>::kDynamic;
   if (!di.attr_set[bi][EPI][CG - 1]) {
@@ -95,13 +95,35 @@ cudaError_t launch_any(int block_n, int kind, int grid, const CUtensorMap& a0,
   if (block_n == 256)
     return kind == kEpiSwiGLU ? launch_one<256, kEpiSwiGLU, CG>(grid, a0, b0, a1, b1, p, di, stream)
                               : launch_one<256, kEpiStore, CG>(grid, a0, b0, a1, b1, p, di, stream);
-  return kind == kEpiSwiGLU ? launch_one<128, kEpiSwiGLU, CG>(grid, a0, b0, a1, b1, p, di, stream)
-                            : launch_one<128, kEpiStore, CG>(grid, a0, b0, a1, b1, p, di, stream);
+  if (block_n == 128)
+    return kind == kEpiSwiGLU ? launch_one<128, kEpiSwiGLU, CG>(grid, a0, b0, a1, b1, p, di, stream)
+                              : launch_one<128, kEpiStore, CG>(grid, a0, b0, a1, b1, p, di, stream);
+  // narrow tiles: few rows (decode), single-CTA only
+  if constexpr (CG == 1) {
+    if (block_n == 64)
+      return kind == kEpiSwiGLU ? launch_one<64, kEpiSwiGLU, 1>(grid, a0, b0, a1, b1, p, di, stream)
+                                : launch_one<64, kEpiStore, 1>(grid, a0, b0, a1, b1, p, di, stream);
+    if (block_n == 32)
+      return kind == kEpiSwiGLU ? launch_one<32, kEpiSwiGLU, 1>(grid, a0, b0, a1, b1, p, di, stream)
+                                : launch_one<32, kEpiStore, 1>(grid, a0, b0, a1, b1, p, di, stream);
+  }
+  return cudaErrorInvalidValue;
 }
 
 // CTA pairs (256-row tiles) pay off once there are enough rows to keep every pair busy; small
 // row counts keep 128-row tiles so more SMs get a tile.  CDEEP_CTA_GROUP=1|2 forces a choice
 // (tuning aid).
+// Accumulator-tile width for the store epilogue: the widest tile that still gives (almost)
+// every SM a tile.  With few rows (decode) the GEMM streams weights and is HBM-bound, so
+// narrow tiles spread the weight stream over all SMs.
+int store_block_n_impl(int M, int N, int sm_count) {
+  const long long m_tiles = (M + kBlockM - 1) / kBlockM;
+  for (int bn : {256, 128, 64}) {
+    if (m_tiles * ((N + bn - 1) / bn) * 4 >= 3LL * sm_count) return bn;
+  }
+  return 32;
+}
+
 int choose_cta_group(int M, int block_n, int sm_count) {
   static const int forced = [] {
     const char* e = getenv("CDEEP_CTA_GROUP");
@@ -143,6 +165,14 @@ static DeviceInfo* device_info(int* status_out) {
   return &di;
 }
 
+int choose_store_block_n(int M, int N, int sm_count) { return store_block_n_impl(M, N, sm_count); }
+
+int current_sm_count() {
+  int st;
+  DeviceInfo* di = device_info(&st);
+  return di ? di->sm_count : 148;
+}
+
 int* device_status_word() {
   int st;
   DeviceInfo* di = device_info(&st);
@@ -153,7 +183,7 @@ int launch_gemm(int M, int N, int num_groups, const int* seg_offsets, const Gemm
                 const GemmOperand* op1, const GemmEpilogueArgs& epi, int block_n,
                 cudaStream_t stream) {
   if (M < 0 || N <= 0 || num_groups < 1 || num_groups > kMaxGroups) return CD_ERR_INVALID;
-  if (block_n != 128 && block_n != 256) return CD_ERR_INVALID;
+  if (block_n != 32 && block_n != 64 && block_n != 128 && block_n != 256) return CD_ERR_INVALID;
   if (num_groups > 1 && !seg_offsets) return CD_ERR_INVALID;
   if (op0.K <= 0 || (op0.K & 7) || (op0.lda & 7) || (op0.ldb & 7)) return CD_ERR_INVALID;
   if (op1 && (op1->K <= 0 || (op1->K & 7) || (op1->lda & 7) || (op1->ldb & 7)))

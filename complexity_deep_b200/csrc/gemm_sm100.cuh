@@ -73,7 +73,9 @@ struct GemmSmem {
   static constexpr int kABytes = kBlockM * kBlockK * 2;
   static constexpr int kBBytes = (BN / CG) * kBlockK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = (kStageBytes > 32768) ? 4 : 6;
+  // as many stages as fit in 192 KB (4 x 48 KB, 6 x 32 KB, 8 x 24 KB, 9 x 20 KB): narrow tiles
+  // run with few rows, where the K loop is bound by load latency, not bandwidth
+  static constexpr int kStages = (196608 / kStageBytes) > 12 ? 12 : (196608 / kStageBytes);
   static constexpr int kTileBytes = kStages * kStageBytes;
   // after the tiles: epilogue staging (4 warps x 2 buffers), barriers, TMEM base, abort
   // flag, schedule tables
@@ -152,7 +154,8 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
   const int tile0 = blockIdx.x / CG;               // both CTAs of a pair walk the same tiles
   const int tstride = gridDim.x / CG;
   constexpr uint32_t kTmemCols = 2 * BN;  // two accumulators of BN fp32 columns
-  static_assert(kTmemCols == 256 || kTmemCols == 512, "TMEM allocation must be a power of two");
+  static_assert(kTmemCols == 64 || kTmemCols == 128 || kTmemCols == 256 || kTmemCols == 512,
+                "TMEM allocation must be a power of two >= 32");
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -360,12 +363,13 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
       const int ocol_span = (EPI == kEpiStore) ? BN : BN / 2;
       const int ocols = min(ocol_span, p.out_cols - ocol_base);
       const int nsub = (ocols + kEpiCols - 1) / kEpiCols;
+      const int col_end = ocol_base + ocols;   // one past the last output column of this tile
       const bool has_res = (EPI == kEpiStore) && p.residual != nullptr;
 
       auto fetch_residual = [&](int sub) {
         uint8_t* buf = stage0 + (sub & 1) * kEpiStageBytes;
         const int col = ocol_base + sub * kEpiCols + cchunk * 8;
-        if (col < p.out_cols) {
+        if (col < col_end) {
 #pragma unroll
           for (int it = 0; it < 8; ++it) {
             if ((cvalid >> it) & 1u) {
@@ -406,7 +410,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
           if (res2_row) {
 #pragma unroll
             for (int q = 0; q < 8; ++q)
-              if (col0 + q * 8 < p.out_cols) r2[q] = ld_nc_v4(res2_row + col0 + q * 8);
+              if (col0 + q * 8 < col_end) r2[q] = ld_nc_v4(res2_row + col0 + q * 8);
           }
           uint32_t v[64];
           tmem_ld32(t_row + sub * 64, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
@@ -423,7 +427,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
 #pragma unroll
             for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[q * 8 + j]);
             uint8_t* slot = buf + own_off + ((q ^ (lane & 7)) << 4);
-            if (col < p.out_cols) {
+            if (col < col_end) {
               if (p.bias) {
                 const uint4 b = *reinterpret_cast<const uint4*>(p.bias + col);
                 const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
@@ -465,8 +469,11 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
         } else {
           // SwiGLU: accumulator columns [0, BN/2) hold gate, [BN/2, BN) hold up, for output
           // columns (n0 / 2) .. (n0 / 2) + BN / 2; 32 output columns per TMEM round trip.
+          // narrow tiles (BN / 2 <= 32 output columns) need a single round trip; columns read
+          // past the tile's own are never stored
+          constexpr int kHalves = (BN / 2 > 32) ? 2 : 1;
 #pragma unroll
-          for (int half = 0; half < 2; ++half) {
+          for (int half = 0; half < kHalves; ++half) {
             uint32_t g[32], u[32];
             tmem_ld32(t_row + sub * 64 + half * 32, g);
             tmem_ld32(t_row + BN / 2 + sub * 64 + half * 32, u);
@@ -490,7 +497,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
         // coalesced copy-out: 4 rows x 128 bytes per warp instruction
         {
           const int col = col0 + cchunk * 8;
-          if (col < p.out_cols) {
+          if (col < col_end) {
 #pragma unroll
             for (int it = 0; it < 8; ++it) {
               if ((cvalid >> it) & 1u) {

@@ -19,6 +19,13 @@ cudaError_t launch_qk_norm_rope(void* qkv, const void* q_w, const void* k_w, con
                                 const float* sin_t, float eps, int T, int S, int pos0, int hq,
                                 int hkv, int D, cudaStream_t stream);
 
+size_t decode_attention_workspace_bytes(int B, int hq, int hkv, int L, int D);
+cudaError_t launch_decode_attention(const void* q, long long q_stride_b, const void* k,
+                                    const void* v, long long kv_stride_b, long long kv_stride_h,
+                                    long long kv_stride_t, const void* mask,
+                                    long long mask_stride_b, float scale, int B, int hq, int hkv,
+                                    int L, int D, void* out, void* ws, cudaStream_t stream);
+
 // One operand pair of the GEMM: row-major bf16 matrices with K contiguous.
 struct GemmOperand {
   const void* a;   // [M, K], leading dimension lda
@@ -51,6 +58,8 @@ int launch_gemm(int M, int N, int num_groups, const int* seg_offsets, const Gemm
                 const GemmOperand* op1, const GemmEpilogueArgs& epi, int block_n,
                 cudaStream_t stream);
 
+int choose_store_block_n(int M, int N, int sm_count);  // needs the current device's SM count
+int current_sm_count();
 int* device_status_word();  // per-device word the kernels raise when a bounded wait ran out
 
 extern thread_local char g_cuda_err[256];        // text behind cd_last_cuda_error()

@@ -198,15 +198,52 @@ def qk_norm_rope_(qkv: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Optional[
     return qkv
 
 
+def decode_attention(qkv: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                     mask: Optional[torch.Tensor], hq: int, hkv: int, head_dim: int
+                     ) -> torch.Tensor:
+    """Single-query attention: qkv [B, (hq + 2 hkv) * D] (its q columns are used), k / v
+    [B, hkv, L, D] views of the cache (any batch / head / token strides, D contiguous),
+    mask None or a bf16 additive mask viewable as [B or 1, L].  Returns [B, hq * D]."""
+    lib = _lib.load()
+    B, D = qkv.shape[0], head_dim
+    L = k.shape[2]
+    for t, name in ((qkv, "qkv"), (k, "k cache"), (v, "v cache")):
+        if not t.is_cuda or t.dtype != BF16 or t.stride(-1) != 1:
+            raise RuntimeError(f"{name}: expected a CUDA bf16 tensor with a contiguous last dim")
+    if tuple(k.shape) != (B, hkv, L, D) or tuple(v.shape) != (B, hkv, L, D):
+        raise RuntimeError("cache shapes do not match")
+    if k.stride() != v.stride():
+        raise RuntimeError("k and v caches must share their strides")
+    mptr, mstride = None, 0
+    if mask is not None:
+        m2 = mask.reshape(-1, L)
+        if m2.dtype != BF16 or not m2.is_cuda or m2.stride(1) != 1 or m2.shape[0] not in (1, B):
+            raise RuntimeError("mask: expected a CUDA bf16 additive mask of shape [B or 1, 1, 1, L]")
+        mptr, mstride = m2.data_ptr(), (m2.stride(0) if m2.shape[0] == B else 0)
+    ws_bytes = lib.cd_decode_attention_workspace_bytes(B, hq, hkv, L, D)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=qkv.device)
+    out = torch.empty(B, hq * D, dtype=BF16, device=qkv.device)
+    with _Span("decode_attention", 2):
+        _lib.check(lib.cd_decode_attention(
+            qkv.data_ptr(), qkv.stride(0), k.data_ptr(), v.data_ptr(), k.stride(0), k.stride(1),
+            k.stride(2), mptr, mstride, float(head_dim) ** -0.5, B, hq, hkv, L, D, out.data_ptr(),
+            ws.data_ptr(), ws_bytes, _stream()), "cd_decode_attention")
+    return out
+
+
 # --------------------------------------------------------------------------- weights
-def choose_block_n(width: int) -> int:
+def choose_block_n(width: int, rows: Optional[int] = None) -> int:
     """Accumulator-tile width for the SwiGLU up-projection of an expert `width` wide.
 
-    256 (128 gate + 128 up columns per tile) unless padding `width` to a multiple of 128
-    would waste more than a quarter of the tile columns; then 128 (64 + 64).  Measured on
-    B200 at width 704 (padded to 768, 9 % waste): 1146 TFLOP/s with 256-wide tiles against
-    672 TFLOP/s with 128-wide ones, which are bound by shared-memory bandwidth.
+    Many rows (prefill): 256 (128 gate + 128 up columns per tile) unless padding `width` to a
+    multiple of 128 would waste more than a quarter of the tile columns; then 128 (64 + 64).
+    Measured on B200 at width 704 (padded to 768, 9 % waste): 1146 TFLOP/s with 256-wide tiles
+    against 672 TFLOP/s with 128-wide ones, which are bound by shared-memory bandwidth.
+    Few rows (decode, `rows` <= 512): the GEMM only streams weights, so 32-wide tiles
+    (16 + 16) spread that stream over as many SMs as possible.
     """
+    if rows is not None and rows <= 512:
+        return 32
     padded = -(-width // 128) * 128
     return 256 if (padded - width) / width <= 0.25 else 128
 

@@ -104,6 +104,22 @@ int cd_qk_norm_rope(void* qkv, const void* q_w, const void* k_w, const float* co
                     const float* sin_t, float eps, int T, int S, int pos0, int hq, int hkv, int D,
                     void* stream);
 
+/* ---- single-query attention over a KV cache (decode) ---------------------------------------
+ * Replaces, for q_len == 1, complexity_deep/core/attention.py:163-177 (repeat_interleave of the
+ * KV heads + scaled_dot_product_attention with an additive mask):
+ *   out[b, h, :] = softmax(scale * q[b, h] . K[b, h / G]^T + mask[b]) V[b, h / G],  G = hq / hkv
+ * q: row b at q + b * q_stride_b, heads contiguous [hq, D] (the q columns of the fused
+ * projection buffer).  k, v: element strides (batch, kv head, token), D contiguous — the
+ * cache is read in place, whatever buffer it lives in.  mask: bf16 additive [B, L] with row
+ * stride mask_stride_b (0 = one row for all), or NULL.  out: [B, hq * D] bf16.
+ * ws: cd_decode_attention_workspace_bytes(...) bytes.  D is 64 or 128, G <= 4; all strides
+ * multiples of 8 elements. */
+size_t cd_decode_attention_workspace_bytes(int B, int hq, int hkv, int L, int D);
+int cd_decode_attention(const void* q, long long q_stride_b, const void* k, const void* v,
+                        long long kv_stride_b, long long kv_stride_h, long long kv_stride_t,
+                        const void* mask, long long mask_stride_b, float scale, int B, int hq,
+                        int hkv, int L, int D, void* out, void* ws, size_t ws_bytes, void* stream);
+
 /* ---- expert up-projection with fused SwiGLU ---------------------------------------------
  * Replaces gate/up GEMMs and silu(gate)*up of the routed experts
  * (token_routed_mlp.py:171-173) or, with num_groups = 1 and seg_offsets = NULL, of the
@@ -113,7 +129,8 @@ int cd_qk_norm_rope(void* qkv, const void* q_w, const void* k_w, const float* co
  * packed_w: [num_groups, cd_gate_up_packed_rows(I, block_n), H] — per group, for each tile
  *   of block_n/2 output columns, block_n/2 gate rows followed by block_n/2 up rows (each
  *   row = one output feature, H contiguous), zero rows padding the last tile.
- * h: [T, I].  block_n is 128 or 256.  H % 8 == 0, I % 8 == 0. */
+ * h: [T, I].  block_n is 32, 64, 128 or 256 (narrow tiles for few rows: more CTAs share the
+ * weight stream).  H % 8 == 0, I % 8 == 0. */
 int cd_gate_up_packed_rows(int I, int block_n);
 int cd_moe_up(const void* x_sorted, const int32_t* seg_offsets, int num_groups,
               const void* packed_w, void* h, int T, int H, int I, int block_n, void* stream);

@@ -45,3 +45,4 @@ def test_argument_checks_need_no_gpu():
     assert lib.cd_route(None, None, 0, 8, 16, None, None, None, None, None, None, 0, None) == 1
     assert lib.cd_linear(None, None, None, None, 16, 12, 64, None) == 1      # K % 8 != 0
     assert lib.cd_moe_up(None, None, 1, None, None, 16, 64, 48, 100, None) == 1  # block_n
+    assert lib.cd_gate_up_packed_rows(704, 32) == 1408

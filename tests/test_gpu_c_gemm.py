@@ -100,7 +100,8 @@ def _swiglu_ref(x, gate, up):
 
 @pytest.mark.parametrize("T,H,I,bn", [(128, 64, 128, 256), (200, 128, 64, 128), (77, 256, 40, 128),
                                       (1000, 768, 512, 256), (512, 2048, 704, 128),
-                                      (512, 2048, 704, 256), (300, 512, 200, 256)])
+                                      (512, 2048, 704, 256), (300, 512, 200, 256),
+                                      (32, 2048, 704, 32), (200, 256, 72, 64), (8, 64, 16, 32)])
 def test_moe_up_dense(T, H, I, bn):
     from complexity_deep_b200 import ops
     g = torch.Generator().manual_seed(11)
@@ -124,7 +125,8 @@ def _segments(g, T, E, empty=()):
 
 @pytest.mark.parametrize("T,H,I,E,bn,empty", [(300, 64, 64, 4, 128, ()), (1000, 128, 136, 8, 256, (2,)),
                                               (4096, 768, 512, 4, 256, ()), (517, 256, 72, 32, 128, (0, 31)),
-                                              (129, 64, 64, 4, 128, (1, 2, 3))])
+                                              (129, 64, 64, 4, 128, (1, 2, 3)),
+                                              (256, 256, 88, 8, 32, (3,)), (40, 128, 48, 4, 64, ())])
 def test_moe_up_grouped_ragged(T, H, I, E, bn, empty):
     from complexity_deep_b200 import ops
     g = torch.Generator().manual_seed(13)

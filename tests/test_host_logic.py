@@ -132,6 +132,7 @@ def test_pack_gate_up_layout():
     assert torch.equal(packed2[0, 384:384 + 72], 2 * gate2[0, 128:])
     assert ops.choose_block_n(5632) == 256 and ops.choose_block_n(704) == 256
     assert ops.choose_block_n(64) == 128 and ops.choose_block_n(48) == 128
+    assert ops.choose_block_n(704, rows=256) == 32 and ops.choose_block_n(704, rows=4096) == 256
     assert ops.choose_block_n(2816) == 256 and ops.choose_block_n(512) == 256
 
 
