@@ -207,7 +207,7 @@ qk_norm_rope_kernel(__nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __rest
 // lane groups take adjacent heads, and every lane walks over heads with the SAME column
 // chunk, so the cos/sin values of the token's position are loaded once and reused for all
 // its heads.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 qk_norm_rope_vec_kernel(__nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ q_w,
                         const __nv_bfloat16* __restrict__ k_w, const float* __restrict__ cos_t,
                         const float* __restrict__ sin_t, float eps, int T, int S, int pos0, int hq,
@@ -238,28 +238,19 @@ qk_norm_rope_vec_kernel(__nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __
       s2[4 * v] = d.x; s2[4 * v + 1] = d.y; s2[4 * v + 2] = d.z; s2[4 * v + 3] = d.w;
     }
   }
-  // norm weights of this lane's columns (q and k heads use different weights)
-  float wq1[8], wq2[8], wk1[8], wk2[8];
+  // norm weights of this lane's columns, kept packed (q and k heads use different weights)
+  uint4 wq1 = make_uint4(0, 0, 0, 0), wq2 = wq1, wk1 = wq1, wk2 = wq1;
   if (q_w) {
-    const uint4 a = *reinterpret_cast<const uint4*>(q_w + j);
-    const uint4 b = *reinterpret_cast<const uint4*>(q_w + half + j);
-    const uint4 c = *reinterpret_cast<const uint4*>(k_w + j);
-    const uint4 d = *reinterpret_cast<const uint4*>(k_w + half + j);
-    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
-    const uint32_t cw[4] = {c.x, c.y, c.z, c.w}, dw[4] = {d.x, d.y, d.z, d.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      wq1[2 * i] = lo_f(aw[i]); wq1[2 * i + 1] = hi_f(aw[i]);
-      wq2[2 * i] = lo_f(bw[i]); wq2[2 * i + 1] = hi_f(bw[i]);
-      wk1[2 * i] = lo_f(cw[i]); wk1[2 * i + 1] = hi_f(cw[i]);
-      wk2[2 * i] = lo_f(dw[i]); wk2[2 * i + 1] = hi_f(dw[i]);
-    }
+    wq1 = *reinterpret_cast<const uint4*>(q_w + j);
+    wq2 = *reinterpret_cast<const uint4*>(q_w + half + j);
+    wk1 = *reinterpret_cast<const uint4*>(k_w + j);
+    wk2 = *reinterpret_cast<const uint4*>(k_w + half + j);
   }
   const int ld = (hq + 2 * hkv) * D;
   __nv_bfloat16* row = qkv + static_cast<size_t>(t) * ld;
   // All loads of the token are issued before any arithmetic (up to kMaxIter heads per lane
   // group) so enough bytes are in flight to cover HBM latency.
-  constexpr int kMaxIter = 8;
+  constexpr int kMaxIter = 3;
   for (int hb = 0; hb < heads; hb += groups * kMaxIter) {   // uniform trip count across the warp
     uint4 a[kMaxIter], b[kMaxIter];
 #pragma unroll
@@ -292,11 +283,12 @@ qk_norm_rope_vec_kernel(__nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __
       if (!active) continue;
       if (q_w) {
         const float rstd = rsqrtf(ss / static_cast<float>(D) + eps);
-        const bool is_q = h < hq;
+        const uint4 w1 = (h < hq) ? wq1 : wk1, w2 = (h < hq) ? wq2 : wk2;
+        const uint32_t w1w[4] = {w1.x, w1.y, w1.z, w1.w}, w2w[4] = {w2.x, w2.y, w2.z, w2.w};
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          x1[e] *= rstd * (is_q ? wq1[e] : wk1[e]);
-          x2[e] *= rstd * (is_q ? wq2[e] : wk2[e]);
+        for (int e = 0; e < 4; ++e) {
+          x1[2 * e] *= rstd * lo_f(w1w[e]); x1[2 * e + 1] *= rstd * hi_f(w1w[e]);
+          x2[2 * e] *= rstd * lo_f(w2w[e]); x2[2 * e + 1] *= rstd * hi_f(w2w[e]);
         }
       }
       float o1[8], o2[8];

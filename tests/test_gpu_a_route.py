@@ -60,7 +60,7 @@ def test_empty_batch_and_empty_experts():
 
 
 def test_full_size_config5_properties():
-    """BASELINE config 5 size (T=65536, V=100000, E=32): compared with the oracle and through
+    """The expert-parallel layer's size (T=65536, V=100000, E=32): compared with the oracle and through
     size-independent properties (permutation validity, sortedness, stability)."""
     V, E, T = 100000, 32, 65536
     ids = oracle.zipf_token_ids(V, 1.0, T).numpy()

@@ -144,7 +144,7 @@ def test_dense_swiglu_block():
 
 
 def test_isolated_layer_config2_shape_sampled_rows():
-    """BASELINE's isolated-layer configuration (T=16384, H=2048, 8 experts + shared of width
+    """The isolated-layer configuration (T=16384, H=2048, 8 experts + shared of width
     5632, Zipf ids, bin-packed table).  The layer is row-independent, so the oracle is run on
     a sample of rows with their token ids; the stated tolerance is asserted as written."""
     import complexity_deep_b200 as cd

@@ -64,7 +64,7 @@ def test_generate_greedy_runs_and_extends():
 
 @torch.no_grad()
 def test_readme_model_shape_logits():
-    """BASELINE's first configuration at reduced depth/batch so the fp32 oracle runs in
+    """The README-model configuration at reduced depth/batch so the fp32 oracle runs in
     seconds: hidden 768, 12 Q / 4 KV heads (D 64), intermediate 2048, 4 experts + shared,
     vocab 32000, Zipf ids, bin-packed table; 3 layers, 2 x 256 tokens."""
     from complexity_deep_b200.models import ComplexityConfig, ComplexityModel
