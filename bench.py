@@ -364,9 +364,14 @@ def run_layer(args):
         for lin in (mlp.shared_gate, mlp.shared_up, mlp.shared_down):
             nn.init.normal_(lin.weight, 0.0, 0.02)
     mlp = mlp.to(torch.bfloat16).eval()
+    table = TokenRoutedMLP._build_token_mapping(V, E, p)
     with torch.no_grad():
-        mlp.token_to_expert.copy_(TokenRoutedMLP._build_token_mapping(V, E, p))
-    ep = ExpertParallelMoE(mlp) if args.workload == "ep_layer" else None
+        mlp.token_to_expert.copy_(table)
+    ep = None
+    if args.workload == "ep_layer":
+        # expected rows per expert from the token frequencies, for the balanced placement
+        load = torch.bincount(table, weights=p.double(), minlength=E)
+        ep = ExpertParallelMoE(mlp, expert_load=load if args.ep_placement == "balanced" else None)
     steps_total = args.warmup + args.steps
     gen = torch.Generator(device=dev).manual_seed(1 + rank)
     x = torch.randn(t_loc, H, device=dev, generator=gen).to(torch.bfloat16)
@@ -422,7 +427,7 @@ def run_layer(args):
     pk = peaks()
     received = None
     if ep is not None:
-        rows = torch.tensor([ep.plan_for(mlp.routing(ids[-1].view(1, t_loc)))[0].received],
+        rows = torch.tensor([ep.plan_for(ep.routing(ids[-1].view(1, t_loc)))[0].received],
                             device=dev)
         gathered = [torch.empty_like(rows) for _ in range(world)]
         dist.all_gather(gathered, rows)
@@ -436,7 +441,8 @@ def run_layer(args):
         "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "b200",
         "config": {"workload": args.workload, **{k: v for k, v in cfg.items()},
-                   "parallelism": (f"ep{world}: {E // world} experts per GPU, tokens dp{world}"
+                   "parallelism": (f"ep{world}: {E // world} experts per GPU ({args.ep_placement} "
+                                   f"placement), tokens dp{world}"
                                    if ep is not None else "1 GPU"),
                    "tokens_per_gpu": t_loc, "flop_per_step": flop},
         "tokens_per_s": round(T * args.steps / (ms / 1e3), 1),
@@ -567,6 +573,8 @@ def main():
     ap.add_argument("--cpu-tokens", type=int, default=1024,
                     help="tokens of the bounded CPU sample (one sequence)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ep-placement", default="balanced", choices=["balanced", "contiguous"],
+                    help="ep_layer: which experts share a GPU")
     ap.add_argument("--cache-len", type=int, default=4096, help="decode_1b: prefilled KV tokens")
     ap.add_argument("--workload", default="prefill_1b", choices=["prefill_1b", "decode_1b"] + list(LAYER_CONFIGS),
                     help="prefill_1b is the headline; the layer modes report MoE-layer TFLOP/s")

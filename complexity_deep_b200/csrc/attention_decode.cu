@@ -192,7 +192,7 @@ decode_attn_combine_kernel(const float* __restrict__ part_acc, const float* __re
 
 int choose_splits(int B, int hkv, int L) {
   const int pairs = B * hkv;
-  int splits = (4 * 148 + pairs - 1) / pairs;       // aim at ~4 blocks per SM
+  int splits = (16 * 148 + pairs - 1) / pairs;      // several waves of blocks: small tail
   const int max_splits = (L + 255) / 256;           // at least 256 rows per block
   if (splits > max_splits) splits = max_splits;
   if (splits < 1) splits = 1;

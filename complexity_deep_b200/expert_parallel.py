@@ -68,6 +68,29 @@ def exchange_plan(counts: np.ndarray, rank: int, experts_per_rank: int) -> Excha
                         seg_offsets.astype(np.int32), gather_idx.astype(np.int32))
 
 
+def balanced_placement(expert_load, world: int) -> List[int]:
+    """Longest-processing-time placement: experts in order of decreasing load each go to the
+    rank with the smallest load so far that still has a free slot (E / world slots per rank).
+
+    Returns `order`, a permutation of the expert ids: rank r owns ``order[r*El:(r+1)*El]``.
+    The Zipf head token makes one expert much heavier than the mean and bin-packing cannot
+    split a token, so with contiguous placement one GPU gets the two heaviest experts; this
+    spreads them.
+    """
+    load = [float(v) for v in expert_load]
+    E = len(load)
+    if E % world:
+        raise ValueError(f"{E} experts cannot be split evenly over {world} ranks")
+    El = E // world
+    slots: List[List[int]] = [[] for _ in range(world)]
+    totals = [0.0] * world
+    for e in sorted(range(E), key=lambda i: (-load[i], i)):
+        r = min((r for r in range(world) if len(slots[r]) < El), key=lambda r: (totals[r], r))
+        slots[r].append(e)
+        totals[r] += load[e]
+    return [e for r in range(world) for e in sorted(slots[r])]
+
+
 class ExpertParallelMoE:
     """Sharded runner for one ``TokenRoutedMLP``.
 
@@ -76,7 +99,11 @@ class ExpertParallelMoE:
     full routed weights can be freed by the caller afterwards.
     """
 
-    def __init__(self, mlp: TokenRoutedMLP, group: Optional[dist.ProcessGroup] = None):
+    def __init__(self, mlp: TokenRoutedMLP, group: Optional[dist.ProcessGroup] = None,
+                 expert_load=None):
+        """`expert_load` (one number per expert, e.g. the summed token frequencies of its
+        tokens, identical on every rank) switches from contiguous placement (expert e on rank
+        e // El) to `balanced_placement`."""
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
@@ -84,16 +111,43 @@ class ExpertParallelMoE:
         E = mlp.num_experts
         if E % self.world:
             raise ValueError(f"{E} experts cannot be split evenly over {self.world} ranks")
-        self.experts_per_rank = E // self.world
-        lo, hi = self.rank * self.experts_per_rank, (self.rank + 1) * self.experts_per_rank
+        self.experts_per_rank = El = E // self.world
+        # order[new id] = original expert id; rank r owns new ids r*El .. (r+1)*El - 1
+        order = list(range(E)) if expert_load is None else balanced_placement(expert_load, self.world)
+        self.order = order
+        mine = torch.tensor(order[self.rank * El:(self.rank + 1) * El],
+                            device=mlp.gate_proj_w.device)
         I_e = mlp.expert_intermediate_size
         self.block_n = ops.choose_block_n(I_e)
         with torch.no_grad():
-            self.packed_local = ops.pack_gate_up(mlp.gate_proj_w.detach()[lo:hi].transpose(1, 2),
-                                                 mlp.up_proj_w.detach()[lo:hi].transpose(1, 2),
-                                                 self.block_n)
-            self.down_local = mlp.down_proj_w.detach()[lo:hi].transpose(1, 2).contiguous()
+            self.packed_local = ops.pack_gate_up(
+                mlp.gate_proj_w.detach().index_select(0, mine).transpose(1, 2),
+                mlp.up_proj_w.detach().index_select(0, mine).transpose(1, 2), self.block_n)
+            self.down_local = mlp.down_proj_w.detach().index_select(0, mine).transpose(1, 2).contiguous()
+        self._relabel = None
+        if expert_load is not None:
+            new_of_old = [0] * E
+            for new, old in enumerate(order):
+                new_of_old[old] = new
+            self._relabel = torch.tensor(new_of_old, dtype=torch.long)
+        self._table = None
+        self._table_key = None
         self._plans = {}
+
+    def routing(self, token_ids: torch.Tensor) -> ops.Routing:
+        """Dispatch with expert ids renumbered so that every rank's experts are contiguous."""
+        if self._relabel is None:
+            return self.mlp.routing(token_ids)
+        from .core.token_routed_mlp import ROUTING_CACHE
+        sig = self.mlp._table_signature()
+        if self._table_key != sig:
+            t = self.mlp.token_to_expert
+            self._table = self._relabel.to(t.device)[t]
+            self._table_key = sig
+        if token_ids.dtype != torch.int64:
+            token_ids = token_ids.long()
+        return ROUTING_CACHE.lookup(token_ids, self._table, ("ep", tuple(self.order)) + sig,
+                                    self.mlp.num_experts)
 
     # ------------------------------------------------------------------ plan
     def plan_for(self, routing: ops.Routing):
@@ -155,7 +209,7 @@ class ExpertParallelMoE:
         """Drop-in for ``TokenRoutedMLP.forward`` on this rank's tokens."""
         shape = hidden_states.shape
         H = shape[-1]
-        routing = self.mlp.routing(token_ids)
+        routing = self.routing(token_ids)
         x_sorted = ops.gather_rows(hidden_states.reshape(-1, H).contiguous(), routing.perm)
         return self.forward_sorted(x_sorted, routing, None).view(shape)
 

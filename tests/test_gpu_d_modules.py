@@ -175,3 +175,41 @@ def test_isolated_layer_config2_shape_sampled_rows():
     # size-independent property over ALL rows: rows with the same id and the same input get the
     # same output, and the un-permutation is a bijection (no row left unwritten / NaN)
     assert torch.isfinite(out).all()
+
+
+def test_prefill_layer_full_size_row_permutation_equivariance():
+    """The 1B prefill layer at its full per-GPU size (T = 65 536 rows, H 2048, 8 experts of
+    width 704 + shared): the layer acts on rows independently, so permuting the (row, token id)
+    pairs must permute the output rows — a size-independent check of dispatch, ragged grouped
+    GEMMs and the un-permuting epilogue; plus sampled rows against the oracle."""
+    import complexity_deep_b200 as cd
+    from complexity_deep_b200 import ops
+    T, H, E, I_e, V = 65536, 2048, 8, 704, 32000
+    g = torch.Generator().manual_seed(0)
+    p = oracle.zipf_probabilities(V, 1.1).float()
+    table = torch.from_numpy(oracle.build_token_mapping(V, E, p))
+    ids = oracle.zipf_token_ids(V, 1.1, T)
+    with torch.device("cuda"):
+        mlp = cd.TokenRoutedMLP(H, I_e * E, E, V, True, None).to(BF).eval()
+    sd = {}
+    with torch.no_grad():
+        for name, prm in mlp.named_parameters():
+            w = (torch.randn(prm.shape, generator=g) * 0.02).to(BF)
+            prm.copy_(w)
+            sd[name] = w.float()
+        mlp.token_to_expert.copy_(table)
+    sd["token_to_expert"] = table
+    x = torch.randn(T, H, generator=g).to(BF)
+    xc, ic = x.cuda(), ids.cuda()
+    out = mlp(xc.view(32, 2048, H), ic.view(32, 2048)).view(T, H)
+    pi = torch.randperm(T, generator=g).cuda()
+    out_p = mlp(xc[pi].view(32, 2048, H), ic[pi].view(32, 2048)).view(T, H)
+    ops.status_fetch()
+    assert torch.isfinite(out).all()
+    diff = (out_p.float() - out[pi].float()).abs().max().item()
+    assert diff <= 1e-2 * out.float().abs().max().item(), diff
+    rows = torch.randperm(T, generator=g)[:256]
+    ref = oracle.token_routed_mlp(sd, "", x[rows].float()[None], ids[rows][None])[0]
+    mr, ma = oracle.error_metrics(out[rows.cuda()].float().cpu(), ref)
+    rms = float(ref.pow(2).mean().sqrt())
+    assert mr <= 2e-2 and ma <= 2e-3 * max(1.0, rms), (mr, ma, rms)

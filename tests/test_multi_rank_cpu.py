@@ -106,3 +106,17 @@ def test_exchange_plan_rejects_uneven_split_and_handles_empty():
     plan1 = exchange_plan(np.array([[0, 0, 5, 0], [0, 0, 0, 2]]), 1, 2)
     assert plan1.received == 7 and plan1.seg_offsets.tolist() == [0, 5, 7]
     assert plan1.gather_idx.tolist() == [0, 1, 2, 3, 4, 5, 6]
+
+
+def test_balanced_placement_spreads_heavy_experts():
+    from complexity_deep_b200.expert_parallel import balanced_placement
+    load = [8.3, 4.1] + [2.9] * 30                       # Zipf(1.0) over 32 experts
+    order = balanced_placement(load, 8)
+    assert sorted(order) == list(range(32))
+    per_rank = [sum(load[e] for e in order[r * 4:(r + 1) * 4]) for r in range(8)]
+    assert max(per_rank) <= 8.3 + 3 * 2.9 + 1e-9          # the heaviest expert sits with light ones
+    contiguous = [sum(load[r * 4:(r + 1) * 4]) for r in range(8)]
+    assert max(per_rank) < max(contiguous)
+    owner = {e: i // 4 for i, e in enumerate(order)}
+    assert owner[0] != owner[1]                          # the two heaviest are on different ranks
+    assert balanced_placement([1.0] * 8, 2) == [0, 2, 4, 6, 1, 3, 5, 7]
