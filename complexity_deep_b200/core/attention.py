@@ -110,6 +110,7 @@ class ComplexityAttention(nn.Module):
     # ------------------------------------------------------------------ forward
     def _attend(self, hidden_states, attention_mask, past_key_value, use_cache, mu_prev):
         """Everything up to (not including) o_proj; returns ([T, q_dim], new_kv)."""
+        ops.forward_only(hidden_states, "ComplexityAttention")
         B, S, H = hidden_states.shape
         hq, hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
         x2 = hidden_states.reshape(B * S, H).contiguous()
@@ -132,7 +133,7 @@ class ComplexityAttention(nn.Module):
             v = _kv_append(past_key_value[1], v)
         new_kv = (k, v) if use_cache else None
 
-        if self._decode_kernel_applies(S, attention_mask, k):
+        if self._decode_kernel_applies(S, attention_mask, k, v):
             # one query per sequence: stream the cache once with the library's kernel.  With no
             # mask the reference's is_causal=True is top-left aligned, i.e. only key 0 is seen.
             if attention_mask is None:
@@ -152,8 +153,10 @@ class ComplexityAttention(nn.Module):
             attn = attn.transpose(1, 2).reshape(B * S, hq * D).contiguous()
         return attn, new_kv
 
-    def _decode_kernel_applies(self, S, attention_mask, k) -> bool:
+    def _decode_kernel_applies(self, S, attention_mask, k, v) -> bool:
         if S != 1 or self.head_dim not in (64, 128) or self.num_kv_groups > 4:
+            return False
+        if k.stride() != v.stride() or k.stride(3) != 1 or any(st % 8 for st in k.stride()[:3]):
             return False
         if self.training and self.attention_dropout > 0:
             return False

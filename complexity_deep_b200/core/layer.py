@@ -63,6 +63,7 @@ class MuGuidance(nn.Module):
         nn.init.zeros_(self.mu_proj.weight)
 
     def forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
+        ops.forward_only(hidden_states, "MuGuidance")
         shape = hidden_states.shape
         h2 = hidden_states.reshape(-1, shape[-1]).contiguous()
         return ops.mu_proj(h2, self.mu_proj.weight, self.mu, self.mu_min, self.mu_max).view(shape)
@@ -130,6 +131,7 @@ class TransformerBlock(nn.Module):
         token_ids: Optional[torch.Tensor] = None,
         mu_prev: Optional[torch.Tensor] = None,
     ) -> Tuple[torch.Tensor, Optional[Tuple[torch.Tensor, torch.Tensor]], Optional[torch.Tensor]]:
+        ops.forward_only(hidden_states, "TransformerBlock")
         if self._fusable(token_ids):
             hidden_states, new_kv = self._forward_fused(
                 hidden_states, attention_mask, past_key_value, use_cache, token_ids, mu_prev)

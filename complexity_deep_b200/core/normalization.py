@@ -17,6 +17,7 @@ class RMSNorm(nn.Module):
         self.weight = nn.Parameter(torch.ones(hidden_size))
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        ops.forward_only(x, "RMSNorm")
         return ops.rmsnorm(x.contiguous(), self.weight, self.eps)
 
     def extra_repr(self) -> str:

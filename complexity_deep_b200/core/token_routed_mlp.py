@@ -182,6 +182,7 @@ class TokenRoutedMLP(nn.Module):
 
     def forward(self, hidden_states: torch.Tensor, token_ids: Optional[torch.Tensor] = None
                 ) -> torch.Tensor:
+        ops.forward_only(hidden_states, "TokenRoutedMLP")
         B, S, H = hidden_states.shape
         if token_ids is None:
             return self._forward_all_experts(hidden_states)

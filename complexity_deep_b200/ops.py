@@ -36,6 +36,15 @@ def _need(t: torch.Tensor, name: str, dtype=BF16) -> None:
         raise RuntimeError(f"{name}: expected a contiguous tensor")
 
 
+def forward_only(x: torch.Tensor, what: str) -> None:
+    """The kernels are forward-only.  An activation that carries autograd history would lose
+    its gradient silently, so that case is refused instead."""
+    if torch.is_grad_enabled() and isinstance(x, torch.Tensor) and x.requires_grad:
+        raise RuntimeError(
+            f"{what}: the complexity_deep_b200 kernels implement the forward pass only; call the "
+            "model under torch.no_grad() / torch.inference_mode() (no backward is available)")
+
+
 class _Profile:
     """Optional CUDA-event timing of the GEMM entry points (used by bench.py).
 

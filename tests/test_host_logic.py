@@ -194,3 +194,15 @@ def test_kv_cache_append_in_place_semantics():
     assert torch.equal(c, torch.cat([past, n1, n3], 2))
     assert torch.equal(b, torch.cat([past, n1, n2], 2))            # first branch not clobbered
     assert c._cd_kv.buf.data_ptr() != b._cd_kv.buf.data_ptr()
+
+
+def test_forward_only_is_loud():
+    """An activation with autograd history is refused (no silent loss of gradients)."""
+    x = torch.randn(1, 4, 64, requires_grad=True)
+    with pytest.raises(RuntimeError, match="forward pass only"):
+        cd.RMSNorm(64)(x)
+    with pytest.raises(RuntimeError, match="forward pass only"):
+        cd.TokenRoutedMLP(64, 128, 4, 256)(x, torch.zeros(1, 4, dtype=torch.long))
+    model = create_complexity_model("tiny", vocab_size=64, num_hidden_layers=1)
+    with pytest.raises(RuntimeError, match="forward pass only"):
+        model(torch.zeros(1, 4, dtype=torch.long))          # grad mode: embedding output requires grad
