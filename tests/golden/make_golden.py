@@ -159,6 +159,23 @@ def main():
         "next_ids": nxt, "step_logits": step.logits,
     })
 
+    # ---------------------------------------------------------------- config switches
+    variants = []
+    for flags in (dict(use_mu_guidance=False), dict(use_qk_norm=False), dict(shared_expert=False),
+                  dict(use_token_routed_mlp=False), dict(tie_word_embeddings=False),
+                  dict(num_experts=1)):
+        torch.manual_seed(7)
+        base = dict(vocab_size=48, hidden_size=32, intermediate_size=64, num_hidden_layers=1,
+                    num_attention_heads=2, num_key_value_heads=1, num_experts=2)
+        base.update(flags)
+        vcfg = ComplexityConfig(**base)
+        vm = ComplexityModel(vcfg).eval()
+        vids = zipf_ids(48, 1.1, 12, seed=9).view(2, 6)
+        variants.append({"config": vcfg.to_dict(),
+                         "state": {k: v.clone() for k, v in vm.state_dict().items()},
+                         "input_ids": vids, "logits": vm(vids).logits})
+    save("model_variants.pt", variants)
+
 
 if __name__ == "__main__":
     main()

@@ -98,3 +98,32 @@ def test_readme_model_shape_logits():
     assert mean_abs <= max(2e-3, ref_path_mean), (mean_abs, ref_path_mean)
     agree = (logits.float().cpu().argmax(-1) == ref.argmax(-1)).float().mean()
     assert agree > 0.9
+
+
+@pytest.mark.parametrize("flags", [
+    dict(use_mu_guidance=False), dict(use_qk_norm=False), dict(shared_expert=False),
+    dict(use_token_routed_mlp=False), dict(tie_word_embeddings=False),
+    dict(num_experts=1), dict(num_attention_heads=2, num_key_value_heads=2, hidden_size=256),
+])
+@torch.no_grad()
+def test_config_variants_vs_oracle(flags):
+    """Every switch of ComplexityConfig that changes the forward path, on a small model built by
+    this package's own constructor, against the oracle on the same (bf16-rounded) weights."""
+    from complexity_deep_b200.models import ComplexityConfig, ComplexityModel
+    torch.manual_seed(0)
+    base = dict(vocab_size=300, hidden_size=128, intermediate_size=256, num_hidden_layers=2,
+                num_attention_heads=4, num_key_value_heads=2, num_experts=4)
+    base.update(flags)
+    cfg = ComplexityConfig(**base)
+    model = ComplexityModel(cfg)
+    if cfg.use_mu_guidance:
+        model.mu_init.data.normal_(0, 0.5)
+    sd = {k: (v.to(BF).float() if v.is_floating_point() else v.clone())
+          for k, v in model.state_dict().items()}
+    model = model.to(device="cuda", dtype=BF).eval()
+    ids = oracle.zipf_token_ids(300, 1.1, 48, seed=5).view(3, 16)
+    out = model(ids.cuda(), use_cache=True)
+    ref, ref_kv = oracle.model_forward(sd, cfg.to_dict(), ids, use_cache=True)
+    _close(out.logits, ref)
+    assert len(out.past_key_values) == 2
+    _close(out.past_key_values[1][0], ref_kv[1][0])

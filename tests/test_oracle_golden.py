@@ -127,3 +127,10 @@ def test_model_forward_and_decode_step():
     loss = torch.nn.functional.cross_entropy(logits[:, :-1].reshape(-1, 256),
                                              g["input_ids"][:, 1:].reshape(-1))
     torch.testing.assert_close(loss, g["loss"], **TOL)
+
+
+def test_model_config_switches():
+    """mu guidance off, QK-norm off, no shared expert, dense SwiGLU, untied lm_head, one expert."""
+    for g in load_golden("model_variants.pt"):
+        logits, _ = oracle.model_forward(g["state"], g["config"], g["input_ids"])
+        torch.testing.assert_close(logits, g["logits"], **TOL)
