@@ -409,6 +409,15 @@ def linear(x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = 
     N = w.shape[0]
     if w.shape[1] != K:
         raise RuntimeError("weight does not match x")
+    if N % 8:
+        # rows of the output must stay 16-byte aligned: compute into a padded buffer against
+        # zero-padded weight rows and hand back the first N columns (e.g. an lm_head whose
+        # vocabulary size is not a multiple of 8)
+        if residual is not None:
+            raise RuntimeError("residual with an output width that is not a multiple of 8")
+        pad = 8 - N % 8
+        w_pad = torch.cat([w, w.new_zeros(pad, K)], dim=0)
+        return linear(x, w_pad, None, tag)[:, :N]
     if residual is not None:
         _need(residual, "residual")
         if tuple(residual.shape) != (T, N):

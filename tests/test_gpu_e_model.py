@@ -126,4 +126,6 @@ def test_config_variants_vs_oracle(flags):
     ref, ref_kv = oracle.model_forward(sd, cfg.to_dict(), ids, use_cache=True)
     _close(out.logits, ref)
     assert len(out.past_key_values) == 2
-    _close(out.past_key_values[1][0], ref_kv[1][0])
+    # layer-1 keys: unit-scale values (QK-norm) computed from a bf16 residual stream, so the
+    # rounding of the stream (~2^-9 relative) shows up undamped: mean bound 3 roundings wide
+    _close(out.past_key_values[1][0], ref_kv[1][0], max_rel=2e-2, mean_abs=6e-3)
