@@ -44,6 +44,10 @@ SIGNATURES = {
                                c_int, c_int, c_void_p]),
     "cd_mu_qkv": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                           c_void_p]),
+    "cd_mu_qkv_rope_supported": (c_int, [c_int, c_int, c_int, c_int, c_int]),
+    "cd_mu_qkv_rope": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                               c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int,
+                               c_int, c_int, c_int, c_void_p]),
     "cd_mu_proj": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_float, c_int, c_float, c_float,
                            c_void_p, c_int, c_int, c_void_p]),
     "cd_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),

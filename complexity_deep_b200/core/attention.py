@@ -117,13 +117,12 @@ class ComplexityAttention(nn.Module):
         mu2 = None
         if mu_prev is not None:
             mu2 = mu_prev.reshape(B * S, H).contiguous()  # materialises a broadcast mu_init
-        qkv = ops.mu_qkv(x2, mu2, self._w_qkv(), self._w_mu() if mu2 is not None else None)
-
         past_len = past_key_value[0].shape[2] if past_key_value is not None else 0
         cos, sin = self.rotary_emb.tables_fp32(past_len + S)
-        ops.qk_norm_rope_(qkv, self.q_norm.weight if self.use_qk_norm else None,
-                          self.k_norm.weight if self.use_qk_norm else None, cos, sin, 1e-6, S,
-                          past_len, hq, hkv, D)
+        qkv = ops.mu_qkv_rope(x2, mu2, self._w_qkv(), self._w_mu() if mu2 is not None else None,
+                              self.q_norm.weight if self.use_qk_norm else None,
+                              self.k_norm.weight if self.use_qk_norm else None, cos, sin, 1e-6, S,
+                              past_len, hq, hkv, D)
 
         q = qkv[:, : hq * D].view(B, S, hq, D).transpose(1, 2)
         k = qkv[:, hq * D: (hq + hkv) * D].view(B, S, hkv, D).transpose(1, 2)

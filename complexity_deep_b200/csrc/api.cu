@@ -243,6 +243,56 @@ int cd_mu_qkv(const void* x, const void* mu_prev, const void* w, const void* w_m
                      choose_store_block_n(T, N, current_sm_count()), as_stream(stream));
 }
 
+int cd_mu_qkv_rope_supported(int T, int N, int hq, int hkv, int D) {
+  if (T < 1 || N < 8 || hq < 1 || hkv < 1) return 0;
+  if (D != 128 || N != (hq + 2 * hkv) * D) return 0;
+  if ((hq * D) % 256 || ((hq + hkv) * D) % 256) return 0;     // heads aligned to 256-wide tiles
+  return choose_store_block_n(T, N, current_sm_count()) == 256 ? 1 : 0;
+}
+
+int cd_mu_qkv_rope(const void* x, const void* mu_prev, const void* w, const void* w_mu, void* qkv,
+                   int T, int H, int N, const void* q_w, const void* k_w, const float* cos_t,
+                   const float* sin_t, float eps, int S, int pos0, int hq, int hkv, int D,
+                   void* stream) {
+  if (T < 0 || H < 8 || (H & 7) || N < 8 || (N & 7) || S < 1 || pos0 < 0) return CD_ERR_INVALID;
+  if ((mu_prev == nullptr) != (w_mu == nullptr)) return CD_ERR_INVALID;
+  if ((q_w == nullptr) != (k_w == nullptr) || !cos_t || !sin_t) return CD_ERR_INVALID;
+  if (!aligned16(cos_t) || !aligned16(sin_t) || !aligned16(q_w) || !aligned16(k_w))
+    return CD_ERR_INVALID;
+  if (T > 0 && !cd_mu_qkv_rope_supported(T, N, hq, hkv, D)) return CD_ERR_UNSUPPORTED;
+  GemmOperand op0{};
+  op0.a = x;
+  op0.lda = H;
+  op0.b = w;
+  op0.ldb = H;
+  op0.b_rows = N;
+  op0.K = H;
+  GemmOperand op1{};
+  if (mu_prev) {
+    op1.a = mu_prev;
+    op1.lda = H;
+    op1.b = w_mu;
+    op1.ldb = H;
+    op1.b_rows = N;
+    op1.K = H;
+  }
+  GemmEpilogueArgs epi{};
+  epi.kind = kEpiStore;
+  epi.out = qkv;
+  epi.ldo = N;
+  epi.out_cols = N;
+  epi.rope_cos = cos_t;
+  epi.rope_sin = sin_t;
+  epi.rope_qw = q_w;
+  epi.rope_kw = k_w;
+  epi.rope_eps = eps;
+  epi.rope_S = S;
+  epi.rope_pos0 = pos0;
+  epi.rope_q_cols = hq * D;
+  epi.rope_cols = (hq + hkv) * D;
+  return launch_gemm(T, N, 1, nullptr, op0, mu_prev ? &op1 : nullptr, epi, 256, as_stream(stream));
+}
+
 int cd_mu_proj(const void* h, const void* w, const void* mu_param, float mu_min, float mu_max,
                int clamp_out, float out_lo, float out_hi, void* out, int T, int H, void* stream) {
   if (T < 0 || H < 8 || (H & 7) || !mu_param) return CD_ERR_INVALID;

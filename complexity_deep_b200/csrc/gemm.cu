@@ -198,6 +198,9 @@ int launch_gemm(int M, int N, int num_groups, const int* seg_offsets, const Gemm
     return CD_ERR_INVALID;
   if (op1 && (!op1->a || !op1->b || !aligned16(op1->a) || !aligned16(op1->b)))
     return CD_ERR_INVALID;
+  if (epi.rope_cos && (block_n != 256 || epi.kind != kEpiStore || epi.residual || epi.bias ||
+                       epi.residual2 || epi.row_map))
+    return CD_ERR_UNSUPPORTED;
   if (M == 0) return CD_OK;
 
   int st;
@@ -248,6 +251,15 @@ int launch_gemm(int M, int N, int num_groups, const int* seg_offsets, const Gemm
   p.do_clamp = epi.do_clamp;
   p.clamp_lo = epi.clamp_lo;
   p.clamp_hi = epi.clamp_hi;
+  p.rope_cos = epi.rope_cos;
+  p.rope_sin = epi.rope_sin;
+  p.rope_qw = static_cast<const __nv_bfloat16*>(epi.rope_qw);
+  p.rope_kw = static_cast<const __nv_bfloat16*>(epi.rope_kw);
+  p.rope_eps = epi.rope_eps;
+  p.rope_S = epi.rope_S;
+  p.rope_pos0 = epi.rope_pos0;
+  p.rope_q_cols = epi.rope_q_cols;
+  p.rope_cols = epi.rope_cols;
   p.status = di->status;
 
   // Upper bound of the tile count without reading the segment sizes (they live on the

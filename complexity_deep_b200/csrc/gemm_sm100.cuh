@@ -63,6 +63,16 @@ struct GemmParams {
   float bias_lo, bias_hi;
   int do_clamp;            // clamp the result to [clamp_lo, clamp_hi]
   float clamp_lo, clamp_hi;
+  // optional: per-head RMSNorm + rotary embedding on the first rope_cols output columns
+  // (heads of 128 columns; store epilogue with 256-wide tiles only, no residual / bias)
+  const float* rope_cos;   // [positions, 128] fp32 (nullptr = off)
+  const float* rope_sin;
+  const __nv_bfloat16* rope_qw;   // [128] norm weights of the q / k heads (both nullptr = no norm)
+  const __nv_bfloat16* rope_kw;
+  float rope_eps;
+  int rope_S, rope_pos0;   // row r sits at position rope_pos0 + r % rope_S
+  int rope_q_cols;         // columns [0, rope_q_cols) are q heads, [rope_q_cols, rope_cols) k heads
+  int rope_cols;
   int* status;             // device word; set non-zero when a bounded wait ran out
 };
 
@@ -401,6 +411,110 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
       tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
 
+      // coalesced copy-out of one staged 32 x 64 sub-tile: 4 rows x 128 bytes per warp instruction
+      auto copy_out = [&](const uint8_t* buf, int col0) {
+        const int col = col0 + cchunk * 8;
+        if (col < col_end) {
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            if ((cvalid >> it) & 1u) {
+              const int rr = it * 4 + crow_l;
+              const uint4 o = *reinterpret_cast<const uint4*>(buf + rr * 128 + ((cchunk ^ (rr & 7)) << 4));
+              *reinterpret_cast<uint4*>(p.out + static_cast<long long>(crow[it]) * p.ldo + col) = o;
+            }
+          }
+        }
+      };
+
+      bool rope_tile = false;
+      if constexpr (EPI == kEpiStore && BN == 256) {
+        rope_tile = p.rope_cos != nullptr && c.n0 < p.rope_cols;
+      }
+      if (rope_tile) {
+        if constexpr (EPI == kEpiStore && BN == 256) {
+          // Q/K RMSNorm + RoPE on the fp32 accumulators (reference: attention.py:138-155): the
+          // tile holds two heads of 128 columns; a thread owns a row, so the norm is a plain
+          // per-thread sum and rotate-half pairs column j with j + 64 of the same thread.
+          const int pos = p.rope_pos0 + (row_ok ? r % p.rope_S : 0);
+          const float* cs = p.rope_cos + static_cast<size_t>(pos) * 128;
+          const float* sn = p.rope_sin + static_cast<size_t>(pos) * 128;
+          uint8_t* buf_a = stage0;                    // columns [0, 64) of the head
+          uint8_t* buf_b = stage0 + kEpiStageBytes;   // columns [64, 128)
+#pragma unroll 1
+          for (int hh = 0; hh < 2; ++hh) {
+            const int hcol = c.n0 + hh * 128;
+            if (hcol >= col_end) break;               // uniform
+            const __nv_bfloat16* nw = (hcol < p.rope_q_cols) ? p.rope_qw : p.rope_kw;
+            float rstd = 1.0f;
+            if (nw) {
+              float ss = 0.f;
+#pragma unroll 1
+              for (int cch = 0; cch < 4; ++cch) {
+                uint32_t v[32];
+                tmem_ld32(t_row + hh * 128 + cch * 32, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) ss += __uint_as_float(v[j]) * __uint_as_float(v[j]);
+              }
+              rstd = rsqrtf(ss * (1.0f / 128.0f) + p.rope_eps);
+            }
+#pragma unroll 1
+            for (int cch = 0; cch < 2; ++cch) {
+              uint32_t a[32], b[32];
+              tmem_ld32(t_row + hh * 128 + cch * 32, a);
+              tmem_ld32(t_row + hh * 128 + 64 + cch * 32, b);
+              tmem_ld_wait();
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const int j0 = cch * 32 + q * 8;
+                float w1[8], w2[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) w1[e] = w2[e] = rstd;
+                if (nw) {
+                  const uint4 wa = *reinterpret_cast<const uint4*>(nw + j0);
+                  const uint4 wb = *reinterpret_cast<const uint4*>(nw + 64 + j0);
+                  const uint32_t wwa[4] = {wa.x, wa.y, wa.z, wa.w}, wwb[4] = {wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    w1[2 * e] *= bf16_lo(wwa[e]); w1[2 * e + 1] *= bf16_hi(wwa[e]);
+                    w2[2 * e] *= bf16_lo(wwb[e]); w2[2 * e + 1] *= bf16_hi(wwb[e]);
+                  }
+                }
+                float o1[8], o2[8];
+#pragma unroll
+                for (int v4 = 0; v4 < 2; ++v4) {
+                  const float4 ca = __ldg(reinterpret_cast<const float4*>(cs + j0) + v4);
+                  const float4 sa = __ldg(reinterpret_cast<const float4*>(sn + j0) + v4);
+                  const float4 cb = __ldg(reinterpret_cast<const float4*>(cs + 64 + j0) + v4);
+                  const float4 sb = __ldg(reinterpret_cast<const float4*>(sn + 64 + j0) + v4);
+                  const float cav[4] = {ca.x, ca.y, ca.z, ca.w}, sav[4] = {sa.x, sa.y, sa.z, sa.w};
+                  const float cbv[4] = {cb.x, cb.y, cb.z, cb.w}, sbv[4] = {sb.x, sb.y, sb.z, sb.w};
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) {
+                    const int e = v4 * 4 + i;
+                    const float x1 = __uint_as_float(a[q * 8 + e]) * w1[e];
+                    const float x2 = __uint_as_float(b[q * 8 + e]) * w2[e];
+                    o1[e] = x1 * cav[i] - x2 * sav[i];   // x cos + rotate_half(x) sin, first half
+                    o2[e] = x2 * cbv[i] + x1 * sbv[i];   // second half
+                  }
+                }
+                uint4 oa, ob;
+                oa.x = pack_bf16x2(o1[0], o1[1]); oa.y = pack_bf16x2(o1[2], o1[3]);
+                oa.z = pack_bf16x2(o1[4], o1[5]); oa.w = pack_bf16x2(o1[6], o1[7]);
+                ob.x = pack_bf16x2(o2[0], o2[1]); ob.y = pack_bf16x2(o2[2], o2[3]);
+                ob.z = pack_bf16x2(o2[4], o2[5]); ob.w = pack_bf16x2(o2[6], o2[7]);
+                const uint32_t slot = own_off + (((cch * 4 + q) ^ (lane & 7)) << 4);
+                *reinterpret_cast<uint4*>(buf_a + slot) = oa;
+                *reinterpret_cast<uint4*>(buf_b + slot) = ob;
+              }
+            }
+            __syncwarp();
+            copy_out(buf_a, hcol);
+            copy_out(buf_b, hcol + 64);
+            __syncwarp();
+          }
+        }
+      } else {
 #pragma unroll 1
       for (int sub = 0; sub < nsub; ++sub) {
         uint8_t* buf = stage0 + (sub & 1) * kEpiStageBytes;
@@ -494,23 +608,11 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
           }
         }
         __syncwarp();
-        // coalesced copy-out: 4 rows x 128 bytes per warp instruction
-        {
-          const int col = col0 + cchunk * 8;
-          if (col < col_end) {
-#pragma unroll
-            for (int it = 0; it < 8; ++it) {
-              if ((cvalid >> it) & 1u) {
-                const int rr = it * 4 + crow_l;
-                const uint4 o = *reinterpret_cast<const uint4*>(buf + rr * 128 + ((cchunk ^ (rr & 7)) << 4));
-                *reinterpret_cast<uint4*>(p.out + static_cast<long long>(crow[it]) * p.ldo + col) = o;
-              }
-            }
-          }
-        }
+        copy_out(buf, col0);
         __syncwarp();  // the buffer may be refilled from here on
         if (has_res && sub + 2 < nsub) fetch_residual(sub + 2);
       }
+      }  // plain tiles
       // this warp is done reading the accumulator
       tc_fence_before();
       __syncwarp();

@@ -51,6 +51,13 @@ struct GemmEpilogueArgs {
   float bias_lo, bias_hi;
   int do_clamp;
   float clamp_lo, clamp_hi;
+  // optional fused Q/K RMSNorm + RoPE (see GemmParams)
+  const float* rope_cos;
+  const float* rope_sin;
+  const void* rope_qw;
+  const void* rope_kw;
+  float rope_eps;
+  int rope_S, rope_pos0, rope_q_cols, rope_cols;
 };
 
 // Returns a CD_* status code.

@@ -384,6 +384,41 @@ def mu_qkv(x: torch.Tensor, mu_prev: Optional[torch.Tensor], w: torch.Tensor,
     return out
 
 
+def mu_qkv_rope(x: torch.Tensor, mu_prev: Optional[torch.Tensor], w: torch.Tensor,
+                w_mu: Optional[torch.Tensor], q_w: Optional[torch.Tensor],
+                k_w: Optional[torch.Tensor], cos: torch.Tensor, sin: torch.Tensor, eps: float,
+                seq_len: int, pos0: int, hq: int, hkv: int, head_dim: int) -> torch.Tensor:
+    """The mu-guided QKV projection with Q/K RMSNorm + RoPE applied before the output is
+    rounded: the fused kernel where it applies, else cd_mu_qkv followed by cd_qk_norm_rope."""
+    lib = _lib.load()
+    T, H = x.shape
+    N = w.shape[0]
+    if not lib.cd_mu_qkv_rope_supported(T, N, hq, hkv, head_dim):
+        qkv = mu_qkv(x, mu_prev, w, w_mu)
+        return qk_norm_rope_(qkv, q_w, k_w, cos, sin, eps, seq_len, pos0, hq, hkv, head_dim)
+    _need(x, "x")
+    _need(w, "qkv weight")
+    _need(cos, "cos", torch.float32)
+    _need(sin, "sin", torch.float32)
+    if mu_prev is not None:
+        _need(mu_prev, "mu_prev")
+        _need(w_mu, "mu qkv weight")
+        if tuple(mu_prev.shape) != (T, H) or tuple(w_mu.shape) != (N, H):
+            raise RuntimeError("mu_prev / mu weights do not match x / qkv weights")
+    if q_w is not None:
+        _need(q_w, "q_norm.weight")
+        _need(k_w, "k_norm.weight")
+    if cos.shape[0] < pos0 + seq_len or cos.shape[1] != head_dim:
+        raise RuntimeError("cos/sin tables too short for the requested positions")
+    out = torch.empty(T, N, dtype=BF16, device=x.device)
+    with _Span("mu_qkv"):
+        _lib.check(lib.cd_mu_qkv_rope(
+            x.data_ptr(), _ptr(mu_prev), w.data_ptr(), _ptr(w_mu) if mu_prev is not None else None,
+            out.data_ptr(), T, H, N, _ptr(q_w), _ptr(k_w), cos.data_ptr(), sin.data_ptr(),
+            float(eps), seq_len, pos0, hq, hkv, head_dim, _stream()), "cd_mu_qkv_rope")
+    return out
+
+
 def mu_proj(h: torch.Tensor, w: torch.Tensor, mu_param: torch.Tensor, mu_min: float,
             mu_max: float, out_clamp: Optional[Tuple[float, float]] = None) -> torch.Tensor:
     lib = _lib.load()

@@ -171,6 +171,19 @@ int cd_moe_combine(const void* h_shared, int I_s, const void* wd_shared, const v
 int cd_mu_qkv(const void* x, const void* mu_prev, const void* w, const void* w_mu, void* qkv,
               int T, int H, int N, void* stream);
 
+/* ---- mu-guided QKV with Q/K RMSNorm + rotary embedding in the epilogue ---------------------
+ * cd_mu_qkv followed by cd_qk_norm_rope, in one kernel: the norm and the rotation are applied
+ * to the fp32 accumulators before the single bf16 rounding (replaces
+ * complexity_deep/core/attention.py:120-131 and :138-155).  Arguments as in those two entry
+ * points.  Only for head size 128 with q and k column ranges that are multiples of 256 and
+ * enough rows for 256-wide tiles: cd_mu_qkv_rope_supported(...) returns 1 when the fused
+ * kernel applies, otherwise call the two entry points one after the other. */
+int cd_mu_qkv_rope_supported(int T, int N, int hq, int hkv, int D);
+int cd_mu_qkv_rope(const void* x, const void* mu_prev, const void* w, const void* w_mu, void* qkv,
+                   int T, int H, int N, const void* q_w, const void* k_w, const float* cos_t,
+                   const float* sin_t, float eps, int S, int pos0, int hq, int hkv, int D,
+                   void* stream);
+
 /* ---- mu projection ------------------------------------------------------------------------
  * Replaces MuGuidance.forward, complexity_deep/core/layer.py:54-61, and optionally the
  * model's clamp of the result, complexity_deep/models/modeling.py:199-200:

@@ -201,3 +201,42 @@ def test_moe_combine_shared_plus_routed_partial(T, H, Is, perm, res, routed):
     if res:
         ref = ref + rs.float()
     _close(out, ref)
+
+
+@pytest.mark.parametrize("T,S,pos0,norm,with_mu", [(4096, 512, 3, True, True), (4224, 1056, 0, False, True),
+                                                   (8192, 2048, 0, True, False), (96, 32, 5, True, True)])
+def test_mu_qkv_with_fused_qk_norm_rope(T, S, pos0, norm, with_mu):
+    """QKV projection with per-head RMSNorm + RoPE applied to the fp32 accumulators (the fused
+    kernel for many rows, the two-kernel path for few) vs fp32 arithmetic in the reference's
+    order: project, norm, rotate (attention.py:120-155)."""
+    from complexity_deep_b200 import _lib, ops
+    hq, hkv, D, H = 4, 2, 128, 256
+    N = (hq + 2 * hkv) * D
+    g = torch.Generator().manual_seed(T + pos0)
+    x, mu = _rand(g, T, H), _rand(g, T, H)
+    w, wm = _rand(g, N, H, scale=0.05), _rand(g, N, H, scale=0.05)
+    qw = (torch.randn(D, generator=g) * 0.1 + 1).to(BF)
+    kw = (torch.randn(D, generator=g) * 0.1 + 1).to(BF)
+    cos, sin = oracle.rope_tables(D, pos0 + S, 10000.0)
+    fused = bool(_lib.load().cd_mu_qkv_rope_supported(T, N, hq, hkv, D))
+    assert fused == (T >= 4096)
+    out = ops.mu_qkv_rope(x.cuda(), mu.cuda() if with_mu else None, w.cuda(),
+                          wm.cuda() if with_mu else None, qw.cuda() if norm else None,
+                          kw.cuda() if norm else None, cos.cuda(), sin.cuda(), 1e-6, S, pos0,
+                          hq, hkv, D)
+    _fetch()
+    ref = x.float() @ w.float().t()
+    if with_mu:
+        ref = ref + mu.float() @ wm.float().t()
+    B = T // S
+    q = ref[:, : hq * D].view(B, S, hq, D)
+    k = ref[:, hq * D:(hq + hkv) * D].view(B, S, hkv, D)
+    if norm:
+        q = F.rms_norm(q, (D,), qw.float(), 1e-6)
+        k = F.rms_norm(k, (D,), kw.float(), 1e-6)
+    c, s = cos[pos0:, None, :], sin[pos0:, None, :]
+    rot = lambda t: torch.cat([-t[..., D // 2:], t[..., : D // 2]], -1)
+    q, k = q * c + rot(q) * s, k * c + rot(k) * s
+    _close(out[:, : hq * D], q.reshape(T, -1))
+    _close(out[:, hq * D:(hq + hkv) * D], k.reshape(T, -1))
+    _close(out[:, (hq + hkv) * D:], ref[:, (hq + hkv) * D:])
