@@ -526,6 +526,12 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
             for (int q = 0; q < 8; ++q)
               if (col0 + q * 8 < col_end) r2[q] = ld_nc_v4(res2_row + col0 + q * 8);
           }
+          uint4 bb[8];
+          if (p.bias) {   // same for every row: issued before the TMEM loads, L1 hits
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              if (col0 + q * 8 < col_end) bb[q] = *reinterpret_cast<const uint4*>(p.bias + col0 + q * 8);
+          }
           uint32_t v[64];
           tmem_ld32(t_row + sub * 64, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
           tmem_ld32(t_row + sub * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
@@ -543,8 +549,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
             uint8_t* slot = buf + own_off + ((q ^ (lane & 7)) << 4);
             if (col < col_end) {
               if (p.bias) {
-                const uint4 b = *reinterpret_cast<const uint4*>(p.bias + col);
-                const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+                const uint32_t bw[4] = {bb[q].x, bb[q].y, bb[q].z, bb[q].w};
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                   f[2 * j] += fminf(fmaxf(bf16_lo(bw[j]), p.bias_lo), p.bias_hi);
