@@ -371,7 +371,8 @@ def run_layer(args):
     if args.workload == "ep_layer":
         # expected rows per expert from the token frequencies, for the balanced placement
         load = torch.bincount(table, weights=p.double(), minlength=E)
-        ep = ExpertParallelMoE(mlp, expert_load=load if args.ep_placement == "balanced" else None)
+        ep = ExpertParallelMoE(mlp, expert_load=load if args.ep_placement == "balanced" else None,
+                               exchange=args.ep_exchange, max_tokens_per_rank=t_loc + 64)
     steps_total = args.warmup + args.steps
     gen = torch.Generator(device=dev).manual_seed(1 + rank)
     x = torch.randn(t_loc, H, device=dev, generator=gen).to(torch.bfloat16)
@@ -442,7 +443,7 @@ def run_layer(args):
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "b200",
         "config": {"workload": args.workload, **{k: v for k, v in cfg.items()},
                    "parallelism": (f"ep{world}: {E // world} experts per GPU ({args.ep_placement} "
-                                   f"placement), tokens dp{world}"
+                                   f"placement, {args.ep_exchange} exchange), tokens dp{world}"
                                    if ep is not None else "1 GPU"),
                    "tokens_per_gpu": t_loc, "flop_per_step": flop},
         "tokens_per_s": round(T * args.steps / (ms / 1e3), 1),
@@ -575,6 +576,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ep-placement", default="balanced", choices=["balanced", "contiguous"],
                     help="ep_layer: which experts share a GPU")
+    ap.add_argument("--ep-exchange", default="peer", choices=["peer", "nccl"],
+                    help="ep_layer: peer stores from the kernels, or NCCL all-to-all")
     ap.add_argument("--cache-len", type=int, default=4096, help="decode_1b: prefilled KV tokens")
     ap.add_argument("--workload", default="prefill_1b", choices=["prefill_1b", "decode_1b"] + list(LAYER_CONFIGS),
                     help="prefill_1b is the headline; the layer modes report MoE-layer TFLOP/s")

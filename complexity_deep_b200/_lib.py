@@ -40,6 +40,10 @@ SIGNATURES = {
                           c_int, c_void_p]),
     "cd_moe_down": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
                             c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "cd_push_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int,
+                             c_int, c_void_p]),
+    "cd_moe_down_push": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                                 c_int, c_void_p]),
     "cd_moe_combine": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                c_int, c_int, c_void_p]),
     "cd_mu_qkv": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,

@@ -188,6 +188,42 @@ int cd_moe_down(const void* h_routed, int I_e, const void* wd_routed, const void
                      choose_store_block_n(T, H, current_sm_count()), as_stream(stream));
 }
 
+int cd_push_rows(const void* x, const int32_t* src_rows, const int32_t* offsets,
+                 const int32_t* push_base, int E, int experts_per_rank, const uint64_t* peer_ptrs,
+                 int T, int H, void* stream) {
+  if (T < 0 || H < 8 || (H & 7) || E < 1 || E > 256 || experts_per_rank < 1 ||
+      E % experts_per_rank)
+    return CD_ERR_INVALID;
+  if (!offsets || !push_base || !peer_ptrs || (T > 0 && !x) || !aligned16(x)) return CD_ERR_INVALID;
+  cudaError_t e = launch_push_rows(x, src_rows, offsets, push_base, E, experts_per_rank,
+                                   reinterpret_cast<const unsigned long long*>(peer_ptrs), T, H,
+                                   as_stream(stream));
+  return e == cudaSuccess ? CD_OK : cuda_fail(e, "push_rows launch");
+}
+
+int cd_moe_down_push(const void* h_routed, int I_e, const void* wd_routed,
+                     const int32_t* seg_offsets, int E, const int64_t* out_row_ptrs, int T, int H,
+                     void* stream) {
+  if (T < 0 || H < 8 || (H & 7) || I_e < 8 || (I_e & 7) || E < 1 || !out_row_ptrs)
+    return CD_ERR_INVALID;
+  GemmOperand op0{};
+  op0.a = h_routed;
+  op0.lda = I_e;
+  op0.b = wd_routed;
+  op0.ldb = I_e;
+  op0.b_rows = static_cast<long long>(E) * H;
+  op0.b_group_rows = H;
+  op0.K = I_e;
+  GemmEpilogueArgs epi{};
+  epi.kind = kEpiStore;
+  epi.out = nullptr;
+  epi.ldo = H;
+  epi.out_cols = H;
+  epi.out_row_ptrs = reinterpret_cast<const long long*>(out_row_ptrs);
+  return launch_gemm(T, H, E, seg_offsets, op0, nullptr, epi,
+                     choose_store_block_n(T, H, current_sm_count()), as_stream(stream));
+}
+
 int cd_moe_combine(const void* h_shared, int I_s, const void* wd_shared, const void* routed_sorted,
                    const int32_t* row_map, const void* residual, void* out, int T, int H,
                    void* stream) {

@@ -192,7 +192,7 @@ int launch_gemm(int M, int N, int num_groups, const int* seg_offsets, const Gemm
   if ((epi.ldo & 7) || (epi.out_cols & 7) || (epi.residual && (epi.ldr & 7)))
     return CD_ERR_INVALID;
   auto aligned16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
-  if (!op0.a || !op0.b || !epi.out || !aligned16(op0.a) || !aligned16(op0.b) ||
+  if (!op0.a || !op0.b || (!epi.out && !epi.out_row_ptrs) || !aligned16(op0.a) || !aligned16(op0.b) ||
       !aligned16(epi.out) || !aligned16(epi.residual) || !aligned16(epi.residual2) ||
       !aligned16(epi.bias) || (epi.residual2 && (epi.ldr2 & 7)))
     return CD_ERR_INVALID;
@@ -241,6 +241,7 @@ int launch_gemm(int M, int N, int num_groups, const int* seg_offsets, const Gemm
   p.ldo = epi.ldo;
   p.out_cols = epi.out_cols;
   p.row_map = epi.row_map;
+  p.out_row_ptrs = epi.out_row_ptrs;
   p.residual = static_cast<const __nv_bfloat16*>(epi.residual);
   p.ldr = epi.ldr;
   p.residual2 = static_cast<const __nv_bfloat16*>(epi.residual2);

@@ -55,6 +55,8 @@ struct GemmParams {
   int ldo;
   int out_cols;            // valid output columns (N for store, N/2-ish width I for SwiGLU)
   const int* row_map;      // sorted row -> destination row (nullptr = identity)
+  const long long* out_row_ptrs;  // sorted row -> ADDRESS of its destination row (overrides out /
+                                  // row_map; rows may live in another GPU's peer-mapped memory)
   const __nv_bfloat16* residual;  // indexed like out (nullptr = none)
   int ldr;
   const __nv_bfloat16* residual2;  // second addend, indexed by the tile row itself (nullptr = none)
@@ -368,6 +370,18 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
         crow[it] = __shfl_sync(0xffffffffu, orow, it * 4 + crow_l);
         cvalid |= (__shfl_sync(0xffffffffu, row_ok ? 1 : 0, it * 4 + crow_l) ? 1u : 0u) << it;
       }
+      // destination row addresses when rows are pushed to arbitrary (peer) memory
+      long long cptr[8];
+      const bool use_ptrs = (EPI == kEpiStore) && p.out_row_ptrs != nullptr;
+      if (use_ptrs) {
+        const long long mine = row_ok ? p.out_row_ptrs[r] : 0;
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+          const unsigned lo = __shfl_sync(0xffffffffu, static_cast<unsigned>(mine), it * 4 + crow_l);
+          const unsigned hi = __shfl_sync(0xffffffffu, static_cast<unsigned>(mine >> 32), it * 4 + crow_l);
+          cptr[it] = static_cast<long long>((static_cast<unsigned long long>(hi) << 32) | lo);
+        }
+      }
       // output columns of this tile and the number of 64-column sub-tiles
       const int ocol_base = (EPI == kEpiStore) ? c.n0 : c.n0 / 2;
       const int ocol_span = (EPI == kEpiStore) ? BN : BN / 2;
@@ -420,7 +434,9 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
             if ((cvalid >> it) & 1u) {
               const int rr = it * 4 + crow_l;
               const uint4 o = *reinterpret_cast<const uint4*>(buf + rr * 128 + ((cchunk ^ (rr & 7)) << 4));
-              *reinterpret_cast<uint4*>(p.out + static_cast<long long>(crow[it]) * p.ldo + col) = o;
+              __nv_bfloat16* drow = use_ptrs ? reinterpret_cast<__nv_bfloat16*>(cptr[it])
+                                             : p.out + static_cast<long long>(crow[it]) * p.ldo;
+              *reinterpret_cast<uint4*>(drow + col) = o;
             }
           }
         }

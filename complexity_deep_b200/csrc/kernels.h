@@ -15,6 +15,10 @@ cudaError_t launch_rmsnorm(const void* x, const void* residual, const void* weig
                            cudaStream_t stream);
 cudaError_t launch_gather_rows(const void* x, const int* src_rows, void* out, int T, int H,
                                cudaStream_t stream);
+cudaError_t launch_push_rows(const void* x, const int* src_rows, const int* offsets,
+                             const int* push_base, int E, int experts_per_rank,
+                             const unsigned long long* peer_ptrs, int T, int H,
+                             cudaStream_t stream);
 cudaError_t launch_qk_norm_rope(void* qkv, const void* q_w, const void* k_w, const float* cos_t,
                                 const float* sin_t, float eps, int T, int S, int pos0, int hq,
                                 int hkv, int D, cudaStream_t stream);
@@ -43,6 +47,7 @@ struct GemmEpilogueArgs {
   int ldo;
   int out_cols;
   const int* row_map;
+  const long long* out_row_ptrs;  // per sorted row: address of its destination row (may be peer memory)
   const void* residual;
   int ldr;
   const void* residual2;   // indexed by the un-mapped row

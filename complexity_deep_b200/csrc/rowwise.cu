@@ -151,6 +151,37 @@ gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ 
   }
 }
 
+// Expert-parallel dispatch by peer stores: sorted row j (source row src_rows[j] of x, or j
+// itself) belongs to expert e with offsets[e] <= j < offsets[e + 1]; it is written to row
+// push_base[e] + (j - offsets[e]) of the receive buffer of rank e / experts_per_rank, whose
+// base address (peer-mapped memory) is peer_ptrs[rank].  Plain 16-byte stores over NVLink.
+__global__ void __launch_bounds__(256)
+push_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ src_rows,
+                 const int* __restrict__ offsets, const int* __restrict__ push_base, int E,
+                 int experts_per_rank, const unsigned long long* __restrict__ peer_ptrs, int T,
+                 int H) {
+  extern __shared__ int s_off[];   // [E + 1] offsets, [E] push_base
+  for (int i = threadIdx.x; i <= E; i += blockDim.x) s_off[i] = offsets[i];
+  for (int i = threadIdx.x; i < E; i += blockDim.x) s_off[E + 1 + i] = push_base[i];
+  __syncthreads();
+  const int j = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (j >= T) return;
+  const int lane = threadIdx.x & 31;
+  int lo = 0, hi = E;              // largest e with offsets[e] <= j
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (s_off[mid] <= j) lo = mid; else hi = mid;
+  }
+  const int e = lo;
+  const int rank = e / experts_per_rank;
+  const long long drow = static_cast<long long>(s_off[E + 1 + e]) + (j - s_off[e]);
+  __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(peer_ptrs[rank]) + drow * H;
+  const __nv_bfloat16* src = x + static_cast<size_t>(src_rows ? src_rows[j] : j) * H;
+  const uint4* s4 = reinterpret_cast<const uint4*>(src);
+  uint4* d4 = reinterpret_cast<uint4*>(dst);
+  for (int c = lane; c < (H >> 3); c += 32) d4[c] = s4[c];
+}
+
 // One warp per (token, head) over the q and k heads of the fused [T, (hq + 2 hkv) * D]
 // buffer: y = rmsnorm(head) * norm_w, then rotate-half RoPE with fp32 cos/sin tables
 // [positions, D].  Lane l owns the element pairs (2l', 2l'+1) of the first half together
@@ -334,6 +365,18 @@ cudaError_t launch_gather_rows(const void* x, const int* src_rows, void* out, in
   const int wpb = 8;
   gather_rows_kernel<<<(T + wpb - 1) / wpb, wpb * 32, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(x), src_rows, static_cast<__nv_bfloat16*>(out), T, H);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_push_rows(const void* x, const int* src_rows, const int* offsets,
+                             const int* push_base, int E, int experts_per_rank,
+                             const unsigned long long* peer_ptrs, int T, int H,
+                             cudaStream_t stream) {
+  if (T == 0) return cudaSuccess;
+  const int wpb = 8;
+  push_rows_kernel<<<(T + wpb - 1) / wpb, wpb * 32, (2 * E + 1) * sizeof(int), stream>>>(
+      static_cast<const __nv_bfloat16*>(x), src_rows, offsets, push_base, E, experts_per_rank,
+      peer_ptrs, T, H);
   return cudaGetLastError();
 }
 

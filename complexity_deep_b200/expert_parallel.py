@@ -68,6 +68,46 @@ def exchange_plan(counts: np.ndarray, rank: int, experts_per_rank: int) -> Excha
                         seg_offsets.astype(np.int32), gather_idx.astype(np.int32))
 
 
+def push_plan(counts: np.ndarray, rank: int, experts_per_rank: int, ret_ptrs: List[int],
+              row_bytes: int):
+    """Index arithmetic of the exchange by peer stores (no NCCL call on the data path).
+
+    Receive buffers are laid out expert-major, source-minor — the order the grouped GEMM wants —
+    so nothing is regrouped on arrival.  Returns
+      push_base  [E] int32: row in the owner's receive buffer where THIS rank's rows of expert
+                 e start (the owner's segment start of e plus the rows of lower-ranked sources);
+      seg_offsets [El + 1] int32: segments of this rank's own receive buffer;
+      received   rows this rank receives;
+      row_ptrs   [received] int64: for every received row, the address of its slot in its home
+                 rank's return buffer (home base + (home's sorted offset of e + k) * row_bytes).
+    """
+    counts = np.asarray(counts, dtype=np.int64)
+    G, E = counts.shape
+    El = experts_per_rank
+    if G * El != E:
+        raise ValueError(f"{E} experts do not split {El} per rank over {G} ranks")
+    per_expert = counts.sum(axis=0)                              # rows of expert e over all sources
+    seg_start = np.zeros(E, dtype=np.int64)                      # start of e in ITS OWNER's buffer
+    for r in range(G):
+        block = per_expert[r * El:(r + 1) * El]
+        seg_start[r * El:(r + 1) * El] = np.concatenate([[0], np.cumsum(block)[:-1]])
+    before = np.concatenate([np.zeros((1, E), np.int64), np.cumsum(counts, axis=0)[:-1]])  # [G, E]
+    push_base = seg_start + before[rank]
+    mine = counts[:, rank * El:(rank + 1) * El]                  # [source, local expert]
+    seg_offsets = np.concatenate([[0], np.cumsum(mine.sum(axis=0))])
+    received = int(seg_offsets[-1])
+    home_off = np.concatenate([np.zeros((G, 1), np.int64), np.cumsum(counts, axis=1)[:, :-1]], 1)
+    row_ptrs = np.empty(received, dtype=np.int64)
+    pos = 0
+    for e in range(El):
+        ge = rank * El + e
+        for i in range(G):
+            n = int(mine[i, e])
+            row_ptrs[pos:pos + n] = ret_ptrs[i] + (home_off[i, ge] + np.arange(n)) * row_bytes
+            pos += n
+    return push_base.astype(np.int32), seg_offsets.astype(np.int32), received, row_ptrs
+
+
 def balanced_placement(expert_load, world: int) -> List[int]:
     """Longest-processing-time placement: experts in order of decreasing load each go to the
     rank with the smallest load so far that still has a free slot (E / world slots per rank).
@@ -100,10 +140,22 @@ class ExpertParallelMoE:
     """
 
     def __init__(self, mlp: TokenRoutedMLP, group: Optional[dist.ProcessGroup] = None,
-                 expert_load=None):
+                 expert_load=None, exchange: str = "nccl", max_tokens_per_rank: int = 0):
         """`expert_load` (one number per expert, e.g. the summed token frequencies of its
         tokens, identical on every rank) switches from contiguous placement (expert e on rank
-        e // El) to `balanced_placement`."""
+        e // El) to `balanced_placement`.
+
+        `exchange`: "nccl" — two all_to_all_single per call; "peer" — the rows are stored
+        straight into the other GPUs' buffers (symmetric memory over NVLink) by the kernels
+        that produce them: a push kernel for the dispatch, the down-projection's epilogue for
+        the way back, with a cross-GPU barrier between the phases and no NCCL call on the
+        data path.  "peer" needs `max_tokens_per_rank` (same on every rank) to size the
+        buffers once."""
+        if exchange not in ("nccl", "peer"):
+            raise ValueError("exchange must be 'nccl' or 'peer'")
+        self.exchange = exchange
+        self.max_tokens = int(max_tokens_per_rank)
+        self._symm = None
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
@@ -169,11 +221,80 @@ class ExpertParallelMoE:
         self._plans[key] = (routing, plan, seg, gidx)
         return plan, seg, gidx
 
+    # ------------------------------------------------------------------ peer exchange
+    def _peer_buffers(self, H: int, device):
+        """Symmetric (peer-mapped) receive and return buffers, allocated once."""
+        if self._symm is None:
+            import os
+            # plain peer loads/stores only: no NVLink multicast object is bound to these buffers
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+            import torch.distributed._symmetric_memory as symm_mem
+            if self.max_tokens <= 0:
+                raise ValueError("exchange='peer' needs max_tokens_per_rank")
+            group = self.group if self.group is not None else dist.group.WORLD
+            recv = symm_mem.empty(self.world * self.max_tokens, H, dtype=torch.bfloat16,
+                                  device=device)
+            ret = symm_mem.empty(self.max_tokens, H, dtype=torch.bfloat16, device=device)
+            recv_h = symm_mem.rendezvous(recv, group=group)
+            ret_h = symm_mem.rendezvous(ret, group=group)
+            self._symm = (recv, ret, recv_h, ret_h)
+        return self._symm
+
+    def peer_plan_for(self, routing: ops.Routing, H: int):
+        key = ("peer", id(routing))
+        hit = self._plans.get(key)
+        if hit is not None and hit[0] is routing:
+            return hit[1:]
+        recv, ret, recv_h, ret_h = self._peer_buffers(H, routing.counts.device)
+        E = self.mlp.num_experts
+        all_counts = torch.empty(self.world, E, dtype=torch.int32, device=routing.counts.device)
+        dist.all_gather_into_tensor(all_counts, routing.counts, group=self.group)
+        counts = all_counts.cpu().numpy()
+        if int(counts.sum(axis=1).max()) > self.max_tokens:
+            raise ValueError("a rank has more tokens than max_tokens_per_rank")
+        push_base, seg, received, row_ptrs = push_plan(
+            counts, self.rank, self.experts_per_rank, [int(p) for p in ret_h.buffer_ptrs], H * 2)
+        dev = routing.counts.device
+        out = (torch.from_numpy(push_base).to(dev), torch.from_numpy(seg).to(dev), received,
+               torch.from_numpy(row_ptrs).to(dev))
+        if len(self._plans) > 8:
+            self._plans.clear()
+        self._plans[key] = (routing,) + out
+        return out
+
+    def _forward_sorted_peer(self, x_sorted, routing, residual):
+        mlp = self.mlp
+        T, H = x_sorted.shape
+        recv, ret, recv_h, ret_h = self._peer_buffers(H, x_sorted.device)
+        push_base, seg, received, row_ptrs = self.peer_plan_for(routing, H)
+        # dispatch: every row goes straight into its expert's GPU
+        ops.push_rows(x_sorted, routing.offsets, push_base, mlp.num_experts,
+                      self.experts_per_rank, recv_h.buffer_ptrs_dev)
+        h_s = wd_s = None
+        if mlp.use_shared_expert:          # local work while the pushes of the peers land
+            packed_s, bn_s = mlp._packed_shared(T)
+            h_s = ops.moe_up(x_sorted, None, 1, packed_s, mlp.shared_gate.weight.shape[0], bn_s)
+            wd_s = mlp.shared_down.weight.detach()
+        recv_h.barrier(channel=0)          # all pushes visible; also: peers are done reading `ret`
+        if received > 0:
+            h_r = ops.moe_up(recv[:received], seg, self.experts_per_rank, self.packed_local,
+                             mlp.expert_intermediate_size, self.block_n)
+            # the epilogue stores every finished row in its home GPU's return buffer
+            ops.moe_down_push(h_r, self.down_local, seg, self.experts_per_rank, row_ptrs)
+        ret_h.barrier(channel=0)           # all routed rows are home; peers are done reading `recv`
+        y_sorted = ret[:T]
+        if h_s is not None:
+            return ops.moe_combine(h_s, wd_s, y_sorted, routing.perm, residual)
+        out = ops.gather_rows(y_sorted, routing.inv_perm)
+        return out if residual is None else out + residual.reshape(out.shape)
+
     # ------------------------------------------------------------------ forward
     def forward_sorted(self, x_sorted: torch.Tensor, routing: ops.Routing,
                        residual: Optional[torch.Tensor]) -> torch.Tensor:
         """x_sorted: this rank's rows in expert-sorted order [T_local, H]; returns rows in
         ORIGINAL order with shared + routed (+ residual) combined in fp32."""
+        if self.exchange == "peer":
+            return self._forward_sorted_peer(x_sorted, routing, residual)
         mlp = self.mlp
         H = x_sorted.shape[1]
         plan, seg, gidx = self.plan_for(routing)

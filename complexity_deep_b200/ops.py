@@ -335,6 +335,39 @@ def moe_down(h_routed: torch.Tensor, wd_routed: torch.Tensor, h_shared: Optional
     return out
 
 
+def push_rows(x_sorted: torch.Tensor, offsets: torch.Tensor, push_base: torch.Tensor,
+              num_experts: int, experts_per_rank: int, peer_ptrs_dev: int) -> None:
+    """Writes every expert-sorted row into the receive buffer of the GPU that owns its expert
+    (peer-mapped memory; `peer_ptrs_dev` = device address of the array of buffer addresses)."""
+    lib = _lib.load()
+    _need(x_sorted, "x_sorted")
+    _need(offsets, "offsets", torch.int32)
+    _need(push_base, "push_base", torch.int32)
+    T, H = x_sorted.shape
+    with _Span("push_rows"):
+        _lib.check(lib.cd_push_rows(x_sorted.data_ptr(), None, offsets.data_ptr(),
+                                    push_base.data_ptr(), num_experts, experts_per_rank,
+                                    peer_ptrs_dev, T, H, _stream()), "cd_push_rows")
+
+
+def moe_down_push(h_routed: torch.Tensor, wd_routed: torch.Tensor, seg_offsets: torch.Tensor,
+                  num_experts: int, out_row_ptrs: torch.Tensor) -> None:
+    """Routed down projection whose epilogue stores each row at its own address."""
+    lib = _lib.load()
+    _need(h_routed, "h_routed")
+    _need(wd_routed, "routed down weights")
+    _need(seg_offsets, "seg_offsets", torch.int32)
+    _need(out_row_ptrs, "out_row_ptrs", torch.int64)
+    T, I_e = h_routed.shape
+    E, H, _ = wd_routed.shape
+    if E != num_experts or out_row_ptrs.numel() != T:
+        raise RuntimeError("moe_down_push: shapes do not match")
+    with _Span("moe_down"):
+        _lib.check(lib.cd_moe_down_push(h_routed.data_ptr(), I_e, wd_routed.data_ptr(),
+                                        seg_offsets.data_ptr(), E, out_row_ptrs.data_ptr(), T, H,
+                                        _stream()), "cd_moe_down_push")
+
+
 def moe_combine(h_shared: torch.Tensor, wd_shared: torch.Tensor,
                 routed_sorted: Optional[torch.Tensor], row_map: Optional[torch.Tensor],
                 residual: Optional[torch.Tensor]) -> torch.Tensor:

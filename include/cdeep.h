@@ -161,6 +161,28 @@ int cd_moe_combine(const void* h_shared, int I_s, const void* wd_shared, const v
                    const int32_t* row_map, const void* residual, void* out, int T, int H,
                    void* stream);
 
+/* ---- expert-parallel exchange by peer stores --------------------------------------------------
+ * (The reference has no distributed code; these two entry points replace the NCCL all-to-alls
+ * of the expert-parallel layer with stores into peer-mapped memory, issued by the kernels that
+ * produce the rows.  The caller provides peer-mapped buffers, e.g. CUDA IPC or symmetric
+ * memory, and orders the phases with a barrier across the GPUs.)
+ *
+ * cd_push_rows: sorted row j (= x[src_rows[j]], or x[j] when src_rows is NULL) of expert e
+ * (offsets[e] <= j < offsets[e+1]) is written to row push_base[e] + (j - offsets[e]) of the
+ * buffer whose address is peer_ptrs[e / experts_per_rank] (device array of E /
+ * experts_per_rank addresses).
+ *
+ * cd_moe_down_push: the routed down projection of cd_moe_down (no shared expert, no residual)
+ * whose epilogue writes sorted row r to the ADDRESS out_row_ptrs[r] (device array, one per row;
+ * rows may live in another GPU's memory), so each finished tile leaves for its home GPU while
+ * the next one is being computed. */
+int cd_push_rows(const void* x, const int32_t* src_rows, const int32_t* offsets,
+                 const int32_t* push_base, int E, int experts_per_rank, const uint64_t* peer_ptrs,
+                 int T, int H, void* stream);
+int cd_moe_down_push(const void* h_routed, int I_e, const void* wd_routed,
+                     const int32_t* seg_offsets, int E, const int64_t* out_row_ptrs, int T, int H,
+                     void* stream);
+
 /* ---- mu-guided QKV -------------------------------------------------------------------------
  * Replaces complexity_deep/core/attention.py:120-131: torch.cat([x, mu_prev]) against the
  * re-concatenated weights, three F.linear calls.  One GEMM whose K loop walks x then

@@ -16,7 +16,7 @@ pytestmark = pytest.mark.gpu
 BF = torch.bfloat16
 
 
-def _rank_main(rank, world, port, balanced, out):
+def _rank_main(rank, world, port, balanced, exchange, out):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank),
                       WORLD_SIZE=str(world))
     sys.path.insert(0, ROOT)
@@ -43,12 +43,15 @@ def _rank_main(rank, world, port, balanced, out):
         sd["token_to_expert"] = table
         mlp = mlp.to(device="cuda", dtype=BF).eval()
         load = torch.bincount(table, weights=oracle.zipf_probabilities(V, 1.0), minlength=E)
-        ep = ExpertParallelMoE(mlp, expert_load=load if balanced else None)
+        ep = ExpertParallelMoE(mlp, expert_load=load if balanced else None, exchange=exchange,
+                               max_tokens_per_rank=1024)
         gi = torch.Generator().manual_seed(100 + rank)            # different tokens per rank
         x = torch.randn(1, T, H, generator=gi).to(BF)
         ids = oracle.zipf_token_ids(V, 1.0, T, seed=100 + rank).view(1, T)
         res = torch.randn(T, H, generator=gi).to(BF)
         y = ep(x.cuda(), ids.cuda())
+        y_again = ep(x.cuda(), ids.cuda())                        # buffers are reused call to call
+        assert torch.equal(y, y_again)
         routing = ep.routing(ids.cuda())
         xs = ops.gather_rows(x.cuda().view(T, H), routing.perm)
         y_res = ep.forward_sorted(xs, routing, res.cuda())
@@ -64,13 +67,15 @@ def _rank_main(rank, world, port, balanced, out):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("balanced", [False, True])
-def test_expert_parallel_layer_two_gpus(balanced):
+@pytest.mark.parametrize("balanced,exchange", [(False, "nccl"), (True, "nccl"), (True, "peer"),
+                                               (False, "peer")])
+def test_expert_parallel_layer_two_gpus(balanced, exchange):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     mgr = mp.Manager()
     out = mgr.dict()
-    mp.spawn(_rank_main, args=(2, 29655 + int(balanced), balanced, out), nprocs=2, join=True)
+    port = 29655 + int(balanced) + 2 * int(exchange == "peer")
+    mp.spawn(_rank_main, args=(2, port, balanced, exchange, out), nprocs=2, join=True)
     total = 0
     for rank in range(2):
         (mr1, ma1), (mr2, ma2), (mr3, ma3), rms, received = out[rank]

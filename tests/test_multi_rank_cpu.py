@@ -120,3 +120,40 @@ def test_balanced_placement_spreads_heavy_experts():
     owner = {e: i // 4 for i, e in enumerate(order)}
     assert owner[0] != owner[1]                          # the two heaviest are on different ranks
     assert balanced_placement([1.0] * 8, 2) == [0, 2, 4, 6, 1, 3, 5, 7]
+
+
+def test_push_plan_addresses_cover_every_row_exactly_once():
+    """Peer-store exchange arithmetic, all ranks simulated on the host: every (source, sorted
+    row) is written to a distinct slot of its expert owner's buffer inside that expert's
+    segment, and every received row is sent back to the slot it came from."""
+    import numpy as np
+    from complexity_deep_b200.expert_parallel import push_plan
+    rng = np.random.default_rng(0)
+    G, El, H = 4, 2, 16
+    E = G * El
+    counts = rng.integers(0, 7, size=(G, E))
+    counts[2, 3] = 0
+    ret_base = [1000000 * (i + 1) for i in range(G)]
+    plans = [push_plan(counts, r, El, ret_base, H * 2) for r in range(G)]
+    recv = [dict() for _ in range(G)]                    # owner -> {row: (source, expert, k)}
+    for src in range(G):
+        push_base = plans[src][0]
+        for e in range(E):
+            owner = e // El
+            for k in range(counts[src, e]):
+                row = int(push_base[e]) + k
+                assert row not in recv[owner]
+                recv[owner][row] = (src, e, k)
+    for r in range(G):
+        _, seg, received, row_ptrs = plans[r]
+        assert received == len(recv[r]) == counts[:, r * El:(r + 1) * El].sum()
+        assert sorted(recv[r]) == list(range(received))  # dense, no holes
+        home_off = np.concatenate([np.zeros((G, 1), np.int64), np.cumsum(counts, 1)[:, :-1]], 1)
+        seen = set()
+        for row in range(received):
+            src, e, k = recv[r][row]
+            assert seg[e - r * El] <= row < seg[e - r * El + 1]        # inside its expert's segment
+            want = ret_base[src] + (home_off[src, e] + k) * H * 2       # its sorted slot at home
+            assert int(row_ptrs[row]) == want
+            seen.add(want)
+        assert len(seen) == received
