@@ -96,15 +96,51 @@ def peaks() -> dict:
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons of one GPU while the timed region runs."""
+    """Samples SM clock and throttle reasons of one GPU while the timed region runs: NVML from a
+    thread of this process (no start-up delay, so short regions still get samples), nvidia-smi
+    as the fallback."""
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
+    REASON_BITS = {"sw_power_cap": 0x4, "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20,
+                   "hw_thermal_slowdown": 0x40}
+    _nvml_ready = False
 
     def __init__(self, index: int):
         self.index, self.rows, self.proc = index, [], None
+        self.samples, self.mask, self.max_mhz = [], 0, None
+        self.handle, self.stop_flag, self.thread = None, threading.Event(), None
+        try:
+            import pynvml
+            if not ClockSampler._nvml_ready:
+                pynvml.nvmlInit()
+                ClockSampler._nvml_ready = True
+            uuid = str(torch.cuda.get_device_properties(index).uuid)
+            uuid = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+            try:
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            except Exception:
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(uuid)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+            self.nvml = pynvml
+        except Exception:
+            self.handle = None
+
+    def _poll(self):
+        nv = self.nvml
+        while not self.stop_flag.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
+                self.mask |= int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle))
+            except Exception:
+                pass
+            self.stop_flag.wait(0.01)
 
     def start(self):
+        if self.handle is not None:
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+            return
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
@@ -119,6 +155,14 @@ class ClockSampler:
             self.rows.append([c.strip() for c in line.split(",")])
 
     def stop(self) -> dict:
+        if self.thread is not None:
+            self.stop_flag.set()
+            self.thread.join(timeout=1.0)
+            if not self.samples:
+                return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["no samples"]}
+            reasons = [n for n, bit in self.REASON_BITS.items() if self.mask & bit]
+            return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz,
+                    "samples": len(self.samples), "reasons": sorted(reasons), "source": "nvml"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.15)
@@ -129,7 +173,8 @@ class ClockSampler:
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = [n for i, n in enumerate(names) if any(r[2 + i] == "Active" for r in rows)]
         return {"sm_mhz": statistics.median(int(r[0]) for r in rows),
-                "sm_max_mhz": int(rows[0][1]), "samples": len(rows), "reasons": reasons}
+                "sm_max_mhz": int(rows[0][1]), "samples": len(rows), "reasons": reasons,
+                "source": "nvidia-smi"}
 
 
 # ------------------------------------------------------------------------------- our arm
