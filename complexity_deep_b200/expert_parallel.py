@@ -108,6 +108,36 @@ def push_plan(counts: np.ndarray, rank: int, experts_per_rank: int, ret_ptrs: Li
     return push_base.astype(np.int32), seg_offsets.astype(np.int32), received, row_ptrs
 
 
+def push_plan_tensors(counts: torch.Tensor, rank: int, experts_per_rank: int,
+                      ret_ptrs: torch.Tensor, row_bytes: int, capacity: int):
+    """`push_plan` with tensor operations on the device that holds `counts` ([ranks, E]), so the
+    layer needs no device->host copy: nothing here depends on a host-side value of the counts.
+    `ret_ptrs`: int64 [ranks] base addresses of the ranks' return buffers.  `row_ptrs` has
+    `capacity` entries; entries past the received rows are never used (the grouped GEMM's tile
+    schedule comes from `seg_offsets` on the device)."""
+    G, E = counts.shape
+    El = experts_per_rank
+    c = counts.to(torch.int64)
+    per_expert = c.sum(dim=0).view(G, El)
+    seg_start = (per_expert.cumsum(dim=1) - per_expert).reshape(E)
+    before = c.cumsum(dim=0) - c
+    push_base = (seg_start + before[rank]).to(torch.int32)
+    mine = c[:, rank * El:(rank + 1) * El]                                   # [source, local e]
+    zero = torch.zeros(1, dtype=torch.int64, device=c.device)
+    seg_offsets = torch.cat([zero, mine.sum(dim=0).cumsum(dim=0)]).to(torch.int32)
+    blocks = mine.t().reshape(-1)                                            # (local e, source)
+    block_end = blocks.cumsum(dim=0)
+    block_start = block_end - blocks
+    rows = torch.arange(capacity, dtype=torch.int64, device=c.device)
+    bid = torch.searchsorted(block_end, rows, right=True).clamp_(max=El * G - 1)
+    k = rows - block_start[bid]
+    e_loc, src = bid // G, bid % G
+    home_off = c.cumsum(dim=1) - c                                           # [rank, expert]
+    slot = home_off[src, rank * El + e_loc] + k
+    row_ptrs = ret_ptrs[src] + slot * row_bytes
+    return push_base, seg_offsets, row_ptrs
+
+
 def balanced_placement(expert_load, world: int) -> List[int]:
     """Longest-processing-time placement: experts in order of decreasing load each go to the
     rank with the smallest load so far that still has a free slot (E / world slots per rank).
@@ -156,6 +186,7 @@ class ExpertParallelMoE:
         self.exchange = exchange
         self.max_tokens = int(max_tokens_per_rank)
         self._symm = None
+        self._ret_ptrs = None
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
@@ -241,22 +272,22 @@ class ExpertParallelMoE:
         return self._symm
 
     def peer_plan_for(self, routing: ops.Routing, H: int):
+        """Exchange plan of a routed batch for the peer-store exchange, computed on the device
+        from one small all-gather of the counts (no device->host copy); cached per batch."""
         key = ("peer", id(routing))
         hit = self._plans.get(key)
         if hit is not None and hit[0] is routing:
             return hit[1:]
         recv, ret, recv_h, ret_h = self._peer_buffers(H, routing.counts.device)
         E = self.mlp.num_experts
-        all_counts = torch.empty(self.world, E, dtype=torch.int32, device=routing.counts.device)
-        dist.all_gather_into_tensor(all_counts, routing.counts, group=self.group)
-        counts = all_counts.cpu().numpy()
-        if int(counts.sum(axis=1).max()) > self.max_tokens:
-            raise ValueError("a rank has more tokens than max_tokens_per_rank")
-        push_base, seg, received, row_ptrs = push_plan(
-            counts, self.rank, self.experts_per_rank, [int(p) for p in ret_h.buffer_ptrs], H * 2)
         dev = routing.counts.device
-        out = (torch.from_numpy(push_base).to(dev), torch.from_numpy(seg).to(dev), received,
-               torch.from_numpy(row_ptrs).to(dev))
+        all_counts = torch.empty(self.world, E, dtype=torch.int32, device=dev)
+        dist.all_gather_into_tensor(all_counts, routing.counts, group=self.group)
+        if self._ret_ptrs is None:
+            self._ret_ptrs = torch.tensor([int(p) for p in ret_h.buffer_ptrs], dtype=torch.int64,
+                                          device=dev)
+        out = push_plan_tensors(all_counts, self.rank, self.experts_per_rank, self._ret_ptrs,
+                                H * 2, recv.shape[0])
         if len(self._plans) > 8:
             self._plans.clear()
         self._plans[key] = (routing,) + out
@@ -266,7 +297,9 @@ class ExpertParallelMoE:
         mlp = self.mlp
         T, H = x_sorted.shape
         recv, ret, recv_h, ret_h = self._peer_buffers(H, x_sorted.device)
-        push_base, seg, received, row_ptrs = self.peer_plan_for(routing, H)
+        push_base, seg, row_ptrs = self.peer_plan_for(routing, H)
+        if T > self.max_tokens:
+            raise ValueError("more tokens than max_tokens_per_rank")
         # dispatch: every row goes straight into its expert's GPU
         ops.push_rows(x_sorted, routing.offsets, push_base, mlp.num_experts,
                       self.experts_per_rank, recv_h.buffer_ptrs_dev)
@@ -276,11 +309,13 @@ class ExpertParallelMoE:
             h_s = ops.moe_up(x_sorted, None, 1, packed_s, mlp.shared_gate.weight.shape[0], bn_s)
             wd_s = mlp.shared_down.weight.detach()
         recv_h.barrier(channel=0)          # all pushes visible; also: peers are done reading `ret`
-        if received > 0:
-            h_r = ops.moe_up(recv[:received], seg, self.experts_per_rank, self.packed_local,
-                             mlp.expert_intermediate_size, self.block_n)
-            # the epilogue stores every finished row in its home GPU's return buffer
-            ops.moe_down_push(h_r, self.down_local, seg, self.experts_per_rank, row_ptrs)
+        # The number of received rows is only known on the device: the GEMMs are launched over
+        # the whole buffer and schedule tiles from `seg` (device), so rows past the last segment
+        # are never touched.
+        h_r = ops.moe_up(recv, seg, self.experts_per_rank, self.packed_local,
+                         mlp.expert_intermediate_size, self.block_n)
+        # the epilogue stores every finished row in its home GPU's return buffer
+        ops.moe_down_push(h_r, self.down_local, seg, self.experts_per_rank, row_ptrs)
         ret_h.barrier(channel=0)           # all routed rows are home; peers are done reading `recv`
         y_sorted = ret[:T]
         if h_s is not None:

@@ -157,3 +157,23 @@ def test_push_plan_addresses_cover_every_row_exactly_once():
             assert int(row_ptrs[row]) == want
             seen.add(want)
         assert len(seen) == received
+
+
+def test_device_side_push_plan_equals_host_plan():
+    """The tensor-op plan (run on the device in production, no host copy) gives the same
+    numbers as the host arithmetic, for every rank."""
+    import numpy as np
+    from complexity_deep_b200.expert_parallel import push_plan, push_plan_tensors
+    rng = np.random.default_rng(1)
+    G, El, H = 4, 3, 32
+    counts = rng.integers(0, 9, size=(G, G * El))
+    counts[1, 4] = 0
+    counts[:, 7] = 0                                       # an expert nobody uses
+    ret_base = [7000000 * (i + 1) for i in range(G)]
+    for r in range(G):
+        pb, seg, received, ptrs = push_plan(counts, r, El, ret_base, H * 2)
+        tpb, tseg, tptrs = push_plan_tensors(torch.from_numpy(counts).int(), r, El,
+                                             torch.tensor(ret_base), H * 2, received + 5)
+        assert tpb.dtype == torch.int32 and tseg.dtype == torch.int32 and tptrs.dtype == torch.int64
+        assert np.array_equal(tpb.numpy(), pb) and np.array_equal(tseg.numpy(), seg)
+        assert np.array_equal(tptrs.numpy()[:received], ptrs)
