@@ -211,6 +211,16 @@ def run_ours(args):
     batch = args.batch or GLOBAL_BATCH
     lo, hi = shard_batch(batch, world, rank)
     n_local = hi - lo
+    if args.expert_parallel:
+        # tokens stay data-parallel, the 8 routed experts of every layer are sharded over the
+        # ranks (not the headline configuration, which replicates the weights)
+        if dist is None:
+            raise SystemExit("--expert-parallel needs more than one GPU")
+        table = model.layers[0].mlp.token_to_expert.cpu()
+        load = torch.bincount(table, weights=zipf_probabilities(MODEL["vocab_size"], 1.1),
+                              minlength=MODEL["num_experts"])
+        model.enable_expert_parallel(exchange=args.ep_exchange, expert_load=load,
+                                     max_tokens_per_rank=n_local * SEQ_LEN)
     steps_total = args.warmup + args.steps
     # a different id batch per step, all drawn up front on the host (seeded), pinned
     host_ids = [zipf_token_ids(MODEL["vocab_size"], 1.1, batch * SEQ_LEN, seed=s)
@@ -295,7 +305,9 @@ def run_ours(args):
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic", "impl": "b200",
         "config": {"workload": WORKLOAD, "global_batch": batch, "seq_len": SEQ_LEN,
-                   "parallelism": f"dp{world}", "tokens_per_gpu_per_step": local_tokens,
+                   "parallelism": (f"dp{world} tokens + ep{world} routed experts ({args.ep_exchange})"
+                                   if args.expert_parallel else f"dp{world}"),
+                   "tokens_per_gpu_per_step": local_tokens,
                    "l2": "no flush: per-step working set (3.2 GB weights, 268 MB per activation) >> 126 MB L2; new ids each step"},
         "e2e": {"value": round(e2e, 1), "unit": UNIT, "ms_per_step": round(ms_e2e / args.steps, 3),
                 "h2d_bytes_per_step": n_local * SEQ_LEN * 8, "d2h_bytes_per_step": n_local * 8,
@@ -619,6 +631,8 @@ def main():
     ap.add_argument("--cpu-tokens", type=int, default=1024,
                     help="tokens of the bounded CPU sample (one sequence)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--expert-parallel", action="store_true",
+                    help="prefill_1b: shard the routed experts over the ranks (extra, not the headline)")
     ap.add_argument("--ep-placement", default="balanced", choices=["balanced", "contiguous"],
                     help="ep_layer: which experts share a GPU")
     ap.add_argument("--ep-exchange", default="peer", choices=["peer", "nccl"],

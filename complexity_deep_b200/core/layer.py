@@ -115,6 +115,9 @@ class TransformerBlock(nn.Module):
             self.mlp = SwiGLU(hidden_size=hidden_size, intermediate_size=intermediate_size)
         self.use_mu_guidance = use_mu_guidance
         self.mu_guidance = MuGuidance(hidden_size=hidden_size) if use_mu_guidance else None
+        # set by ComplexityModel.enable_expert_parallel: runs the routed experts sharded over
+        # the GPUs of a process group (the parameters stay where they are)
+        self.expert_parallel = None
 
     def _fusable(self, token_ids) -> bool:
         subs = [self.input_layernorm, self.self_attn, self.post_attention_layernorm, self.mlp]
@@ -177,10 +180,11 @@ class TransformerBlock(nn.Module):
         h1 = h1.view(B * S, H)
         ln2 = self.post_attention_layernorm
         if self.use_token_routed_mlp:
-            routing = self.mlp.routing(token_ids)
+            runner = self.expert_parallel if self.expert_parallel is not None else self.mlp
+            routing = runner.routing(token_ids)
             # normalised rows land directly in expert-sorted order
             x_sorted = ops.rmsnorm(h1, ln2.weight, ln2.eps, dst_rows=routing.inv_perm)
-            h2 = self.mlp.forward_sorted(x_sorted, routing, residual=h1)
+            h2 = runner.forward_sorted(x_sorted, routing, residual=h1)
         else:
             x = ops.rmsnorm(h1, ln2.weight, ln2.eps)
             h2 = self.mlp._run(x, residual=h1)

@@ -161,6 +161,25 @@ def balanced_placement(expert_load, world: int) -> List[int]:
     return [e for r in range(world) for e in sorted(slots[r])]
 
 
+class _PeerContext:
+    """Symmetric buffers, their handles and the per-batch plans, shared by every layer that
+    uses the same process group, row width, capacity and expert placement: the layers of a
+    model run one after the other, and the barriers of the exchange order the re-use."""
+    pool = {}
+
+    def __init__(self):
+        self.buffers = None      # (recv, ret, recv_handle, ret_handle)
+        self.ret_ptrs = None
+        self.plans = {}
+
+    @classmethod
+    def get(cls, key):
+        ctx = cls.pool.get(key)
+        if ctx is None:
+            ctx = cls.pool[key] = cls()
+        return ctx
+
+
 class ExpertParallelMoE:
     """Sharded runner for one ``TokenRoutedMLP``.
 
@@ -185,8 +204,7 @@ class ExpertParallelMoE:
             raise ValueError("exchange must be 'nccl' or 'peer'")
         self.exchange = exchange
         self.max_tokens = int(max_tokens_per_rank)
-        self._symm = None
-        self._ret_ptrs = None
+        self._peer = None
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
@@ -253,9 +271,17 @@ class ExpertParallelMoE:
         return plan, seg, gidx
 
     # ------------------------------------------------------------------ peer exchange
+    def _peer_context(self, H: int) -> _PeerContext:
+        if self._peer is None:
+            group = self.group if self.group is not None else dist.group.WORLD
+            self._peer = _PeerContext.get((group.group_name, H, self.max_tokens,
+                                           self.mlp.num_experts, tuple(self.order)))
+        return self._peer
+
     def _peer_buffers(self, H: int, device):
-        """Symmetric (peer-mapped) receive and return buffers, allocated once."""
-        if self._symm is None:
+        """Symmetric (peer-mapped) receive and return buffers, allocated once per context."""
+        ctx = self._peer_context(H)
+        if ctx.buffers is None:
             import os
             # plain peer loads/stores only: no NVLink multicast object is bound to these buffers
             os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
@@ -268,29 +294,30 @@ class ExpertParallelMoE:
             ret = symm_mem.empty(self.max_tokens, H, dtype=torch.bfloat16, device=device)
             recv_h = symm_mem.rendezvous(recv, group=group)
             ret_h = symm_mem.rendezvous(ret, group=group)
-            self._symm = (recv, ret, recv_h, ret_h)
-        return self._symm
+            ctx.buffers = (recv, ret, recv_h, ret_h)
+            ctx.ret_ptrs = torch.tensor([int(p) for p in ret_h.buffer_ptrs], dtype=torch.int64,
+                                        device=device)
+        return ctx.buffers
 
     def peer_plan_for(self, routing: ops.Routing, H: int):
         """Exchange plan of a routed batch for the peer-store exchange, computed on the device
-        from one small all-gather of the counts (no device->host copy); cached per batch."""
-        key = ("peer", id(routing))
-        hit = self._plans.get(key)
+        from one small all-gather of the counts (no device->host copy); cached per batch and
+        shared by all layers of the context."""
+        recv, ret, recv_h, ret_h = self._peer_buffers(H, routing.counts.device)
+        ctx = self._peer_context(H)
+        key = id(routing)
+        hit = ctx.plans.get(key)
         if hit is not None and hit[0] is routing:
             return hit[1:]
-        recv, ret, recv_h, ret_h = self._peer_buffers(H, routing.counts.device)
         E = self.mlp.num_experts
         dev = routing.counts.device
         all_counts = torch.empty(self.world, E, dtype=torch.int32, device=dev)
         dist.all_gather_into_tensor(all_counts, routing.counts, group=self.group)
-        if self._ret_ptrs is None:
-            self._ret_ptrs = torch.tensor([int(p) for p in ret_h.buffer_ptrs], dtype=torch.int64,
-                                          device=dev)
-        out = push_plan_tensors(all_counts, self.rank, self.experts_per_rank, self._ret_ptrs,
+        out = push_plan_tensors(all_counts, self.rank, self.experts_per_rank, ctx.ret_ptrs,
                                 H * 2, recv.shape[0])
-        if len(self._plans) > 8:
-            self._plans.clear()
-        self._plans[key] = (routing,) + out
+        if len(ctx.plans) > 8:
+            ctx.plans.clear()
+        ctx.plans[key] = (routing,) + out
         return out
 
     def _forward_sorted_peer(self, x_sorted, routing, residual):

@@ -100,6 +100,25 @@ class ComplexityModel(nn.Module):
             if isinstance(getattr(mlp, "shared_down", None), nn.Linear):
                 nn.init.normal_(mlp.shared_down.weight, mean=0.0, std=std)
 
+    # ------------------------------------------------------------------ expert parallelism
+    def enable_expert_parallel(self, group=None, exchange: str = "peer",
+                               max_tokens_per_rank: int = 0, expert_load=None) -> None:
+        """Shards the routed experts of every layer over the ranks of `group` (needs
+        num_experts % world_size == 0); tokens stay data-parallel, each rank calls forward on
+        its own sequences and gets the same logits as without sharding.  Not part of the
+        reference's API (it has no distributed code).  `max_tokens_per_rank`: upper bound of
+        batch x sequence length per rank (sizes the exchange buffers, which all layers share)."""
+        from ..expert_parallel import ExpertParallelMoE
+        for layer in self.layers:
+            if layer.use_token_routed_mlp:
+                layer.expert_parallel = ExpertParallelMoE(
+                    layer.mlp, group, expert_load=expert_load, exchange=exchange,
+                    max_tokens_per_rank=max_tokens_per_rank)
+
+    def disable_expert_parallel(self) -> None:
+        for layer in self.layers:
+            layer.expert_parallel = None
+
     # ------------------------------------------------------------------ forward
     def forward(
         self,
