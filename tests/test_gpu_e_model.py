@@ -129,3 +129,21 @@ def test_config_variants_vs_oracle(flags):
     # layer-1 keys: unit-scale values (QK-norm) computed from a bf16 residual stream, so the
     # rounding of the stream (~2^-9 relative) shows up undamped: mean bound 3 roundings wide
     _close(out.past_key_values[1][0], ref_kv[1][0], max_rel=2e-2, mean_abs=6e-3)
+
+
+@torch.no_grad()
+def test_prefill_graph_replays_route_new_ids():
+    """CUDA-graph replay of the forward: same logits as the eager call, for ids that differ
+    from the ones seen at capture (the dispatch is inside the graph)."""
+    from complexity_deep_b200.models import ComplexityConfig, ComplexityModel, PrefillGraph
+    torch.manual_seed(0)
+    cfg = ComplexityConfig(vocab_size=512, hidden_size=256, intermediate_size=512,
+                           num_hidden_layers=2, num_attention_heads=2, num_key_value_heads=1,
+                           num_experts=4)
+    model = ComplexityModel(cfg).to(device="cuda", dtype=BF).eval()
+    graph = PrefillGraph(model, batch=2, seq_len=64)
+    for seed in (11, 12):
+        ids = oracle.zipf_token_ids(512, 1.1, 128, seed=seed).view(2, 64).cuda()
+        eager = model(ids).logits
+        replayed = graph(ids).clone()
+        assert torch.equal(eager, replayed)
