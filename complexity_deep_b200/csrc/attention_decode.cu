@@ -74,35 +74,28 @@ decode_attn_partial_kernel(const __nv_bfloat16* __restrict__ q, long long q_stri
   const __nv_bfloat16* vb = v + b * kv_stride_b + kvh * kv_stride_h + sub * DPL;
   const __nv_bfloat16* mb = mask ? mask + b * mask_stride_b : nullptr;
 
-  // rows of this block: t_begin + 16 * i + (warp * 4 + rgrp); the loop bound is the same for
-  // every lane of a warp (the shuffles below need the whole warp).  The loads of the next
-  // step are issued before the arithmetic of the current one.
-  uint4 kn[DPL / 8], vn[DPL / 8];
-  auto load_rows = [&](int t) {
+  // Rows of this block: t_begin + 16 * i + (warp * 4 + rgrp), two steps (rows t and t + 16) per
+  // iteration; the loads of the next iteration are issued before the arithmetic of the current
+  // one, so 8 x 16 bytes per lane are in flight.  The loop bound is the same for every lane of
+  // a warp (the shuffles need the whole warp).
+  constexpr int kV = DPL / 8;
+  uint4 kn[2][kV], vn[2][kV];
+  auto load_rows = [&](int t, int s) {
 #pragma unroll
-    for (int i = 0; i < DPL / 8; ++i) {
-      kn[i] = make_uint4(0, 0, 0, 0);
-      vn[i] = make_uint4(0, 0, 0, 0);
+    for (int i = 0; i < kV; ++i) {
+      kn[s][i] = make_uint4(0, 0, 0, 0);
+      vn[s][i] = make_uint4(0, 0, 0, 0);
       if (t < t_end) {
-        kn[i] = *reinterpret_cast<const uint4*>(kb + t * kv_stride_t + i * 8);
-        vn[i] = *reinterpret_cast<const uint4*>(vb + t * kv_stride_t + i * 8);
+        kn[s][i] = *reinterpret_cast<const uint4*>(kb + t * kv_stride_t + i * 8);
+        vn[s][i] = *reinterpret_cast<const uint4*>(vb + t * kv_stride_t + i * 8);
       }
     }
   };
-  load_rows(t_begin + warp * 4 + rgrp);
-  for (int tb = t_begin + warp * 4; tb < t_end; tb += 16) {
-    const int t = tb + rgrp;
+  auto process = [&](const uint4 (&kr)[kV], const uint4 (&vr)[kV], int t) {
     const bool valid = t < t_end;
-    uint4 kr[DPL / 8], vr[DPL / 8];
-#pragma unroll
-    for (int i = 0; i < DPL / 8; ++i) {
-      kr[i] = kn[i];
-      vr[i] = vn[i];
-    }
-    load_rows(t + 16);
     float kf[DPL], vf[DPL];
 #pragma unroll
-    for (int i = 0; i < DPL / 8; ++i) {
+    for (int i = 0; i < kV; ++i) {
       const uint32_t kw[4] = {kr[i].x, kr[i].y, kr[i].z, kr[i].w};
       const uint32_t vw[4] = {vr[i].x, vr[i].y, vr[i].z, vr[i].w};
 #pragma unroll
@@ -134,6 +127,22 @@ decode_attn_partial_kernel(const __nv_bfloat16* __restrict__ q, long long q_stri
         }
       }
     }
+  };
+  const int t_first = t_begin + warp * 4 + rgrp;
+  load_rows(t_first, 0);
+  load_rows(t_first + 16, 1);
+  for (int tb = t_begin + warp * 4; tb < t_end; tb += 32) {
+    const int t = tb + rgrp;
+    uint4 k0[kV], v0[kV], k1[kV], v1[kV];
+#pragma unroll
+    for (int i = 0; i < kV; ++i) {
+      k0[i] = kn[0][i]; v0[i] = vn[0][i];
+      k1[i] = kn[1][i]; v1[i] = vn[1][i];
+    }
+    load_rows(t + 32, 0);
+    load_rows(t + 48, 1);
+    process(k0, v0, t);
+    process(k1, v1, t + 16);
   }
 
   // merge the 16 row streams of the block (4 warps x 4 lane groups) in shared memory
