@@ -19,6 +19,7 @@ SIGNATURES = {
     "cd_error_string": (c_char_p, [c_int]),
     "cd_last_cuda_error": (c_char_p, []),
     "cd_status_fetch": (c_int, [ctypes.POINTER(c_int)]),
+    "cd_selftest_wait_timeout": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "cd_route_workspace_bytes": (c_size_t, [c_int, c_int]),
     "cd_route": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
                          c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),

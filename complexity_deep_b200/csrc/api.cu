@@ -50,6 +50,25 @@ int cd_status_fetch(int* h_status) {
   return CD_OK;
 }
 
+int cd_selftest_wait_timeout(const void* a, const void* b, void* out, int limit_ms, void* stream) {
+  if (!a || !b || !out || limit_ms < 1 || limit_ms > 1000) return CD_ERR_INVALID;
+  GemmOperand op0{};
+  op0.a = a;
+  op0.lda = 64;
+  op0.b = b;
+  op0.ldb = 64;
+  op0.b_rows = 128;
+  op0.K = 64;
+  GemmEpilogueArgs epi{};
+  epi.kind = kEpiStore;
+  epi.out = out;
+  epi.ldo = 128;
+  epi.out_cols = 128;
+  epi.selftest_stall = 1;
+  epi.wait_limit_ns = static_cast<unsigned long long>(limit_ms) * 1000000ull;
+  return launch_gemm(128, 128, 1, nullptr, op0, nullptr, epi, 128, as_stream(stream));
+}
+
 size_t cd_route_workspace_bytes(int T, int E) {
   if (T < 0 || E < 1) return 0;
   return route_workspace_bytes(T, E);

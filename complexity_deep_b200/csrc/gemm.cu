@@ -261,6 +261,8 @@ int launch_gemm(int M, int N, int num_groups, const int* seg_offsets, const Gemm
   p.rope_pos0 = epi.rope_pos0;
   p.rope_q_cols = epi.rope_q_cols;
   p.rope_cols = epi.rope_cols;
+  p.selftest_stall = epi.selftest_stall;
+  p.wait_limit_ns = epi.wait_limit_ns;
   p.status = di->status;
 
   // Upper bound of the tile count without reading the segment sizes (they live on the

@@ -75,6 +75,11 @@ struct GemmParams {
   int rope_S, rope_pos0;   // row r sits at position rope_pos0 + r % rope_S
   int rope_q_cols;         // columns [0, rope_q_cols) are q heads, [rope_q_cols, rope_cols) k heads
   int rope_cols;
+  // self-test of the failure path: with `selftest_stall` the producer issues no loads, so the
+  // pipeline waits run into `wait_limit_ns` (0 = the default limit) and the kernel must leave
+  // cleanly with the status word raised
+  unsigned long long wait_limit_ns;
+  int selftest_stall;
   int* status;             // device word; set non-zero when a bounded wait ran out
 };
 
@@ -187,6 +192,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
   const int kb0 = (p.K0 + kBlockK - 1) / kBlockK;
   const int kb1 = (p.K1 + kBlockK - 1) / kBlockK;
   const int kb_total = kb0 + kb1;
+  const uint64_t wait_limit = p.wait_limit_ns ? p.wait_limit_ns : kWaitLimitNs;
 
   // ---------------------------------------------------------------- set-up
   if (warp == 0 && lane == 0) {
@@ -248,12 +254,13 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
         for (int kb = 0; kb < kb_total; ++kb, ++it) {
           const uint32_t s = it % S;
           const uint32_t ph = (it / S) & 1u;
-          if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) {
+          if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag, wait_limit)) {
             ok = false;
             break;
           }
           uint8_t* a_dst = smem + s * L::kStageBytes;
           uint8_t* b_dst = a_dst + L::kABytes;
+          if (p.selftest_stall) continue;  // nothing is loaded: the consumers' waits must expire
           if constexpr (CG == 2) {
             // the leader's barrier collects the bytes of both CTAs
             if (crank == 0) mbar_arrive_expect_tx(&full_bar[s], 2 * L::kStageBytes);
@@ -283,7 +290,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
         const uint32_t filled = it < static_cast<uint32_t>(S) ? it : static_cast<uint32_t>(S);
         for (uint32_t d = 0; d < filled && ok; ++d) {
           const uint32_t j = it - filled + d;  // the last `filled` fills
-          ok = mbar_wait(&empty_bar[j % S], (j / S) & 1u, abort_flag);
+          ok = mbar_wait(&empty_bar[j % S], (j / S) & 1u, abort_flag, wait_limit);
         }
       }
     }
@@ -298,7 +305,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
       for (int t = tile0; t < total_tiles && ok; t += tstride, ++tcount) {
         const uint32_t acc = tcount & 1u;
         const uint32_t acc_ph = (tcount >> 1) & 1u;
-        if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1u, abort_flag)) {
+        if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1u, abort_flag, wait_limit)) {
           ok = false;
           break;
         }
@@ -307,7 +314,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
         for (int kb = 0; kb < kb_total; ++kb, ++it) {
           const uint32_t s = it % S;
           const uint32_t ph = (it / S) & 1u;
-          if (!mbar_wait(&full_bar[s], ph, abort_flag)) {
+          if (!mbar_wait(&full_bar[s], ph, abort_flag, wait_limit)) {
             ok = false;
             break;
           }
@@ -418,7 +425,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
         }
       }
 
-      if (!mbar_wait(&tmem_full[acc], acc_ph, abort_flag)) {
+      if (!mbar_wait(&tmem_full[acc], acc_ph, abort_flag, wait_limit)) {
         ok = false;
         break;
       }

@@ -56,6 +56,9 @@ struct GemmEpilogueArgs {
   float bias_lo, bias_hi;
   int do_clamp;
   float clamp_lo, clamp_hi;
+  // failure-path self-test (see GemmParams)
+  int selftest_stall;
+  unsigned long long wait_limit_ns;
   // optional fused Q/K RMSNorm + RoPE (see GemmParams)
   const float* rope_cos;
   const float* rope_sin;

@@ -72,7 +72,8 @@ constexpr uint64_t kWaitLimitNs = 2000ull * 1000ull * 1000ull;
 // and leaves its loop). `abort_flag` (shared memory) lets the other roles stop early
 // once one of them gave up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
-                                          volatile int* abort_flag) {
+                                          volatile int* abort_flag,
+                                          uint64_t limit_ns = kWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   uint32_t spins = 0;
@@ -80,7 +81,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 0x3ffu) == 0) {
       if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) {
+      if (global_timer_ns() - t0 > limit_ns) {
         *abort_flag = 1;
         return false;
       }

@@ -43,6 +43,13 @@ const char* cd_last_cuda_error(void);
  * (0 = every bounded wait completed) and clears it. */
 int cd_status_fetch(int* h_status);
 
+/* Self-test of the kernels' failure detection (no counterpart in the reference).  Every wait of
+ * the GEMM pipeline is bounded; this launches one 128 x 128 x 64 tile whose loader is switched
+ * off, with the limit set to limit_ms (1..1000): the kernel must give up, free its resources and
+ * return, after which cd_status_fetch reports 1 and the device remains usable.  Nothing faults,
+ * traps or spins forever.  a, b: [128, 64] bf16, out: [128, 128] bf16 (contents unspecified). */
+int cd_selftest_wait_timeout(const void* a, const void* b, void* out, int limit_ms, void* stream);
+
 /* ---- dispatch -------------------------------------------------------------------------
  * Replaces TokenRoutedMLP.forward's lookup and mask loop,
  * complexity_deep/core/token_routed_mlp.py:149-150 (clamp + table lookup) and :166-170,

@@ -240,3 +240,36 @@ def test_mu_qkv_with_fused_qk_norm_rope(T, S, pos0, norm, with_mu):
     _close(out[:, : hq * D], q.reshape(T, -1))
     _close(out[:, hq * D:(hq + hkv) * D], k.reshape(T, -1))
     _close(out[:, (hq + hkv) * D:], ref[:, (hq + hkv) * D:])
+
+
+def test_bounded_waits_report_a_stalled_pipeline_and_leave_the_device_usable():
+    """Failure detection without a fault: a tile whose loader is switched off makes the pipeline
+    waits run into a 20 ms limit; the kernel returns, the status word is raised once, and the
+    next GEMM on the same context is correct."""
+    import ctypes
+    import time
+    from complexity_deep_b200 import _lib, ops
+    lib = _lib.load()
+    a = torch.zeros(128, 64, dtype=BF, device="cuda")
+    b = torch.zeros(128, 64, dtype=BF, device="cuda")
+    out = torch.zeros(128, 128, dtype=BF, device="cuda")
+    ops.status_fetch()                                            # clean before the test
+    t0 = time.perf_counter()
+    _lib.check(lib.cd_selftest_wait_timeout(a.data_ptr(), b.data_ptr(), out.data_ptr(), 20,
+                                            torch.cuda.current_stream().cuda_stream), "selftest")
+    st = ctypes.c_int(0)
+    _lib.check(lib.cd_status_fetch(ctypes.byref(st)), "cd_status_fetch")
+    elapsed = time.perf_counter() - t0
+    assert st.value == 1                                          # the wait ran out and said so
+    assert elapsed < 1.0                                          # bounded: ~20 ms, not seconds
+    _lib.check(lib.cd_status_fetch(ctypes.byref(st)), "cd_status_fetch")
+    assert st.value == 0                                          # cleared by the first read
+    with pytest.raises(_lib.CdeepError):                          # the Python layer raises on it
+        _lib.check(lib.cd_selftest_wait_timeout(a.data_ptr(), b.data_ptr(), out.data_ptr(), 20,
+                                                torch.cuda.current_stream().cuda_stream), "st")
+        ops.status_fetch()
+    g = torch.Generator().manual_seed(3)                          # the context still works
+    x, w = _rand(g, 300, 256), _rand(g, 512, 256, scale=0.05)
+    y = ops.linear(x.cuda(), w.cuda())
+    _fetch()
+    _close(y, x.float() @ w.float().t())
