@@ -34,8 +34,8 @@ MODEL = dict(vocab_size=32000, hidden_size=2048, intermediate_size=5632, num_hid
              num_attention_heads=16, num_key_value_heads=8, num_experts=8)
 GLOBAL_BATCH, SEQ_LEN = 32, 2048
 # DRAM traffic of one cd_mu_qkv launch per token, from the ncu capture summarised in
-# profiles/gemm_bf16_sm100_1b_layer_small_case.md (719 MB at 24 576 tokens)
-MU_QKV_DRAM_BYTES_PER_TOKEN = 719.15e6 / 24576
+# profiles/gemm_bf16_sm100_1b_layer_small_case.md (562 + 182 MB at 24 576 tokens)
+MU_QKV_DRAM_BYTES_PER_TOKEN = 743.43e6 / 24576
 
 
 def zipf_probabilities(vocab_size: int, s: float) -> torch.Tensor:
@@ -317,8 +317,8 @@ def run_ours(args):
                     "ms_per_launch": round(k["ms_total"] / k["launches"], 4),
                     "traffic": (round(MU_QKV_DRAM_BYTES_PER_TOKEN * local_tokens)
                                 if dom == "mu_qkv" else None),
-                    "traffic_source": "ncu dram__bytes_read+write of cd_mu_qkv at 24576 tokens "
-                                      "(719 MB), scaled per token; profiles/"}
+                    "traffic_source": "ncu dram__bytes_read+write of cd_mu_qkv_rope at 24576 tokens "
+                                      "(743 MB), scaled per token; profiles/"}
     gpu_launches = sum(v[2] for v in prof.values())
 
     line = {
@@ -546,12 +546,16 @@ def run_layer(args):
 
 def run_decode(args):
     """1B-class decode: concurrent sequences with a prefilled KV cache
-    of 4096 tokens (values N(0,1) bf16), one new Zipf token per sequence per step, an all-zero
-    additive mask so the new token attends to the whole cache.  The batch (256 sequences) is
-    split data-parallel; reports decode tokens/s and the weight-streaming rate of the GEMM
-    entry points (HBM-bound at this M)."""
+    of 4096 tokens (values N(0,1) bf16), one new Zipf token per sequence per step, the new
+    token attending to the whole cache.  The batch (256 sequences) is split data-parallel.
+    Two timed loops over the same caches: the reference's calling convention (growing cache,
+    all-zero additive mask) issued eagerly with events around every entry point -> `kernels`,
+    `ms_per_step_eager`; and the fixed-launch step replayed from its CUDA graph
+    (`DecodeGraph`) -> `value`, plus `e2e` with ids from pinned host memory and the argmax
+    read back."""
     from complexity_deep_b200 import ops
     from complexity_deep_b200.core.attention import _KVBuffer
+    from complexity_deep_b200.models import DecodeGraph
     rank = int(os.environ.get("RANK", 0))
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
@@ -571,21 +575,22 @@ def run_decode(args):
     steps_total = args.warmup + args.steps
     gen = torch.Generator(device=dev).manual_seed(1 + rank)
 
-    def cache_tensor():
-        # a cache as a prefill through this model would leave it: a view of a buffer with room
-        # to grow, so decode steps append in place
-        buf = torch.empty(B, hkv, P + steps_total + 8, D, dtype=torch.bfloat16, device=dev)
-        buf.normal_(0.0, 1.0, generator=gen)
+    # one set of buffers serves both loops: the growing-cache loop appends in place into them
+    dec = DecodeGraph(model, batch=B, capacity=P + steps_total + 8)
+    for t in dec.cache.k + dec.cache.v:
+        t.normal_(0.0, 1.0, generator=gen)
+
+    def growing_view(buf):
         view = buf[:, :, :P]
         view._cd_kv = _KVBuffer(buf, P)
         return view
 
-    past = [(cache_tensor(), cache_tensor()) for _ in range(L)]
     ids = zipf_token_ids(cfg["vocab_size"], 1.1, batch * steps_total, seed=0).view(steps_total, batch)
-    ids = ids[:, lo:hi].contiguous().to(dev)
+    ids_host = ids[:, lo:hi].contiguous().pin_memory()
+    ids = ids_host.to(dev)
 
     @torch.no_grad()
-    def step(i, past):
+    def step_eager(i, past):
         kv_len = past[0][0].shape[2] + 1
         mask = torch.zeros(B, 1, 1, kv_len, dtype=torch.bfloat16, device=dev)
         out = model(ids[i].view(B, 1), attention_mask=mask, past_key_values=past, use_cache=True)
@@ -596,23 +601,46 @@ def run_decode(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for i in range(args.warmup):
-        _, past = step(i, past)
-    barrier()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
-    ops.PROFILE.reset(enabled=True)
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0.record()
-    for i in range(args.warmup, steps_total):
-        _, past = step(i, past)
-    t1.record()
-    barrier()
-    ms = aggregate_ms(t0.elapsed_time(t1), dist, dev)
-    clocks = sampler.stop()
-    prof = ops.PROFILE.collect()
-    ops.PROFILE.reset(enabled=False)
-    ops.status_fetch()
+    def timed(step_fn, instrument):
+        for i in range(args.warmup):
+            step_fn(i)
+        barrier()
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        ops.PROFILE.reset(enabled=instrument)
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for i in range(args.warmup, steps_total):
+            step_fn(i)
+        t1.record()
+        barrier()
+        ms = aggregate_ms(t0.elapsed_time(t1), dist, dev)
+        clocks = sampler.stop()
+        prof = ops.PROFILE.collect() if instrument else {}
+        ops.PROFILE.reset(enabled=False)
+        ops.status_fetch()
+        return ms, clocks, prof
+
+    state = {"past": [(growing_view(k), growing_view(v)) for k, v in zip(dec.cache.k, dec.cache.v)]}
+
+    def eager(i):
+        _, state["past"] = step_eager(i, state["past"])
+
+    ms_eager, _, prof = timed(eager, True)
+    state.clear()
+
+    dec.cache.set_length(P)
+    ms, clocks, _ = timed(lambda i: dec.step(ids[i]), False)
+
+    dec.cache.set_length(P)
+    next_host = torch.empty(B, dtype=torch.int64).pin_memory()
+
+    def step_e2e(i):
+        logits = dec.step(ids_host[i].to(dev, non_blocking=True))
+        next_host.copy_(logits[:, -1].argmax(-1), non_blocking=True)
+
+    ms_e2e, _, _ = timed(step_e2e, False)
+
     H, V, E = cfg["hidden_size"], cfg["vocab_size"], cfg["num_experts"]
     I_e = cfg["intermediate_size"] // E
     nqkv = (cfg["num_attention_heads"] + 2 * hkv) * D
@@ -629,16 +657,23 @@ def run_decode(args):
             entry.update(weight_gbs=round(gbs, 1), frac_of_hbm=round(gbs / pk["hbm_gbs"], 4))
         kernels[name] = entry
     cache_bytes = 2 * L * B * hkv * (P + steps_total / 2) * D * 2
+    floor_w = sum(weight_bytes[k] * (L if k != "linear_lm_head" else 1) for k in weight_bytes)
     line = {
         "metric": "decode tokens/s (1B bf16)", "value": round(batch * args.steps / (ms / 1e3), 1),
         "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": round(ms / args.steps, 3), "higher_is_better": True, "scaling": "strong",
+        "ms_per_step": round(ms / args.steps, 3),
+        "ms_per_step_eager": round(ms_eager / args.steps, 3),
+        "forward": "cuda_graph_replay (DecodeGraph); eager = growing cache + zero additive mask",
+        "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "b200",
-        "config": {"workload": f"1B-class decode, {batch} sequences, KV cache {P} tokens, zero additive mask",
+        "config": {"workload": f"1B-class decode, {batch} sequences, KV cache {P} tokens, whole cache attended",
                    "parallelism": f"dp{world}", "sequences_per_gpu": B},
-        "hbm_floor_ms": {"weights": round(sum(weight_bytes[k] * (L if k != "linear_lm_head" else 1)
-                                              for k in weight_bytes) / pk["hbm_gbs"] / 1e6, 3),
+        "e2e": {"value": round(batch * args.steps / (ms_e2e / 1e3), 1), "unit": "tokens/s",
+                "h2d_bytes_per_step": B * 8, "d2h_bytes_per_step": B * 8,
+                "api": "DecodeGraph(model, batch, capacity).step(ids)"},
+        "hbm_floor_ms": {"weights": round(floor_w / pk["hbm_gbs"] / 1e6, 3),
                          "kv_cache": round(cache_bytes / pk["hbm_gbs"] / 1e6, 3)},
+        "frac_of_hbm_floor": round((floor_w + cache_bytes) / pk["hbm_gbs"] / 1e6 / (ms / args.steps), 4),
         "clocks": clocks, "gpu_launches": sum(v[2] for v in prof.values()), "kernels": kernels,
     }
     if rank == 0:

@@ -11,7 +11,7 @@ from ctypes import c_char_p, c_float, c_int, c_longlong, c_size_t, c_void_p
 
 LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libcdeep.so")
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 # name -> (restype, argtypes); mirrors include/cdeep.h one to one
 SIGNATURES = {
@@ -31,11 +31,14 @@ SIGNATURES = {
     "cd_gather_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "cd_qk_norm_rope": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int,
                                 c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "cd_decode_rope_append": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float,
+                                      c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_longlong,
+                                      c_longlong, c_longlong, c_int, c_void_p, c_void_p]),
     "cd_decode_attention_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "cd_decode_attention": (c_int, [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong,
                                     c_longlong, c_longlong, c_void_p, c_longlong, c_float, c_int,
-                                    c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_size_t,
-                                    c_void_p]),
+                                    c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                                    c_size_t, c_void_p]),
     "cd_gate_up_packed_rows": (c_int, [c_int, c_int]),
     "cd_moe_up": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
                           c_int, c_void_p]),

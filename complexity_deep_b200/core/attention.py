@@ -59,6 +59,69 @@ def _kv_append(past: torch.Tensor, new: torch.Tensor) -> torch.Tensor:
     return out
 
 
+class StaticKVCache:
+    """Fixed-capacity KV cache of a whole model for decode steps whose launches never change.
+
+    The reference's cache is a list of ``(k, v)`` tensors that grow by ``torch.cat``
+    (attention.py:158-161), so every step has new shapes and addresses.  Here each layer owns
+    ``k`` / ``v`` buffers ``[batch, kv_heads, capacity, head_dim]`` and the number of cached
+    tokens lives in DEVICE memory (``state[0]``; ``state[1]`` = that + 1, the keys a step sees
+    after appending its own).  A decode step through ``model(ids, past_key_values=cache.layers,
+    use_cache=True)`` then issues exactly the same launches at every length, which is what a
+    CUDA graph needs (see ``DecodeGraph``).  Steps attend to the whole cache — what the
+    reference computes when it is given an all-zero additive mask.  Not part of the
+    reference's API.
+    """
+
+    def __init__(self, num_layers: int, batch: int, kv_heads: int, head_dim: int, capacity: int,
+                 device, dtype=torch.bfloat16) -> None:
+        self.capacity = capacity
+        self.k = [torch.zeros(batch, kv_heads, capacity, head_dim, dtype=dtype, device=device)
+                  for _ in range(num_layers)]
+        self.v = [torch.zeros_like(t) for t in self.k]
+        self.state = torch.zeros(2, dtype=torch.int32, device=device)
+        self.state[1] = 1
+        self.length = 0                       # host mirror of state[0]
+        self.layers = [StaticKVLayer(self, i) for i in range(num_layers)]
+
+    def load(self, past_key_values) -> None:
+        """Copies a cache produced by a prefill (list of (k, v) [B, kv_heads, P, D])."""
+        P = past_key_values[0][0].shape[2]
+        if P > self.capacity:
+            raise ValueError(f"{P} cached tokens do not fit a capacity of {self.capacity}")
+        for i, (k, v) in enumerate(past_key_values):
+            self.k[i][:, :, :P].copy_(k)
+            self.v[i][:, :, :P].copy_(v)
+        self.set_length(P)
+
+    def set_length(self, length: int) -> None:
+        if not 0 <= length <= self.capacity:
+            raise ValueError("length outside the cache")
+        self.length = length
+        self.state.copy_(torch.tensor([length, length + 1], dtype=torch.int32), non_blocking=False)
+
+    def advance(self) -> None:
+        """One token was appended to every layer: move the device-side position (stream
+        ordered, capturable) and its host mirror."""
+        self.state.add_(1)
+        self.length += 1
+
+
+class StaticKVLayer:
+    """One layer's slice of a StaticKVCache, passed as that layer's ``past_key_value``."""
+
+    def __init__(self, cache: StaticKVCache, index: int) -> None:
+        self.cache, self.index = cache, index
+
+    @property
+    def k(self) -> torch.Tensor:
+        return self.cache.k[self.index]
+
+    @property
+    def v(self) -> torch.Tensor:
+        return self.cache.v[self.index]
+
+
 class ComplexityAttention(nn.Module):
     def __init__(
         self,
@@ -117,6 +180,9 @@ class ComplexityAttention(nn.Module):
         mu2 = None
         if mu_prev is not None:
             mu2 = mu_prev.reshape(B * S, H).contiguous()  # materialises a broadcast mu_init
+        if isinstance(past_key_value, StaticKVLayer):
+            return (self._attend_static(x2, mu2, past_key_value, S, attention_mask),
+                    past_key_value if use_cache else None)
         past_len = past_key_value[0].shape[2] if past_key_value is not None else 0
         cos, sin = self.rotary_emb.tables_fp32(past_len + S)
         qkv = ops.mu_qkv_rope(x2, mu2, self._w_qkv(), self._w_mu() if mu2 is not None else None,
@@ -151,6 +217,26 @@ class ComplexityAttention(nn.Module):
             )
             attn = attn.transpose(1, 2).reshape(B * S, hq * D).contiguous()
         return attn, new_kv
+
+    def _attend_static(self, x2, mu2, past: StaticKVLayer, S, attention_mask) -> torch.Tensor:
+        """Decode step on a StaticKVCache: projection, then one kernel that normalises and
+        rotates q / k at the device-side position and appends k / v to the cache, then the
+        split-KV attention over the device-side length."""
+        hq, hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
+        if S != 1 or attention_mask is not None:
+            raise RuntimeError("a StaticKVCache takes one new token per sequence and no mask "
+                               "(steps attend to the whole cache)")
+        if D not in (64, 128) or self.num_kv_groups > 4:
+            raise RuntimeError("StaticKVCache decode needs head size 64 or 128 and at most 4 "
+                               "query heads per KV head")
+        cache = past.cache
+        cos, sin = self.rotary_emb.tables_fp32(cache.capacity)
+        qkv = ops.mu_qkv(x2, mu2, self._w_qkv(), self._w_mu() if mu2 is not None else None)
+        ops.decode_rope_append(qkv, self.q_norm.weight if self.use_qk_norm else None,
+                               self.k_norm.weight if self.use_qk_norm else None, cos, sin, 1e-6,
+                               hq, hkv, D, past.k, past.v, cache.state[0:1])
+        return ops.decode_attention(qkv, past.k, past.v, None, hq, hkv, D,
+                                    kv_len_dev=cache.state[1:2])
 
     def _decode_kernel_applies(self, S, attention_mask, k, v) -> bool:
         if S != 1 or self.head_dim not in (64, 128) or self.num_kv_groups > 4:

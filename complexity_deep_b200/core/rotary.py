@@ -43,7 +43,10 @@ class RotaryEmbedding(nn.Module):
             if self.inv_freq.dtype != torch.float32:
                 exponents = torch.arange(0, self.dim, 2, device=self.inv_freq.device).float()
                 self.inv_freq = 1.0 / (self.theta ** (exponents / self.dim))
-            self.max_seq_len = max(seq_len, self.max_seq_len)
+            if seq_len > self.max_seq_len:
+                # grow geometrically: decode steps past the configured maximum must not
+                # rebuild the tables on every step
+                self.max_seq_len = 1 << (seq_len - 1).bit_length()
             self._build_cache(self.max_seq_len)
         return self.cos_cached, self.sin_cached
 

@@ -20,7 +20,7 @@ static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t
 
 extern "C" {
 
-int cd_version(void) { return 1; }
+int cd_version(void) { return 2; }
 
 const char* cd_error_string(int status) {
   switch (status) {
@@ -119,6 +119,23 @@ int cd_qk_norm_rope(void* qkv, const void* q_w, const void* k_w, const float* co
   return e == cudaSuccess ? CD_OK : cuda_fail(e, "qk_norm_rope launch");
 }
 
+int cd_decode_rope_append(void* qkv, const void* q_w, const void* k_w, const float* cos_t,
+                          const float* sin_t, float eps, int B, int hq, int hkv, int D,
+                          void* k_cache, void* v_cache, long long kv_stride_b,
+                          long long kv_stride_h, long long kv_stride_t, int capacity,
+                          const int32_t* pos_dev, void* stream) {
+  if (B < 0 || hq < 1 || hkv < 1 || D < 8 || (D & 7) || capacity < 1) return CD_ERR_INVALID;
+  if (!cos_t || !sin_t || !pos_dev || !k_cache || !v_cache || (B > 0 && !qkv))
+    return CD_ERR_INVALID;
+  if ((q_w == nullptr) != (k_w == nullptr)) return CD_ERR_INVALID;
+  if (!aligned16(qkv) || !aligned16(k_cache) || !aligned16(v_cache)) return CD_ERR_INVALID;
+  if ((kv_stride_b & 7) || (kv_stride_h & 7) || (kv_stride_t & 7)) return CD_ERR_INVALID;
+  cudaError_t e = launch_qk_norm_rope(qkv, q_w, k_w, cos_t, sin_t, eps, B, 1, 0, hq, hkv, D,
+                                      as_stream(stream), pos_dev, k_cache, v_cache, kv_stride_b,
+                                      kv_stride_h, kv_stride_t, capacity);
+  return e == cudaSuccess ? CD_OK : cuda_fail(e, "decode rope/append launch");
+}
+
 size_t cd_decode_attention_workspace_bytes(int B, int hq, int hkv, int L, int D) {
   if (B < 1 || hq < 1 || hkv < 1 || L < 1 || D < 1 || hq % hkv) return 0;
   return decode_attention_workspace_bytes(B, hq, hkv, L, D);
@@ -127,7 +144,8 @@ size_t cd_decode_attention_workspace_bytes(int B, int hq, int hkv, int L, int D)
 int cd_decode_attention(const void* q, long long q_stride_b, const void* k, const void* v,
                         long long kv_stride_b, long long kv_stride_h, long long kv_stride_t,
                         const void* mask, long long mask_stride_b, float scale, int B, int hq,
-                        int hkv, int L, int D, void* out, void* ws, size_t ws_bytes, void* stream) {
+                        int hkv, int L, const int32_t* kv_len_dev, int D, void* out, void* ws,
+                        size_t ws_bytes, void* stream) {
   if (B < 1 || hq < 1 || hkv < 1 || L < 1 || hq % hkv) return CD_ERR_INVALID;
   if (D != 64 && D != 128) return CD_ERR_UNSUPPORTED;
   if (hq / hkv > 4) return CD_ERR_UNSUPPORTED;
@@ -138,7 +156,7 @@ int cd_decode_attention(const void* q, long long q_stride_b, const void* k, cons
   if (ws_bytes < decode_attention_workspace_bytes(B, hq, hkv, L, D)) return CD_ERR_INVALID;
   cudaError_t e = launch_decode_attention(q, q_stride_b, k, v, kv_stride_b, kv_stride_h,
                                           kv_stride_t, mask, mask_stride_b, scale, B, hq, hkv, L,
-                                          D, out, ws, as_stream(stream));
+                                          D, out, ws, as_stream(stream), kv_len_dev);
   return e == cudaSuccess ? CD_OK : cuda_fail(e, "decode attention launch");
 }
 

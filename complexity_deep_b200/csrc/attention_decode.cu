@@ -28,7 +28,25 @@ constexpr int kLanesPerRow = 8;
 __device__ __forceinline__ float lo_f(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float hi_f(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
 
+// Blocks per (batch, kv head) pair.  Also evaluated on the device when the cache length is
+// read from device memory, so both forms split (and therefore round) identically.
+__host__ __device__ inline int choose_splits(int B, int hkv, int L) {
+  const int pairs = B * hkv;
+  int splits = (16 * 148 + pairs - 1) / pairs;      // several waves of blocks: small tail
+  const int max_splits = (L + 255) / 256;           // at least 256 rows per block
+  if (splits > max_splits) splits = max_splits;
+  if (splits < 1) splits = 1;
+  if (splits > 64) splits = 64;
+  return splits;
+}
+
+__host__ __device__ inline int chunk_rows(int L, int splits) {
+  return (((L + splits - 1) / splits) + 15) / 16 * 16;
+}
+
 // DPL = dimensions per lane = D / 8 (8 or 16 -> D = 64 or 128), G = query heads per KV head.
+// len_dev (optional): the number of cached rows is min(L, *len_dev) and the split of the rows
+// over blocks is recomputed from it; the grid and the workspace layout stay those of L.
 template <int DPL, int G>
 __global__ void __launch_bounds__(kAttnThreads)
 decode_attn_partial_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride_b,
@@ -36,10 +54,16 @@ decode_attn_partial_kernel(const __nv_bfloat16* __restrict__ q, long long q_stri
                            long long kv_stride_b, long long kv_stride_h, long long kv_stride_t,
                            const __nv_bfloat16* __restrict__ mask, long long mask_stride_b,
                            float scale, int L, int chunk, int hq, float* __restrict__ part_acc,
-                           float* __restrict__ part_ml) {
+                           float* __restrict__ part_ml, const int* __restrict__ len_dev) {
   constexpr int D = DPL * kLanesPerRow;
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int splits = gridDim.x;
+  if (len_dev) {
+    L = max(0, min(L, __ldg(len_dev)));
+    const int live = choose_splits(gridDim.z, gridDim.y, L);
+    if (split >= live) return;       // whole block; the combine kernel skips these slots
+    chunk = chunk_rows(L, live);
+  }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int sub = lane & 7;          // which D/8 slice of the row
   const int rgrp = lane >> 3;        // which of the warp's 4 concurrent rows
@@ -183,8 +207,10 @@ decode_attn_partial_kernel(const __nv_bfloat16* __restrict__ q, long long q_stri
 // out[b, h, :] = sum_s w_s acc_s / sum_s w_s l_s, w_s = exp(m_s - max m)
 __global__ void __launch_bounds__(128)
 decode_attn_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
-                           int splits, int D, __nv_bfloat16* __restrict__ out) {
+                           int splits, int D, __nv_bfloat16* __restrict__ out, int B, int hkv,
+                           int L, const int* __restrict__ len_dev) {
   const long long row0 = static_cast<long long>(blockIdx.x) * splits;   // (b, h)
+  if (len_dev) splits = choose_splits(B, hkv, max(0, min(L, __ldg(len_dev))));
   float m = -FLT_MAX;
   for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[(row0 + s) * 2]);
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
@@ -199,26 +225,16 @@ decode_attn_combine_kernel(const float* __restrict__ part_acc, const float* __re
   }
 }
 
-int choose_splits(int B, int hkv, int L) {
-  const int pairs = B * hkv;
-  int splits = (16 * 148 + pairs - 1) / pairs;      // several waves of blocks: small tail
-  const int max_splits = (L + 255) / 256;           // at least 256 rows per block
-  if (splits > max_splits) splits = max_splits;
-  if (splits < 1) splits = 1;
-  if (splits > 64) splits = 64;
-  return splits;
-}
-
 template <int DPL>
 cudaError_t launch_partial(int G, dim3 grid, cudaStream_t st, const __nv_bfloat16* q,
                            long long qsb, const __nv_bfloat16* k, const __nv_bfloat16* v,
                            long long sb, long long sh, long long stt, const __nv_bfloat16* mask,
                            long long msb, float scale, int L, int chunk, int hq, float* pa,
-                           float* pml) {
+                           float* pml, const int* len_dev) {
 #define CDEEP_ATTN_CASE(GG)                                                                     \
   case GG:                                                                                      \
     decode_attn_partial_kernel<DPL, GG><<<grid, kAttnThreads, 0, st>>>(                         \
-        q, qsb, k, v, sb, sh, stt, mask, msb, scale, L, chunk, hq, pa, pml);                    \
+        q, qsb, k, v, sb, sh, stt, mask, msb, scale, L, chunk, hq, pa, pml, len_dev);                    \
     break;
   switch (G) {
     CDEEP_ATTN_CASE(1)
@@ -243,10 +259,11 @@ cudaError_t launch_decode_attention(const void* q, long long q_stride_b, const v
                                     const void* v, long long kv_stride_b, long long kv_stride_h,
                                     long long kv_stride_t, const void* mask,
                                     long long mask_stride_b, float scale, int B, int hq, int hkv,
-                                    int L, int D, void* out, void* ws, cudaStream_t stream) {
+                                    int L, int D, void* out, void* ws, cudaStream_t stream,
+                                    const int* kv_len_dev) {
   const int G = hq / hkv;
   const int splits = choose_splits(B, hkv, L);
-  const int chunk = (((L + splits - 1) / splits) + 15) / 16 * 16;
+  const int chunk = chunk_rows(L, splits);
   float* part_acc = static_cast<float*>(ws);
   float* part_ml = part_acc + static_cast<size_t>(B) * hq * splits * D;
   dim3 grid(splits, hkv, B);
@@ -257,15 +274,18 @@ cudaError_t launch_decode_attention(const void* q, long long q_stride_b, const v
   cudaError_t e;
   if (D == 128)
     e = launch_partial<16>(G, grid, stream, qb, q_stride_b, kb, vb, kv_stride_b, kv_stride_h,
-                           kv_stride_t, mb, mask_stride_b, scale, L, chunk, hq, part_acc, part_ml);
+                           kv_stride_t, mb, mask_stride_b, scale, L, chunk, hq, part_acc, part_ml,
+                           kv_len_dev);
   else if (D == 64)
     e = launch_partial<8>(G, grid, stream, qb, q_stride_b, kb, vb, kv_stride_b, kv_stride_h,
-                          kv_stride_t, mb, mask_stride_b, scale, L, chunk, hq, part_acc, part_ml);
+                          kv_stride_t, mb, mask_stride_b, scale, L, chunk, hq, part_acc, part_ml,
+                           kv_len_dev);
   else
     return cudaErrorInvalidValue;
   if (e != cudaSuccess) return e;
   decode_attn_combine_kernel<<<B * hq, 128, 0, stream>>>(part_acc, part_ml, splits, D,
-                                                        static_cast<__nv_bfloat16*>(out));
+                                                        static_cast<__nv_bfloat16*>(out), B, hkv,
+                                                        L, kv_len_dev);
   return cudaGetLastError();
 }
 

@@ -19,16 +19,22 @@ cudaError_t launch_push_rows(const void* x, const int* src_rows, const int* offs
                              const int* push_base, int E, int experts_per_rank,
                              const unsigned long long* peer_ptrs, int T, int H,
                              cudaStream_t stream);
+// pos_dev / k_cache / v_cache: decode-step form (position from device memory, rotated k and v
+// also written to the cache at that position); all null for the plain in-place form.
 cudaError_t launch_qk_norm_rope(void* qkv, const void* q_w, const void* k_w, const float* cos_t,
                                 const float* sin_t, float eps, int T, int S, int pos0, int hq,
-                                int hkv, int D, cudaStream_t stream);
+                                int hkv, int D, cudaStream_t stream, const int* pos_dev = nullptr,
+                                void* k_cache = nullptr, void* v_cache = nullptr,
+                                long long kv_stride_b = 0, long long kv_stride_h = 0,
+                                long long kv_stride_t = 0, int capacity = 0);
 
 size_t decode_attention_workspace_bytes(int B, int hq, int hkv, int L, int D);
 cudaError_t launch_decode_attention(const void* q, long long q_stride_b, const void* k,
                                     const void* v, long long kv_stride_b, long long kv_stride_h,
                                     long long kv_stride_t, const void* mask,
                                     long long mask_stride_b, float scale, int B, int hq, int hkv,
-                                    int L, int D, void* out, void* ws, cudaStream_t stream);
+                                    int L, int D, void* out, void* ws, cudaStream_t stream,
+                                    const int* kv_len_dev = nullptr);
 
 // One operand pair of the GEMM: row-major bf16 matrices with K contiguous.
 struct GemmOperand {

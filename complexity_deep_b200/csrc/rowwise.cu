@@ -186,11 +186,23 @@ push_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ sr
 // buffer: y = rmsnorm(head) * norm_w, then rotate-half RoPE with fp32 cos/sin tables
 // [positions, D].  Lane l owns the element pairs (2l', 2l'+1) of the first half together
 // with their partners D/2 further, so the rotation needs no shuffles.
+//
+// Decode-step form (`app.pos_dev` set, one row per sequence): the position of every row is
+// read from device memory, and the rotated k head and the v head of the row are also written
+// to the KV cache at that position (nothing is written when it is outside the cache).
+struct KvAppend {
+  const int* pos_dev;          // device scalar: position of the new token (null: use pos0)
+  __nv_bfloat16* k_cache;      // [B, hkv, capacity, D] with the strides below (null: no append)
+  __nv_bfloat16* v_cache;
+  long long stride_b, stride_h, stride_t;
+  int capacity;
+};
+
 __global__ void __launch_bounds__(256)
 qk_norm_rope_kernel(__nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ q_w,
                     const __nv_bfloat16* __restrict__ k_w, const float* __restrict__ cos_t,
                     const float* __restrict__ sin_t, float eps, int T, int S, int pos0, int hq,
-                    int hkv, int D) {
+                    int hkv, int D, KvAppend app) {
   const int heads = hq + hkv;
   const long long wid = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (wid >= static_cast<long long>(T) * heads) return;
@@ -201,9 +213,20 @@ qk_norm_rope_kernel(__nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __rest
   __nv_bfloat16* head = qkv + static_cast<size_t>(t) * ld + static_cast<size_t>(h) * D;
   const __nv_bfloat16* nw = (h < hq) ? q_w : k_w;
   const int half = D >> 1;
+  if (app.pos_dev) pos0 = __ldg(app.pos_dev);
   const int pos = pos0 + (t % S);
+  if (app.pos_dev && (pos < 0 || pos >= app.capacity)) return;
   const float* cs = cos_t + static_cast<size_t>(pos) * D;
   const float* sn = sin_t + static_cast<size_t>(pos) * D;
+  __nv_bfloat16* kdst = nullptr;
+  if (app.k_cache && h >= hq) {
+    const long long off = t * app.stride_b + (h - hq) * app.stride_h + pos * app.stride_t;
+    kdst = app.k_cache + off;
+    const __nv_bfloat16* vsrc = head + static_cast<size_t>(hkv) * D;   // the v head of this k head
+    __nv_bfloat16* vdst = app.v_cache + off;
+    for (int j = 2 * lane; j < D; j += 64)
+      *reinterpret_cast<uint32_t*>(vdst + j) = *reinterpret_cast<const uint32_t*>(vsrc + j);
+  }
 
   float ss = 0.f;
   for (int j = 2 * lane; j < half; j += 64) {
@@ -229,6 +252,10 @@ qk_norm_rope_kernel(__nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __rest
     const float o_b1 = b1 * cs[half + j + 1] + a1 * sn[half + j + 1];
     *reinterpret_cast<uint32_t*>(head + j) = pack2(o_a0, o_a1);
     *reinterpret_cast<uint32_t*>(head + half + j) = pack2(o_b0, o_b1);
+    if (kdst) {
+      *reinterpret_cast<uint32_t*>(kdst + j) = pack2(o_a0, o_a1);
+      *reinterpret_cast<uint32_t*>(kdst + half + j) = pack2(o_b0, o_b1);
+    }
   }
 }
 
@@ -237,12 +264,13 @@ qk_norm_rope_kernel(__nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __rest
 // first half and the 8 partner columns D/2 further, 16-byte accesses), the warp's 32 / (D/16)
 // lane groups take adjacent heads, and every lane walks over heads with the SAME column
 // chunk, so the cos/sin values of the token's position are loaded once and reused for all
-// its heads.
+// its heads.  kAppend: the decode-step form described at KvAppend (same arithmetic).
+template <bool kAppend>
 __global__ void __launch_bounds__(256, 2)
 qk_norm_rope_vec_kernel(__nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ q_w,
                         const __nv_bfloat16* __restrict__ k_w, const float* __restrict__ cos_t,
                         const float* __restrict__ sin_t, float eps, int T, int S, int pos0, int hq,
-                        int hkv, int D) {
+                        int hkv, int D, KvAppend app) {
   const int heads = hq + hkv;
   const int half = D >> 1;
   const int lph = half >> 3;        // lanes per head
@@ -252,7 +280,9 @@ qk_norm_rope_vec_kernel(__nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __
   const int lane = threadIdx.x & 31;
   const int g = lane / lph;
   const int j = (lane - g * lph) * 8;
+  if (kAppend && app.pos_dev) pos0 = __ldg(app.pos_dev);
   const int pos = pos0 + (t % S);
+  if (kAppend && (pos < 0 || pos >= app.capacity)) return;   // uniform: one position per call
   float c1[8], s1[8], c2[8], s2[8];
   {
     const float* cs = cos_t + static_cast<size_t>(pos) * D;
@@ -334,6 +364,21 @@ qk_norm_rope_vec_kernel(__nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __
       __nv_bfloat16* head = row + static_cast<size_t>(h) * D;
       *reinterpret_cast<uint4*>(head + j) = oa;
       *reinterpret_cast<uint4*>(head + half + j) = ob;
+      if (kAppend && h >= hq) {
+        __nv_bfloat16* kdst = app.k_cache + t * app.stride_b + (h - hq) * app.stride_h +
+                              pos * app.stride_t;
+        *reinterpret_cast<uint4*>(kdst + j) = oa;
+        *reinterpret_cast<uint4*>(kdst + half + j) = ob;
+      }
+    }
+  }
+  if (kAppend) {   // the row's v heads, 16 bytes per lane and step
+    const __nv_bfloat16* vsrc = row + static_cast<size_t>(heads) * D;
+    for (int c = lane * 8; c < hkv * D; c += 256) {
+      const int vh = c / D;
+      __nv_bfloat16* vdst = app.v_cache + t * app.stride_b + vh * app.stride_h +
+                            pos * app.stride_t + (c - vh * D);
+      *reinterpret_cast<uint4*>(vdst) = *reinterpret_cast<const uint4*>(vsrc + c);
     }
   }
 }
@@ -382,27 +427,40 @@ cudaError_t launch_push_rows(const void* x, const int* src_rows, const int* offs
 
 cudaError_t launch_qk_norm_rope(void* qkv, const void* q_w, const void* k_w, const float* cos_t,
                                 const float* sin_t, float eps, int T, int S, int pos0, int hq,
-                                int hkv, int D, cudaStream_t stream) {
+                                int hkv, int D, cudaStream_t stream, const int* pos_dev,
+                                void* k_cache, void* v_cache, long long kv_stride_b,
+                                long long kv_stride_h, long long kv_stride_t, int capacity) {
   if (T == 0) return cudaSuccess;
+  KvAppend app{pos_dev, static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache),
+               kv_stride_b, kv_stride_h, kv_stride_t, capacity};
+  const bool append = k_cache != nullptr;
   const int lph = D >> 4;
   const bool aligned = (reinterpret_cast<uintptr_t>(qkv) & 15) == 0 &&
                        (reinterpret_cast<uintptr_t>(cos_t) & 15) == 0 &&
                        (reinterpret_cast<uintptr_t>(sin_t) & 15) == 0 &&
                        (reinterpret_cast<uintptr_t>(q_w) & 15) == 0 &&
-                       (reinterpret_cast<uintptr_t>(k_w) & 15) == 0;
+                       (reinterpret_cast<uintptr_t>(k_w) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(k_cache) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(v_cache) & 15) == 0 &&
+                       ((kv_stride_b | kv_stride_h | kv_stride_t) & 7) == 0;
+  auto qb = static_cast<__nv_bfloat16*>(qkv);
+  auto qw = static_cast<const __nv_bfloat16*>(q_w);
+  auto kw = static_cast<const __nv_bfloat16*>(k_w);
   if ((D & 15) == 0 && lph >= 1 && lph <= 32 && (lph & (lph - 1)) == 0 && aligned) {
-    const int nblocks = (T + 7) / 8;  // one warp per token, 8 warps per block
-    qk_norm_rope_vec_kernel<<<static_cast<unsigned>(nblocks), 256, 0, stream>>>(
-        static_cast<__nv_bfloat16*>(qkv), static_cast<const __nv_bfloat16*>(q_w),
-        static_cast<const __nv_bfloat16*>(k_w), cos_t, sin_t, eps, T, S, pos0, hq, hkv, D);
+    const unsigned nblocks = static_cast<unsigned>((T + 7) / 8);  // one warp per token
+    if (append)
+      qk_norm_rope_vec_kernel<true><<<nblocks, 256, 0, stream>>>(qb, qw, kw, cos_t, sin_t, eps, T,
+                                                                 S, pos0, hq, hkv, D, app);
+    else
+      qk_norm_rope_vec_kernel<false><<<nblocks, 256, 0, stream>>>(qb, qw, kw, cos_t, sin_t, eps, T,
+                                                                  S, pos0, hq, hkv, D, app);
     return cudaGetLastError();
   }
   const long long warps = static_cast<long long>(T) * (hq + hkv);
   const int wpb = 8;
   const long long blocks = (warps + wpb - 1) / wpb;
   qk_norm_rope_kernel<<<static_cast<unsigned>(blocks), wpb * 32, 0, stream>>>(
-      static_cast<__nv_bfloat16*>(qkv), static_cast<const __nv_bfloat16*>(q_w),
-      static_cast<const __nv_bfloat16*>(k_w), cos_t, sin_t, eps, T, S, pos0, hq, hkv, D);
+      qb, qw, kw, cos_t, sin_t, eps, T, S, pos0, hq, hkv, D, app);
   return cudaGetLastError();
 }
 

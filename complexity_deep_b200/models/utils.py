@@ -69,6 +69,71 @@ class PrefillGraph:
         return self.static_logits
 
 
+class DecodeGraph:
+    """CUDA-graph replay of one decode step (one new token per sequence) on a StaticKVCache.
+
+    A decode step of the 1B model is ~270 launches of a few microseconds each, so the step
+    time is set by how fast the host can issue them.  The cache position is a device scalar
+    (see ``StaticKVCache``), so one captured step serves every length; a replay costs one
+    launch.  Steps attend to the whole cache (the reference's result for an all-zero additive
+    mask).  Not part of the reference's API.
+
+        dec = DecodeGraph(model, batch=32, capacity=prompt_len + max_new_tokens)
+        logits = dec.prefill(prompt_ids)     # ordinary forward; its cache is copied in
+        logits = dec.step(next_ids)          # [batch, 1, vocab], overwritten by the next step
+    """
+
+    def __init__(self, model: ComplexityModel, batch: int, capacity: int, warmup: int = 2):
+        import torch
+        from ..core.attention import StaticKVCache
+        from ..core.token_routed_mlp import ROUTING_CACHE
+        self.model = model
+        cfg = model.config
+        device = next(model.parameters()).device
+        if device.type != "cuda":
+            raise RuntimeError("DecodeGraph needs the model on a CUDA device")
+        self.cache = StaticKVCache(cfg.num_hidden_layers, batch, cfg.num_key_value_heads,
+                                   cfg.hidden_size // cfg.num_attention_heads, capacity, device,
+                                   dtype=next(model.parameters()).dtype)
+        self.static_ids = torch.zeros(batch, 1, dtype=torch.int64, device=device)
+        stream = torch.cuda.Stream(device=device)
+        stream.wait_stream(torch.cuda.current_stream(device))
+        with torch.no_grad(), torch.cuda.stream(stream):
+            for _ in range(warmup):       # builds the packed weights, sets kernel attributes
+                self._eager_step()
+        torch.cuda.current_stream(device).wait_stream(stream)
+        torch.cuda.synchronize(device)
+        self.static_ids.add_(0)           # fresh version: the capture must contain the dispatch
+        ROUTING_CACHE.clear()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.no_grad(), torch.cuda.graph(self.graph):
+            self.static_logits = self._eager_step()
+        ROUTING_CACHE.clear()             # its entries point into the graph's private pool
+        self.cache.set_length(0)          # the warm-up and capture steps wrote scratch rows
+
+    def _eager_step(self):
+        logits = self.model(self.static_ids, past_key_values=self.cache.layers,
+                            use_cache=True).logits
+        self.cache.state.add_(1)
+        return logits
+
+    def prefill(self, input_ids, attention_mask=None):
+        """Runs the prompt through the model and moves its KV cache into the static buffers."""
+        import torch
+        with torch.no_grad():
+            out = self.model(input_ids, attention_mask=attention_mask, use_cache=True)
+        self.cache.load(out.past_key_values)
+        return out.logits
+
+    def step(self, input_ids):
+        if self.cache.length >= self.cache.capacity:
+            raise RuntimeError(f"KV cache full ({self.cache.capacity} tokens)")
+        self.static_ids.copy_(input_ids.view(self.static_ids.shape), non_blocking=True)
+        self.graph.replay()
+        self.cache.length += 1
+        return self.static_logits
+
+
 def count_parameters(config: ComplexityConfig) -> dict:
     """Analytic parameter counts per component (shared expert as wide as one routed expert)."""
     H, I, V, L = (config.hidden_size, config.intermediate_size, config.vocab_size,

@@ -207,12 +207,49 @@ def qk_norm_rope_(qkv: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Optional[
     return qkv
 
 
+def decode_rope_append(qkv: torch.Tensor, q_w: Optional[torch.Tensor],
+                       k_w: Optional[torch.Tensor], cos: torch.Tensor, sin: torch.Tensor,
+                       eps: float, hq: int, hkv: int, head_dim: int, k_cache: torch.Tensor,
+                       v_cache: torch.Tensor, pos_dev: torch.Tensor) -> torch.Tensor:
+    """Decode step (one row of qkv per sequence): Q/K RMSNorm + RoPE in place at the position
+    held by the device scalar `pos_dev` (int32), and the row's rotated k and its v written
+    into k_cache / v_cache [B, hkv, capacity, D] at that position."""
+    lib = _lib.load()
+    _need(qkv, "qkv")
+    _need(cos, "cos", torch.float32)
+    _need(sin, "sin", torch.float32)
+    if q_w is not None:
+        _need(q_w, "q_norm.weight")
+        _need(k_w, "k_norm.weight")
+    B, D = qkv.shape[0], head_dim
+    cap = k_cache.shape[2]
+    if qkv.shape[1] != (hq + 2 * hkv) * D:
+        raise RuntimeError("qkv width does not match the head layout")
+    for t, name in ((k_cache, "k cache"), (v_cache, "v cache")):
+        if not t.is_cuda or t.dtype != BF16 or t.stride(-1) != 1 or tuple(t.shape) != (B, hkv, cap, D):
+            raise RuntimeError(f"{name}: expected a CUDA bf16 tensor [B, kv heads, capacity, D]")
+    if k_cache.stride() != v_cache.stride():
+        raise RuntimeError("k and v caches must share their strides")
+    if cos.shape[0] < cap or cos.shape[1] != D or sin.shape != cos.shape:
+        raise RuntimeError("cos/sin tables must cover the cache capacity")
+    if pos_dev.dtype != torch.int32 or not pos_dev.is_cuda or pos_dev.numel() != 1:
+        raise RuntimeError("pos_dev: expected one int32 on the device")
+    with _Span("decode_rope_append"):
+        _lib.check(lib.cd_decode_rope_append(
+            qkv.data_ptr(), _ptr(q_w), _ptr(k_w), cos.data_ptr(), sin.data_ptr(), float(eps), B,
+            hq, hkv, D, k_cache.data_ptr(), v_cache.data_ptr(), k_cache.stride(0),
+            k_cache.stride(1), k_cache.stride(2), cap, pos_dev.data_ptr(), _stream()),
+            "cd_decode_rope_append")
+    return qkv
+
+
 def decode_attention(qkv: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
-                     mask: Optional[torch.Tensor], hq: int, hkv: int, head_dim: int
-                     ) -> torch.Tensor:
+                     mask: Optional[torch.Tensor], hq: int, hkv: int, head_dim: int,
+                     kv_len_dev: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Single-query attention: qkv [B, (hq + 2 hkv) * D] (its q columns are used), k / v
     [B, hkv, L, D] views of the cache (any batch / head / token strides, D contiguous),
-    mask None or a bf16 additive mask viewable as [B or 1, L].  Returns [B, hq * D]."""
+    mask None or a bf16 additive mask viewable as [B or 1, L].  `kv_len_dev` (one int32 on the
+    device): attend only the first min(L, value) cached tokens.  Returns [B, hq * D]."""
     lib = _lib.load()
     B, D = qkv.shape[0], head_dim
     L = k.shape[2]
@@ -229,14 +266,17 @@ def decode_attention(qkv: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
         if m2.dtype != BF16 or not m2.is_cuda or m2.stride(1) != 1 or m2.shape[0] not in (1, B):
             raise RuntimeError("mask: expected a CUDA bf16 additive mask of shape [B or 1, 1, 1, L]")
         mptr, mstride = m2.data_ptr(), (m2.stride(0) if m2.shape[0] == B else 0)
+    if kv_len_dev is not None and (kv_len_dev.dtype != torch.int32 or not kv_len_dev.is_cuda
+                                   or kv_len_dev.numel() != 1):
+        raise RuntimeError("kv_len_dev: expected one int32 on the device")
     ws_bytes = lib.cd_decode_attention_workspace_bytes(B, hq, hkv, L, D)
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=qkv.device)
     out = torch.empty(B, hq * D, dtype=BF16, device=qkv.device)
     with _Span("decode_attention", 2):
         _lib.check(lib.cd_decode_attention(
             qkv.data_ptr(), qkv.stride(0), k.data_ptr(), v.data_ptr(), k.stride(0), k.stride(1),
-            k.stride(2), mptr, mstride, float(head_dim) ** -0.5, B, hq, hkv, L, D, out.data_ptr(),
-            ws.data_ptr(), ws_bytes, _stream()), "cd_decode_attention")
+            k.stride(2), mptr, mstride, float(head_dim) ** -0.5, B, hq, hkv, L, _ptr(kv_len_dev),
+            D, out.data_ptr(), ws.data_ptr(), ws_bytes, _stream()), "cd_decode_attention")
     return out
 
 

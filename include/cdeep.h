@@ -111,6 +111,23 @@ int cd_qk_norm_rope(void* qkv, const void* q_w, const void* k_w, const float* co
                     const float* sin_t, float eps, int T, int S, int pos0, int hq, int hkv, int D,
                     void* stream);
 
+/* ---- decode step: Q/K RMSNorm + rotary embedding + KV-cache append --------------------------
+ * One new token per sequence (row b of qkv belongs to sequence b).  cd_qk_norm_rope's
+ * arithmetic at the position stored in DEVICE memory (*pos_dev, the number of tokens already
+ * cached), and the rotated k heads and the v heads of every row are also written into the
+ * caches at that position: k_cache[b, h, *pos_dev, :], same for v (element strides batch / kv
+ * head / token, D contiguous, multiples of 8).  Replaces complexity_deep/core/attention.py:138-161
+ * for q_len == 1: the reference grows the cache with torch.cat, which copies all of it every
+ * step; here the cache is a fixed buffer of `capacity` tokens and the position is a device
+ * scalar, so the same launch (same arguments) serves every step and can be replayed from a
+ * CUDA graph.  Nothing is written when *pos_dev is outside [0, capacity); cos_t / sin_t hold
+ * `capacity` rows. */
+int cd_decode_rope_append(void* qkv, const void* q_w, const void* k_w, const float* cos_t,
+                          const float* sin_t, float eps, int B, int hq, int hkv, int D,
+                          void* k_cache, void* v_cache, long long kv_stride_b,
+                          long long kv_stride_h, long long kv_stride_t, int capacity,
+                          const int32_t* pos_dev, void* stream);
+
 /* ---- single-query attention over a KV cache (decode) ---------------------------------------
  * Replaces, for q_len == 1, complexity_deep/core/attention.py:163-177 (repeat_interleave of the
  * KV heads + scaled_dot_product_attention with an additive mask):
@@ -120,12 +137,16 @@ int cd_qk_norm_rope(void* qkv, const void* q_w, const void* k_w, const float* co
  * cache is read in place, whatever buffer it lives in.  mask: bf16 additive [B, L] with row
  * stride mask_stride_b (0 = one row for all), or NULL.  out: [B, hq * D] bf16.
  * ws: cd_decode_attention_workspace_bytes(...) bytes.  D is 64 or 128, G <= 4; all strides
- * multiples of 8 elements. */
+ * multiples of 8 elements.  kv_len_dev (may be NULL): a device scalar; when given, only the
+ * first min(L, *kv_len_dev) cached tokens are attended (L then is the capacity the launch is
+ * sized for), with the same split of the rows over blocks, hence the same bits, as a call
+ * with that L. */
 size_t cd_decode_attention_workspace_bytes(int B, int hq, int hkv, int L, int D);
 int cd_decode_attention(const void* q, long long q_stride_b, const void* k, const void* v,
                         long long kv_stride_b, long long kv_stride_h, long long kv_stride_t,
                         const void* mask, long long mask_stride_b, float scale, int B, int hq,
-                        int hkv, int L, int D, void* out, void* ws, size_t ws_bytes, void* stream);
+                        int hkv, int L, const int32_t* kv_len_dev, int D, void* out, void* ws,
+                        size_t ws_bytes, void* stream);
 
 /* ---- expert up-projection with fused SwiGLU ---------------------------------------------
  * Replaces gate/up GEMMs and silu(gate)*up of the routed experts

@@ -94,3 +94,112 @@ def test_few_rows_use_narrow_tiles(T, K, N):
     wm = (torch.randn(N, K, generator=g) * 0.05).to(BF)
     out2 = ops.mu_qkv(x.cuda(), mu.cuda(), w.cuda(), wm.cuda())
     _close(out2, x.float() @ w.float().t() + mu.float() @ wm.float().t())
+
+
+# ------------------------------------------------------------------ device-side positions
+@pytest.mark.parametrize("B,hq,hkv,D,L", [(3, 16, 8, 128, 300), (2, 12, 4, 64, 1000),
+                                          (5, 4, 1, 128, 513), (2, 4, 2, 128, 1)])
+def test_decode_attention_device_length_is_bit_exact(B, hq, hkv, D, L):
+    """The launch sized for the cache capacity with the length in device memory returns the
+    same bits as the launch sized for that length."""
+    from complexity_deep_b200 import ops
+    g = torch.Generator().manual_seed(L)
+    cap = 4 * L + 123
+    qkv = torch.randn(B, (hq + 2 * hkv) * D, generator=g).to(BF).cuda()
+    kbuf = torch.randn(B, hkv, cap, D, generator=g).to(BF).cuda()
+    vbuf = torch.randn(B, hkv, cap, D, generator=g).to(BF).cuda()
+    ref = ops.decode_attention(qkv, kbuf[:, :, :L], vbuf[:, :, :L], None, hq, hkv, D)
+    n = torch.tensor([L], dtype=torch.int32, device="cuda")
+    got = ops.decode_attention(qkv, kbuf, vbuf, None, hq, hkv, D, kv_len_dev=n)
+    assert torch.equal(got, ref)
+    n.fill_(cap + 50)                      # clamped to the capacity
+    full = ops.decode_attention(qkv, kbuf, vbuf, None, hq, hkv, D)
+    assert torch.equal(ops.decode_attention(qkv, kbuf, vbuf, None, hq, hkv, D, kv_len_dev=n), full)
+
+
+@pytest.mark.parametrize("hq,hkv,D,norm", [(16, 8, 128, True), (4, 2, 64, True),
+                                           (4, 2, 96, True), (6, 3, 128, False)])
+def test_decode_rope_append_matches_in_place_kernel(hq, hkv, D, norm):
+    """cd_decode_rope_append = cd_qk_norm_rope at the device-side position + the new k / v rows
+    stored at that position of the caches; the rest of the caches is untouched."""
+    from complexity_deep_b200 import ops
+    B, cap, pos = 5, 40, 17
+    g = torch.Generator().manual_seed(hq * D)
+    qkv = torch.randn(B, (hq + 2 * hkv) * D, generator=g).to(BF).cuda()
+    qw = (torch.randn(D, generator=g) * 0.1 + 1).to(BF).cuda() if norm else None
+    kw = (torch.randn(D, generator=g) * 0.1 + 1).to(BF).cuda() if norm else None
+    ang = torch.outer(torch.arange(cap).float(), 1.0 / (10000 ** (torch.arange(0, D, 2).float() / D)))
+    cos, sin = torch.cat([ang, ang], -1).cos().cuda(), torch.cat([ang, ang], -1).sin().cuda()
+    ref = ops.qk_norm_rope_(qkv.clone(), qw, kw, cos, sin, 1e-6, 1, pos, hq, hkv, D)
+    big_k = torch.full((B, hkv, cap + 8, D), 7.0, dtype=BF, device="cuda")   # strided views
+    big_v = torch.full((B, hkv, cap + 8, D), 7.0, dtype=BF, device="cuda")
+    kc, vc = big_k[:, :, :cap], big_v[:, :, :cap]
+    p = torch.tensor([pos], dtype=torch.int32, device="cuda")
+    got = ops.decode_rope_append(qkv.clone(), qw, kw, cos, sin, 1e-6, hq, hkv, D, kc, vc, p)
+    assert torch.equal(got, ref)
+    assert torch.equal(kc[:, :, pos], ref[:, hq * D:(hq + hkv) * D].view(B, hkv, D))
+    assert torch.equal(vc[:, :, pos], ref[:, (hq + hkv) * D:].view(B, hkv, D))
+    untouched = torch.ones(cap + 8, dtype=torch.bool)
+    untouched[pos] = False
+    assert bool((big_k[:, :, untouched] == 7.0).all()) and bool((big_v[:, :, untouched] == 7.0).all())
+    p.fill_(cap)                           # outside the cache: nothing is written anywhere
+    before = (big_k.clone(), big_v.clone())
+    ops.decode_rope_append(qkv.clone(), qw, kw, cos, sin, 1e-6, hq, hkv, D, kc, vc, p)
+    assert torch.equal(big_k, before[0]) and torch.equal(big_v, before[1])
+
+
+def _decode_model():
+    import complexity_deep_b200 as cd
+    torch.manual_seed(0)
+    cfg = cd.ComplexityConfig(vocab_size=512, hidden_size=256, intermediate_size=512,
+                              num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                              num_experts=4)
+    model = cd.ComplexityModel(cfg)
+    with torch.no_grad():
+        model.mu_init.normal_(0, 0.5)
+    return cfg, model.to(device="cuda", dtype=BF).eval()
+
+
+def test_static_cache_steps_equal_growing_cache_steps():
+    """Five decode steps on a StaticKVCache (device-side position, fixed launches) give the
+    same logits, bit for bit, as the same steps on the growing cache with an all-zero mask;
+    the eager static path and its CUDA-graph replay (DecodeGraph) agree too, and the last
+    step agrees with the oracle run over the whole sequence."""
+    from complexity_deep_b200.core.attention import StaticKVCache
+    from complexity_deep_b200.models import DecodeGraph
+    cfg, model = _decode_model()
+    B, P, steps = 3, 10, 5
+    g = torch.Generator().manual_seed(5)
+    ids = torch.randint(0, cfg.vocab_size, (B, P + steps), generator=g).cuda()
+    with torch.no_grad():
+        pre = model(ids[:, :P], use_cache=True)
+        # growing cache, zero additive mask
+        past, dyn = pre.past_key_values, []
+        for s in range(steps):
+            mask = torch.zeros(B, 1, 1, P + s + 1, dtype=BF, device="cuda")
+            out = model(ids[:, P + s:P + s + 1], attention_mask=mask, past_key_values=past,
+                        use_cache=True)
+            past = out.past_key_values
+            dyn.append(out.logits.clone())
+        # static cache, eager
+        cache = StaticKVCache(cfg.num_hidden_layers, B, 2, 64, P + steps + 3, "cuda")
+        cache.load(pre.past_key_values)
+        for s in range(steps):
+            out = model(ids[:, P + s:P + s + 1], past_key_values=cache.layers, use_cache=True)
+            cache.advance()
+            assert torch.equal(out.logits, dyn[s]), s
+        assert cache.length == P + steps
+        assert torch.equal(cache.k[1][:, :, :P + steps], past[1][0])
+        assert torch.equal(cache.v[0][:, :, :P + steps], past[0][1])
+    # static cache, graph replay
+    dec = DecodeGraph(model, batch=B, capacity=P + steps)
+    assert torch.equal(dec.prefill(ids[:, :P]), pre.logits)
+    for s in range(steps):
+        assert torch.equal(dec.step(ids[:, P + s:P + s + 1]), dyn[s]), s
+    with pytest.raises(RuntimeError):
+        dec.step(ids[:, :1])               # cache full
+    # oracle over the whole sequence (fp32 on the bf16-rounded weights)
+    state = {k: (v.float().cpu() if v.is_floating_point() else v.cpu())
+             for k, v in model.state_dict().items()}
+    ref, _ = oracle.model_forward(state, cfg.to_dict(), ids.cpu())
+    _close(dyn[-1][:, 0], ref[:, -1])

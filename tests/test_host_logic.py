@@ -206,3 +206,41 @@ def test_forward_only_is_loud():
     model = create_complexity_model("tiny", vocab_size=64, num_hidden_layers=1)
     with pytest.raises(RuntimeError, match="forward pass only"):
         model(torch.zeros(1, 4, dtype=torch.long))          # grad mode: embedding output requires grad
+
+
+def test_static_kv_cache_bookkeeping():
+    """Host side of the fixed-capacity decode cache: load from a prefill cache, position
+    scalars (cached tokens, keys visible to the next step), capacity checks."""
+    from complexity_deep_b200.core.attention import StaticKVCache
+    cache = StaticKVCache(num_layers=2, batch=3, kv_heads=2, head_dim=8, capacity=6, device="cpu",
+                          dtype=torch.float32)
+    assert cache.state.tolist() == [0, 1] and cache.length == 0 and len(cache.layers) == 2
+    past = [(torch.randn(3, 2, 4, 8), torch.randn(3, 2, 4, 8)) for _ in range(2)]
+    cache.load(past)
+    assert cache.state.tolist() == [4, 5] and cache.length == 4
+    assert torch.equal(cache.layers[1].k[:, :, :4], past[1][0])
+    assert torch.equal(cache.layers[0].v[:, :, :4], past[0][1])
+    assert float(cache.k[0][:, :, 4:].abs().sum()) == 0.0
+    cache.advance()
+    assert cache.state.tolist() == [5, 6] and cache.length == 5
+    with pytest.raises(ValueError):
+        cache.load([(torch.zeros(3, 2, 7, 8), torch.zeros(3, 2, 7, 8))] * 2)
+    with pytest.raises(ValueError):
+        cache.set_length(7)
+
+
+def test_rotary_tables_grow_geometrically():
+    """Positions past the configured maximum rebuild the tables once per doubling, not on
+    every decode step; values do not depend on the table length."""
+    from complexity_deep_b200.core.rotary import RotaryEmbedding
+    rot = RotaryEmbedding(16, max_seq_len=8)
+    cos_a, _ = rot.tables_fp32(9)
+    assert rot.max_seq_len == 16 and cos_a.shape[0] == 16
+    ptr = cos_a.data_ptr()
+    for n in range(10, 17):
+        assert rot.tables_fp32(n)[0].data_ptr() == ptr
+    cos_b, sin_b = rot.tables_fp32(17)
+    assert rot.max_seq_len == 32
+    assert torch.equal(cos_b[:16], cos_a)
+    ref = RotaryEmbedding(16, max_seq_len=32)
+    assert torch.equal(ref.cos_cached, cos_b) and torch.equal(ref.sin_cached, sin_b)
