@@ -7,8 +7,10 @@
 // + mask[b]) V[b, h / G].
 //
 // Split-KV: grid (splits, kv heads, batch); a block owns one chunk of the cache for one
-// (batch, kv head) and all G query heads of the group.  8 lanes share a cached row (each
-// owns D/8 dimensions, 16-byte loads), so a warp streams 4 rows per step; every lane group
+// (batch, kv head) and all G query heads of the group.  8 lanes share a cached row: for
+// every 64 dimensions lane s owns dimensions 8 s .. 8 s + 7, so one 16-byte access per lane
+// covers 128 contiguous bytes of the row (whole sectors, no re-fetch); a warp streams 4 rows
+// per step; every lane group
 // keeps an online-softmax state (running max, sum, weighted V) per query head, merged across
 // the block through shared memory and across splits by a second small kernel.
 #include <cfloat>
@@ -44,11 +46,29 @@ __host__ __device__ inline int chunk_rows(int L, int splits) {
   return (((L + splits - 1) / splits) + 15) / 16 * 16;
 }
 
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+  const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+constexpr int kStages = 4;   // row steps staged in shared memory per thread (3 in flight)
+
 // DPL = dimensions per lane = D / 8 (8 or 16 -> D = 64 or 128), G = query heads per KV head.
 // len_dev (optional): the number of cached rows is min(L, *len_dev) and the split of the rows
 // over blocks is recomputed from it; the grid and the workspace layout stay those of L.
+//
+// A row step = 16 cached rows of the block (4 warps x 4 lane groups), 2 * DPL bytes of K and
+// of V per lane.  Every lane copies its own slices of the next kStages - 1 steps into a
+// private slot of shared memory with cp.async (bytes in flight without holding registers:
+// 4 blocks per SM keep ~100 KB on the way) and reads them back with 16-byte loads, so no
+// block-level synchronisation is needed inside the loop.
 template <int DPL, int G>
-__global__ void __launch_bounds__(kAttnThreads)
+__global__ void __launch_bounds__(kAttnThreads, (G * DPL > 48) ? 2 : (G * DPL > 32) ? 3 : 4)
 decode_attn_partial_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride_b,
                            const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
                            long long kv_stride_b, long long kv_stride_h, long long kv_stride_t,
@@ -56,6 +76,13 @@ decode_attn_partial_kernel(const __nv_bfloat16* __restrict__ q, long long q_stri
                            float scale, int L, int chunk, int hq, float* __restrict__ part_acc,
                            float* __restrict__ part_ml, const int* __restrict__ len_dev) {
   constexpr int D = DPL * kLanesPerRow;
+  constexpr int kV = DPL / 8;                               // 16-byte pieces of K (and of V) per lane
+  constexpr int kStepBytes = kAttnThreads * 2 * kV * 16;    // one row step of the block
+  constexpr int kMergeBytes = 16 * G * D * 4;               // the block-level merge re-uses the slots
+  constexpr int kSmemBytes = kStages * kStepBytes > kMergeBytes ? kStages * kStepBytes : kMergeBytes;
+  __shared__ __align__(16) unsigned char s_raw[kSmemBytes];
+  __shared__ float s_m[16][G], s_l[16][G];
+
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int splits = gridDim.x;
   if (len_dev) {
@@ -74,10 +101,10 @@ decode_attn_partial_kernel(const __nv_bfloat16* __restrict__ q, long long q_stri
   float qf[G][DPL];
 #pragma unroll
   for (int g = 0; g < G; ++g) {
-    const __nv_bfloat16* qp = q + b * q_stride_b + static_cast<long long>(kvh * G + g) * D + sub * DPL;
+    const __nv_bfloat16* qp = q + b * q_stride_b + static_cast<long long>(kvh * G + g) * D + sub * 8;
 #pragma unroll
     for (int i = 0; i < DPL; i += 8) {
-      const uint4 w = *reinterpret_cast<const uint4*>(qp + i);
+      const uint4 w = *reinterpret_cast<const uint4*>(qp + i * 8);
       const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
@@ -94,34 +121,48 @@ decode_attn_partial_kernel(const __nv_bfloat16* __restrict__ q, long long q_stri
 #pragma unroll
     for (int i = 0; i < DPL; ++i) acc[g][i] = 0.f;
   }
-  const __nv_bfloat16* kb = k + b * kv_stride_b + kvh * kv_stride_h + sub * DPL;
-  const __nv_bfloat16* vb = v + b * kv_stride_b + kvh * kv_stride_h + sub * DPL;
+  const __nv_bfloat16* kb = k + b * kv_stride_b + kvh * kv_stride_h + sub * 8;
+  const __nv_bfloat16* vb = v + b * kv_stride_b + kvh * kv_stride_h + sub * 8;
   const __nv_bfloat16* mb = mask ? mask + b * mask_stride_b : nullptr;
 
-  // Rows of this block: t_begin + 16 * i + (warp * 4 + rgrp), two steps (rows t and t + 16) per
-  // iteration; the loads of the next iteration are issued before the arithmetic of the current
-  // one, so 8 x 16 bytes per lane are in flight.  The loop bound is the same for every lane of
-  // a warp (the shuffles need the whole warp).
-  constexpr int kV = DPL / 8;
-  uint4 kn[2][kV], vn[2][kV];
-  auto load_rows = [&](int t, int s) {
+  // slot of (stage, piece) for this thread: consecutive threads are 16 bytes apart, so both
+  // the asynchronous writes and the reads are free of bank conflicts
+  auto slot = [&](int stage, int piece) -> uint4* {
+    return reinterpret_cast<uint4*>(s_raw + stage * kStepBytes) + piece * kAttnThreads + threadIdx.x;
+  };
+  const int t_lane = t_begin + warp * 4 + rgrp;             // this lane's row of step 0
+  const int n_steps = (t_end - t_begin + 15) >> 4;          // same for the whole block
+  auto issue = [&](int step) {
+    const int t = t_lane + step * 16;
+    if (step < n_steps && t < t_end) {
+      const int stage = step % kStages;
 #pragma unroll
-    for (int i = 0; i < kV; ++i) {
-      kn[s][i] = make_uint4(0, 0, 0, 0);
-      vn[s][i] = make_uint4(0, 0, 0, 0);
-      if (t < t_end) {
-        kn[s][i] = *reinterpret_cast<const uint4*>(kb + t * kv_stride_t + i * 8);
-        vn[s][i] = *reinterpret_cast<const uint4*>(vb + t * kv_stride_t + i * 8);
+      for (int i = 0; i < kV; ++i) {
+        cp_async16(slot(stage, i), kb + t * kv_stride_t + i * 64);
+        cp_async16(slot(stage, kV + i), vb + t * kv_stride_t + i * 64);
       }
     }
+    cp_async_commit();                                      // one group per step, even if empty
   };
-  auto process = [&](const uint4 (&kr)[kV], const uint4 (&vr)[kV], int t) {
+#pragma unroll
+  for (int s0 = 0; s0 < kStages - 1; ++s0) issue(s0);
+
+  for (int step = 0; step < n_steps; ++step) {
+    issue(step + kStages - 1);
+    cp_async_wait<kStages - 1>();                           // this step's group has landed
+    const int t = t_lane + step * 16;
     const bool valid = t < t_end;
+    const int stage = step % kStages;
     float kf[DPL], vf[DPL];
 #pragma unroll
     for (int i = 0; i < kV; ++i) {
-      const uint32_t kw[4] = {kr[i].x, kr[i].y, kr[i].z, kr[i].w};
-      const uint32_t vw[4] = {vr[i].x, vr[i].y, vr[i].z, vr[i].w};
+      uint4 kr = make_uint4(0, 0, 0, 0), vr = kr;
+      if (valid) {
+        kr = *slot(stage, i);
+        vr = *slot(stage, kV + i);
+      }
+      const uint32_t kw[4] = {kr.x, kr.y, kr.z, kr.w};
+      const uint32_t vw[4] = {vr.x, vr.y, vr.z, vr.w};
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         kf[i * 8 + 2 * e] = lo_f(kw[e]); kf[i * 8 + 2 * e + 1] = hi_f(kw[e]);
@@ -139,39 +180,26 @@ decode_attn_partial_kernel(const __nv_bfloat16* __restrict__ q, long long q_stri
       s += __shfl_xor_sync(0xffffffffu, s, 4);
       if (valid) {
         s += madd;
-        const float m_new = fmaxf(m_run[g], s);
-        // a fully masked prefix (-inf scores) keeps the state untouched
-        if (m_new > -FLT_MAX) {
-          const float corr = __expf(m_run[g] - m_new);
-          const float pr = __expf(s - m_new);
-          l_run[g] = l_run[g] * corr + pr;
+        if (s > m_run[g]) {            // new running maximum: rescale (rare after the first rows)
+          const float corr = __expf(m_run[g] - s);
+          l_run[g] *= corr;
 #pragma unroll
-          for (int i = 0; i < DPL; ++i) acc[g][i] = acc[g][i] * corr + pr * vf[i];
-          m_run[g] = m_new;
+          for (int i = 0; i < DPL; ++i) acc[g][i] *= corr;
+          m_run[g] = s;
         }
+        // s = -inf (masked) gives pr = 0 and leaves the state untouched
+        const float pr = __expf(s - m_run[g]);
+        l_run[g] += pr;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) acc[g][i] += pr * vf[i];
       }
     }
-  };
-  const int t_first = t_begin + warp * 4 + rgrp;
-  load_rows(t_first, 0);
-  load_rows(t_first + 16, 1);
-  for (int tb = t_begin + warp * 4; tb < t_end; tb += 32) {
-    const int t = tb + rgrp;
-    uint4 k0[kV], v0[kV], k1[kV], v1[kV];
-#pragma unroll
-    for (int i = 0; i < kV; ++i) {
-      k0[i] = kn[0][i]; v0[i] = vn[0][i];
-      k1[i] = kn[1][i]; v1[i] = vn[1][i];
-    }
-    load_rows(t + 32, 0);
-    load_rows(t + 48, 1);
-    process(k0, v0, t);
-    process(k1, v1, t + 16);
   }
+  cp_async_wait<0>();
+  __syncthreads();                     // every lane is done with its slots: re-use them
 
   // merge the 16 row streams of the block (4 warps x 4 lane groups) in shared memory
-  __shared__ float s_m[16][G], s_l[16][G];
-  __shared__ float s_acc[16][G][D];
+  float (*s_acc)[G][D] = reinterpret_cast<float (*)[G][D]>(s_raw);
   const int stream = warp * 4 + rgrp;
 #pragma unroll
   for (int g = 0; g < G; ++g) {
@@ -180,7 +208,7 @@ decode_attn_partial_kernel(const __nv_bfloat16* __restrict__ q, long long q_stri
       s_l[stream][g] = l_run[g];
     }
 #pragma unroll
-    for (int i = 0; i < DPL; ++i) s_acc[stream][g][sub * DPL + i] = acc[g][i];
+    for (int i = 0; i < DPL; ++i) s_acc[stream][g][(i >> 3) * 64 + sub * 8 + (i & 7)] = acc[g][i];
   }
   __syncthreads();
   for (int idx = threadIdx.x; idx < G * D; idx += kAttnThreads) {
@@ -234,7 +262,7 @@ cudaError_t launch_partial(int G, dim3 grid, cudaStream_t st, const __nv_bfloat1
 #define CDEEP_ATTN_CASE(GG)                                                                     \
   case GG:                                                                                      \
     decode_attn_partial_kernel<DPL, GG><<<grid, kAttnThreads, 0, st>>>(                         \
-        q, qsb, k, v, sb, sh, stt, mask, msb, scale, L, chunk, hq, pa, pml, len_dev);                    \
+        q, qsb, k, v, sb, sh, stt, mask, msb, scale, L, chunk, hq, pa, pml, len_dev);           \
     break;
   switch (G) {
     CDEEP_ATTN_CASE(1)
