@@ -147,8 +147,26 @@ decode_attn_partial_kernel(const __nv_bfloat16* __restrict__ q, long long q_stri
 #pragma unroll
   for (int s0 = 0; s0 < kStages - 1; ++s0) issue(s0);
 
+  // Additive mask: once per 8 steps lane l fetches the value of row group (l & 3) of step
+  // (window + l / 4) of this warp, one window ahead of its use; a step then takes its value
+  // from the owning lane with a shuffle, so no step waits for a global load.
+  auto mask_window = [&](int step0) -> float {
+    const int t = t_begin + 16 * (step0 + (lane >> 2)) + warp * 4 + (lane & 3);
+    return (mb && t < t_end) ? __bfloat162float(mb[t]) : 0.f;
+  };
+  float mwin = mask_window(0), mwin_next = mask_window(8);
+
   for (int step = 0; step < n_steps; ++step) {
     issue(step + kStages - 1);
+    float madd = 0.f;
+    if (mb) {                                               // uniform
+      const int j = step & 7;
+      if (j == 0 && step > 0) {
+        mwin = mwin_next;
+        mwin_next = mask_window(step + 8);
+      }
+      madd = __shfl_sync(0xffffffffu, mwin, (j << 2) | rgrp);
+    }
     cp_async_wait<kStages - 1>();                           // this step's group has landed
     const int t = t_lane + step * 16;
     const bool valid = t < t_end;
@@ -169,7 +187,6 @@ decode_attn_partial_kernel(const __nv_bfloat16* __restrict__ q, long long q_stri
         vf[i * 8 + 2 * e] = lo_f(vw[e]); vf[i * 8 + 2 * e + 1] = hi_f(vw[e]);
       }
     }
-    const float madd = (valid && mb) ? __bfloat162float(mb[t]) : 0.f;
 #pragma unroll
     for (int g = 0; g < G; ++g) {
       float s = 0.f;
