@@ -74,14 +74,20 @@ constexpr uint64_t kWaitLimitNs = 2000ull * 1000ull * 1000ull;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
                                           volatile int* abort_flag,
                                           uint64_t limit_ns = kWaitLimitNs) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
+  // The clock is read only after 1024 failed polls and then once per 1024: %globaltimer is
+  // slow to read, and a read on every short wait put its latency on the critical path of
+  // pipelines that wait once per k-block (few-row GEMMs).  The limit therefore counts from
+  // the first read.
+  uint64_t t0 = 0;
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 0x3ffu) == 0) {
       if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > limit_ns) {
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > limit_ns) {
         *abort_flag = 1;
         return false;
       }
