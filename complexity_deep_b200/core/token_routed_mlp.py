@@ -144,7 +144,7 @@ class TokenRoutedMLP(nn.Module):
     # ------------------------------------------------------------------ packed weights
     def _packed_routed(self, rows: Optional[int] = None):
         g, u = self.gate_proj_w, self.up_proj_w
-        bn = ops.choose_block_n(self.expert_intermediate_size, rows)
+        bn = ops.choose_block_n(self.expert_intermediate_size, rows, self.num_experts)
         packed = self._derived.get(
             f"routed_gate_up_{bn}", (g, u),
             lambda: ops.pack_gate_up(g.detach().transpose(1, 2), u.detach().transpose(1, 2), bn))

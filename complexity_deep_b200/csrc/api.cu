@@ -222,7 +222,7 @@ int cd_moe_down(const void* h_routed, int I_e, const void* wd_routed, const void
   epi.residual = residual;
   epi.ldr = H;
   return launch_gemm(T, H, E, seg_offsets, op0, h_shared ? &op1 : nullptr, epi,
-                     choose_store_block_n(T, H, current_sm_count()), as_stream(stream));
+                     choose_store_block_n(T, H, E, current_sm_count()), as_stream(stream));
 }
 
 int cd_push_rows(const void* x, const int32_t* src_rows, const int32_t* offsets,
@@ -258,7 +258,7 @@ int cd_moe_down_push(const void* h_routed, int I_e, const void* wd_routed,
   epi.out_cols = H;
   epi.out_row_ptrs = reinterpret_cast<const long long*>(out_row_ptrs);
   return launch_gemm(T, H, E, seg_offsets, op0, nullptr, epi,
-                     choose_store_block_n(T, H, current_sm_count()), as_stream(stream));
+                     choose_store_block_n(T, H, E, current_sm_count()), as_stream(stream));
 }
 
 int cd_moe_combine(const void* h_shared, int I_s, const void* wd_shared, const void* routed_sorted,
@@ -284,7 +284,7 @@ int cd_moe_combine(const void* h_shared, int I_s, const void* wd_shared, const v
   epi.residual2 = routed_sorted;
   epi.ldr2 = H;
   return launch_gemm(T, H, 1, nullptr, op0, nullptr, epi,
-                     choose_store_block_n(T, H, current_sm_count()), as_stream(stream));
+                     choose_store_block_n(T, H, 1, current_sm_count()), as_stream(stream));
 }
 
 int cd_mu_qkv(const void* x, const void* mu_prev, const void* w, const void* w_mu, void* qkv,
@@ -313,14 +313,14 @@ int cd_mu_qkv(const void* x, const void* mu_prev, const void* w, const void* w_m
   epi.ldo = N;
   epi.out_cols = N;
   return launch_gemm(T, N, 1, nullptr, op0, mu_prev ? &op1 : nullptr, epi,
-                     choose_store_block_n(T, N, current_sm_count()), as_stream(stream));
+                     choose_store_block_n(T, N, 1, current_sm_count()), as_stream(stream));
 }
 
 int cd_mu_qkv_rope_supported(int T, int N, int hq, int hkv, int D) {
   if (T < 1 || N < 8 || hq < 1 || hkv < 1) return 0;
   if (D != 128 || N != (hq + 2 * hkv) * D) return 0;
   if ((hq * D) % 256 || ((hq + hkv) * D) % 256) return 0;     // heads aligned to 256-wide tiles
-  return choose_store_block_n(T, N, current_sm_count()) == 256 ? 1 : 0;
+  return choose_store_block_n(T, N, 1, current_sm_count()) == 256 ? 1 : 0;
 }
 
 int cd_mu_qkv_rope(const void* x, const void* mu_prev, const void* w, const void* w_mu, void* qkv,
@@ -388,7 +388,7 @@ int cd_mu_proj(const void* h, const void* w, const void* mu_param, float mu_min,
   epi.clamp_lo = out_lo;
   epi.clamp_hi = out_hi;
   return launch_gemm(T, H, 1, nullptr, op0, nullptr, epi,
-                     choose_store_block_n(T, H, current_sm_count()), as_stream(stream));
+                     choose_store_block_n(T, H, 1, current_sm_count()), as_stream(stream));
 }
 
 int cd_linear(const void* x, const void* w, const void* residual, void* out, int T, int K, int N,
@@ -409,7 +409,7 @@ int cd_linear(const void* x, const void* w, const void* residual, void* out, int
   epi.residual = residual;
   epi.ldr = N;
   return launch_gemm(T, N, 1, nullptr, op0, nullptr, epi,
-                     choose_store_block_n(T, N, current_sm_count()), as_stream(stream));
+                     choose_store_block_n(T, N, 1, current_sm_count()), as_stream(stream));
 }
 
 }  // extern "C"

@@ -110,15 +110,32 @@ cudaError_t launch_any(int block_n, int kind, int grid, const CUtensorMap& a0,
   return cudaErrorInvalidValue;
 }
 
-// Accumulator-tile width for the store epilogue: the widest tile that still gives (almost)
-// every SM a tile.  With few rows (decode) the GEMM streams weights and is HBM-bound, so
-// narrow tiles spread the weight stream over all SMs.
-int store_block_n_impl(int M, int N, int sm_count) {
-  const long long m_tiles = (M + kBlockM - 1) / kBlockM;
-  for (int bn : {256, 128, 64}) {
-    if (m_tiles * ((N + bn - 1) / bn) * 4 >= 3LL * sm_count) return bn;
+// Accumulator-tile width for the store epilogue.
+// Many tiles (prefill): the 256-wide tile whenever it gives (almost) every SM a tile; the GEMM
+// is then bound by tensor throughput.  Few tiles (decode): an output tile is one chain of K/16
+// dependent MMA instructions that cost ~140 cycles each whatever their width (measured: time
+// = 3.8 us + 0.30 us per 64-wide k-block for 32-, 64- and 128-wide tiles alike), so the time
+// is set by how many tiles the busiest SM runs one after the other: the narrowest tile that
+// still leaves at most one tile per SM; if even 256-wide tiles are more than that, the width
+// with the fewest waves.  For grouped calls every non-empty group has at least one row tile.
+int store_block_n_impl(int M, int N, int num_groups, int sm_count) {
+  long long m_tiles = (M + kBlockM - 1) / kBlockM;
+  if (num_groups > m_tiles) m_tiles = num_groups;
+  auto tiles = [&](int bn) { return m_tiles * ((N + bn - 1) / bn); };
+  if (tiles(256) * 4 >= 3LL * sm_count) return 256;
+  for (int bn : {32, 64, 128, 256})
+    if (tiles(bn) <= sm_count) return bn;
+  int best = 256;
+  long long best_cost = -1;
+  for (int bn : {256, 128, 64, 32}) {
+    const long long waves = (tiles(bn) + sm_count - 1) / sm_count;
+    const long long cost = waves * (bn == 256 ? 160 : 140);
+    if (best_cost < 0 || cost < best_cost) {
+      best = bn;
+      best_cost = cost;
+    }
   }
-  return 32;
+  return best;
 }
 
 // CTA pairs (256-row tiles) are used whenever the 256-wide tile is: measured on B200 they win
@@ -166,7 +183,9 @@ static DeviceInfo* device_info(int* status_out) {
   return &di;
 }
 
-int choose_store_block_n(int M, int N, int sm_count) { return store_block_n_impl(M, N, sm_count); }
+int choose_store_block_n(int M, int N, int num_groups, int sm_count) {
+  return store_block_n_impl(M, N, num_groups, sm_count);
+}
 
 int current_sm_count() {
   int st;

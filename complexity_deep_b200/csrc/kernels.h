@@ -79,7 +79,7 @@ int launch_gemm(int M, int N, int num_groups, const int* seg_offsets, const Gemm
                 const GemmOperand* op1, const GemmEpilogueArgs& epi, int block_n,
                 cudaStream_t stream);
 
-int choose_store_block_n(int M, int N, int sm_count);  // needs the current device's SM count
+int choose_store_block_n(int M, int N, int num_groups, int sm_count);  // SM count of the current device
 int current_sm_count();
 int* device_status_word();  // per-device word the kernels raise when a bounded wait ran out
 

@@ -281,18 +281,28 @@ def decode_attention(qkv: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
 
 
 # --------------------------------------------------------------------------- weights
-def choose_block_n(width: int, rows: Optional[int] = None) -> int:
+def choose_block_n(width: int, rows: Optional[int] = None, groups: int = 1,
+                   sm_count: Optional[int] = None) -> int:
     """Accumulator-tile width for the SwiGLU up-projection of an expert `width` wide.
 
     Many rows (prefill): 256 (128 gate + 128 up columns per tile) unless padding `width` to a
     multiple of 128 would waste more than a quarter of the tile columns; then 128 (64 + 64).
     Measured on B200 at width 704 (padded to 768, 9 % waste): 1146 TFLOP/s with 256-wide tiles
     against 672 TFLOP/s with 128-wide ones, which are bound by shared-memory bandwidth.
-    Few rows (decode, `rows` <= 512): the GEMM only streams weights, so 32-wide tiles
-    (16 + 16) spread that stream over as many SMs as possible.
+    Few rows (decode, `rows` <= 512): a tile is one chain of K/16 dependent MMA instructions
+    whose cost hardly depends on the tile width, so the time is set by how many tiles the
+    busiest SM runs back to back: the narrowest tile that leaves at most one tile per SM
+    (every one of the `groups` experts has at least one row tile), else the widest.
     """
     if rows is not None and rows <= 512:
-        return 32
+        if sm_count is None:
+            sm_count = (torch.cuda.get_device_properties(torch.cuda.current_device())
+                        .multi_processor_count if torch.cuda.is_available() else 148)
+        m_tiles = max(groups, -(-rows // 128))
+        for bn in (32, 64, 128, 256):
+            if m_tiles * -(-width // (bn // 2)) <= sm_count:
+                return bn
+        return 256
     padded = -(-width // 128) * 128
     return 256 if (padded - width) / width <= 0.25 else 128
 

@@ -132,7 +132,12 @@ def test_pack_gate_up_layout():
     assert torch.equal(packed2[0, 384:384 + 72], 2 * gate2[0, 128:])
     assert ops.choose_block_n(5632) == 256 and ops.choose_block_n(704) == 256
     assert ops.choose_block_n(64) == 128 and ops.choose_block_n(48) == 128
-    assert ops.choose_block_n(704, rows=256) == 32 and ops.choose_block_n(704, rows=4096) == 256
+    assert ops.choose_block_n(704, rows=4096) == 256
+    # few rows: narrowest tile with at most one tile per SM (148), experts count as row tiles
+    assert ops.choose_block_n(704, rows=256, sm_count=148) == 32            # shared expert: 2 x 44 tiles
+    assert ops.choose_block_n(704, rows=256, groups=8, sm_count=148) == 128  # 8 x 11 tiles
+    assert ops.choose_block_n(5632, rows=32, sm_count=148) == 128           # 88 tiles
+    assert ops.choose_block_n(5632, rows=32, groups=8, sm_count=148) == 256  # nothing fits
     assert ops.choose_block_n(2816) == 256 and ops.choose_block_n(512) == 256
 
 
