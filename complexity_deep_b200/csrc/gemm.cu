@@ -52,7 +52,7 @@ bool make_map(CUtensorMap* m, const void* base, long long rows, long long cols, 
 
 struct DeviceInfo {
   int sm_count = 0;
-  bool attr_set[4][2][2] = {};  // [BN 32/64/128/256][epilogue][CTA group 1/2]
+  bool attr_set[4][3][2] = {};  // [BN 32/64/128/256][epilogue][CTA group 1/2]
   int* status = nullptr;
 };
 constexpr int kMaxDevices = 64;
@@ -67,7 +67,7 @@ cudaError_t launch_one(int grid, const CUtensorMap& a0, const CUtensorMap& b0,
                        DeviceInfo& di, cudaStream_t stream) {
   constexpr int bi = (BN == 256) ? 3 : (BN == 128) ? 2 : (BN == 64) ? 1 : 0;
   auto kern = gemm_bf16_sm100_kernel<BN, EPI, CG>;
-  constexpr int smem = GemmSmem<BN, CG>::kDynamic;
+  constexpr int smem = GemmSmem<BN, CG, gemm_epi_warps<BN, EPI>()>::kDynamic;
   if (!di.attr_set[bi][EPI][CG - 1]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
@@ -75,7 +75,7 @@ cudaError_t launch_one(int grid, const CUtensorMap& a0, const CUtensorMap& b0,
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
-  cfg.blockDim = dim3(kGemmThreads, 1, 1);
+  cfg.blockDim = dim3(gemm_threads<BN, EPI>(), 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -92,9 +92,12 @@ template <int CG>
 cudaError_t launch_any(int block_n, int kind, int grid, const CUtensorMap& a0,
                        const CUtensorMap& b0, const CUtensorMap& a1, const CUtensorMap& b1,
                        const GemmParams& p, DeviceInfo& di, cudaStream_t stream) {
-  if (block_n == 256)
+  if (block_n == 256) {
+    if (kind == kEpiStoreRope) return launch_one<256, kEpiStoreRope, CG>(grid, a0, b0, a1, b1, p, di, stream);
     return kind == kEpiSwiGLU ? launch_one<256, kEpiSwiGLU, CG>(grid, a0, b0, a1, b1, p, di, stream)
                               : launch_one<256, kEpiStore, CG>(grid, a0, b0, a1, b1, p, di, stream);
+  }
+  if (kind == kEpiStoreRope) return cudaErrorInvalidValue;
   if (block_n == 128)
     return kind == kEpiSwiGLU ? launch_one<128, kEpiSwiGLU, CG>(grid, a0, b0, a1, b1, p, di, stream)
                               : launch_one<128, kEpiStore, CG>(grid, a0, b0, a1, b1, p, di, stream);
@@ -296,8 +299,9 @@ int launch_gemm(int M, int N, int num_groups, const int* seg_offsets, const Gemm
 
   cudaError_t e;
   std::lock_guard<std::mutex> lk(g_mu);
-  e = (cg == 2) ? launch_any<2>(block_n, epi.kind, grid, a0, b0, a1, b1, p, *di, stream)
-                : launch_any<1>(block_n, epi.kind, grid, a0, b0, a1, b1, p, *di, stream);
+  const int kind = epi.rope_cos ? static_cast<int>(kEpiStoreRope) : epi.kind;
+  e = (cg == 2) ? launch_any<2>(block_n, kind, grid, a0, b0, a1, b1, p, *di, stream)
+                : launch_any<1>(block_n, kind, grid, a0, b0, a1, b1, p, *di, stream);
   if (e != cudaSuccess) return cuda_fail(e, "gemm launch");
   return CD_OK;
 }

@@ -34,12 +34,28 @@ constexpr int kUmmaK = 16;         // K of one tcgen05.mma for 16-bit inputs
 constexpr int kMaxGroups = 128;
 constexpr int kEpiCols = 64;          // output columns per epilogue sub-tile (128 bytes of bf16)
 constexpr int kEpiStageBytes = 4096;  // 32 rows x 128 bytes, per warp and buffer
-constexpr int kGemmThreads = 192;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
 
 enum GemmEpilogue : int {
-  kEpiStore = 0,   // out[row_map(r), n] = clamp(acc + bias[n] + residual[row_map(r), n])
-  kEpiSwiGLU = 1,  // out[r, j] = silu(acc[r, gate(j)]) * acc[r, up(j)]
+  kEpiStore = 0,      // out[row_map(r), n] = clamp(acc + bias[n] + residual[row_map(r), n])
+  kEpiSwiGLU = 1,     // out[r, j] = silu(acc[r, gate(j)]) * acc[r, up(j)]
+  kEpiStoreRope = 2,  // store with per-head RMSNorm + rotary embedding (256-wide tiles only)
 };
+
+// Warp roles: warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2 .. 2 + EW - 1
+// epilogue.  A warp may only read the TMEM lane quarter (warp id % 4); with EW = 8 two warps
+// share each quarter and take alternate 64-column sub-tiles.  Eight warps halve the part of
+// the epilogue that nothing overlaps (the last tile of every CTA), which matters when a CTA
+// runs only three or four tiles: 1B prefill step at 8 192 tokens 16.33 -> 15.93 ms on B200,
+// unchanged at 65 536 tokens (there the epilogue already ran under the next tile's main
+// loop).  The fused RoPE epilogue keeps four warps and its 255 registers per thread.
+template <int BN, int EPI>
+__host__ __device__ constexpr int gemm_epi_warps() {
+  return (BN == 256 && EPI != kEpiStoreRope) ? 8 : 4;
+}
+template <int BN, int EPI>
+__host__ __device__ constexpr int gemm_threads() {
+  return 64 + 32 * gemm_epi_warps<BN, EPI>();
+}
 
 struct GemmParams {
   int M;                   // rows of A
@@ -85,19 +101,22 @@ struct GemmParams {
 
 // CG = 1: one CTA per 128-row tile.  CG = 2: a CTA pair per 256-row tile (cta_group::2); each
 // CTA stages its 128 rows of A and its BN / 2 rows of B.
-template <int BN, int CG>
+template <int BN, int CG, int EW = 4>
 struct GemmSmem {
   static constexpr int kABytes = kBlockM * kBlockK * 2;
   static constexpr int kBBytes = (BN / CG) * kBlockK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  // as many stages as fit in 192 KB (4 x 48 KB, 6 x 32 KB, 8 x 24 KB, 9 x 20 KB): narrow tiles
-  // run with few rows, where the K loop is bound by load latency, not bandwidth
-  static constexpr int kStages = (196608 / kStageBytes) > 12 ? 12 : (196608 / kStageBytes);
+  // epilogue staging: EW warps x 2 buffers
+  static constexpr int kEpiBytes = EW * 2 * kEpiStageBytes;
+  // as many stages as fit beside it in 224 KB (with four epilogue warps: 4 x 48 KB, 6 x 32 KB,
+  // 8 x 24 KB, 9 x 20 KB): narrow tiles run with few rows, where the K loop is bound by load
+  // latency, not bandwidth
+  static constexpr int kTileBudget = 196608 + 4 * 2 * kEpiStageBytes - kEpiBytes;
+  static constexpr int kStages = (kTileBudget / kStageBytes) > 12 ? 12 : (kTileBudget / kStageBytes);
   static constexpr int kTileBytes = kStages * kStageBytes;
-  // after the tiles: epilogue staging (4 warps x 2 buffers), barriers, TMEM base, abort
-  // flag, schedule tables
+  // after the tiles: epilogue staging, barriers, TMEM base, abort flag, schedule tables
   static constexpr int kEpiOff = kTileBytes;
-  static constexpr int kBarOff = kEpiOff + 4 * 2 * kEpiStageBytes;
+  static constexpr int kBarOff = kEpiOff + kEpiBytes;
   static constexpr int kNumBars = 2 * kStages + 4;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
   static constexpr int kPrefixOff = kMiscOff + 16;
@@ -159,12 +178,15 @@ __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v 
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
 
 template <int BN, int EPI, int CG>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(gemm_threads<BN, EPI>(), 1)
 gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
                        const __grid_constant__ CUtensorMap tmB0,
                        const __grid_constant__ CUtensorMap tmA1,
                        const __grid_constant__ CUtensorMap tmB1, const GemmParams p) {
-  using L = GemmSmem<BN, CG>;
+  constexpr int EW = gemm_epi_warps<BN, EPI>();
+  constexpr int kEpiHalves = EW / 4;               // epilogue warps per TMEM lane quarter
+  constexpr bool kStore = (EPI == kEpiStore || EPI == kEpiStoreRope);
+  using L = GemmSmem<BN, CG, EW>;
   constexpr int S = L::kStages;
   constexpr int kTileM = kBlockM * CG;             // rows per tile (per CTA pair when CG = 2)
   const uint32_t crank = (CG == 2) ? cluster_ctarank() : 0u;  // 0 = leader
@@ -202,7 +224,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full[a], 1);
-      mbar_init(&tmem_empty[a], 4 * CG);  // one arrival per epilogue warp (of both CTAs)
+      mbar_init(&tmem_empty[a], EW * CG);  // one arrival per epilogue warp (of both CTAs)
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -341,7 +363,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------ epilogue (4 warps)
+    // ------------------------------------------------------------ epilogue (EW warps)
     // A thread owns one accumulator row (TMEM lane), but rows are 32 different cache lines:
     // results are therefore staged through a per-warp shared-memory buffer (32 rows x 64
     // bf16 columns = 4 KB, 16-byte chunks XOR-swizzled by row so both access patterns are
@@ -350,6 +372,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
     // cp.async one and two sub-tiles ahead — the first two before the accumulator is even
     // complete — so its latency stays off the critical path.
     const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+    const int ehalf = (warp - 2) >> 2;   // which of the quarter's warps (takes sub-tiles ehalf, ehalf + kEpiHalves, ...)
     uint8_t* stage0 = smem + L::kEpiOff + (warp - 2) * (2 * kEpiStageBytes);
     const int crow_l = lane >> 3;   // row within a group of 4 rows (coalesced phase)
     const int cchunk = lane & 7;    // 16-byte chunk within the 128-byte row
@@ -364,7 +387,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
       const int r = c.m0 + static_cast<int>(crank) * kBlockM + quarter * 32 + lane;
       const bool row_ok = r < c.row_end;
       int orow = 0;
-      if constexpr (EPI == kEpiStore) {
+      if constexpr (kStore) {
         orow = row_ok ? (p.row_map ? p.row_map[r] : r) : 0;
       } else {
         orow = row_ok ? r : 0;
@@ -379,7 +402,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
       }
       // destination row addresses when rows are pushed to arbitrary (peer) memory
       long long cptr[8];
-      const bool use_ptrs = (EPI == kEpiStore) && p.out_row_ptrs != nullptr;
+      const bool use_ptrs = kStore && p.out_row_ptrs != nullptr;
       if (use_ptrs) {
         const long long mine = row_ok ? p.out_row_ptrs[r] : 0;
 #pragma unroll
@@ -390,16 +413,17 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
         }
       }
       // output columns of this tile and the number of 64-column sub-tiles
-      const int ocol_base = (EPI == kEpiStore) ? c.n0 : c.n0 / 2;
-      const int ocol_span = (EPI == kEpiStore) ? BN : BN / 2;
+      const int ocol_base = kStore ? c.n0 : c.n0 / 2;
+      const int ocol_span = kStore ? BN : BN / 2;
       const int ocols = min(ocol_span, p.out_cols - ocol_base);
       const int nsub = (ocols + kEpiCols - 1) / kEpiCols;
       const int col_end = ocol_base + ocols;   // one past the last output column of this tile
-      const bool has_res = (EPI == kEpiStore) && p.residual != nullptr;
+      const bool has_res = kStore && p.residual != nullptr;
 
-      auto fetch_residual = [&](int sub) {
-        uint8_t* buf = stage0 + (sub & 1) * kEpiStageBytes;
-        const int col = ocol_base + sub * kEpiCols + cchunk * 8;
+      // i-th sub-tile of THIS warp (sub-tile index ehalf + i * kEpiHalves of the tile)
+      auto fetch_residual = [&](int i) {
+        uint8_t* buf = stage0 + (i & 1) * kEpiStageBytes;
+        const int col = ocol_base + (ehalf + i * kEpiHalves) * kEpiCols + cchunk * 8;
         if (col < col_end) {
 #pragma unroll
           for (int it = 0; it < 8; ++it) {
@@ -412,12 +436,12 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
         }
         cp_async_commit();
       };
-      if (has_res) {
+      if (has_res && ehalf < nsub) {
         fetch_residual(0);
-        if (nsub > 1) fetch_residual(1);
+        if (ehalf + kEpiHalves < nsub) fetch_residual(1);
       }
       const __nv_bfloat16* res2_row = nullptr;
-      if constexpr (EPI == kEpiStore) {
+      if constexpr (kStore) {
         if (p.residual2 && row_ok) {
           // read lane-per-row (uncoalesced): pull the row's bytes into L2 ahead of time
           res2_row = p.residual2 + static_cast<long long>(r) * p.ldr2;
@@ -450,11 +474,11 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
       };
 
       bool rope_tile = false;
-      if constexpr (EPI == kEpiStore && BN == 256) {
+      if constexpr (EPI == kEpiStoreRope && BN == 256) {
         rope_tile = p.rope_cos != nullptr && c.n0 < p.rope_cols;
       }
       if (rope_tile) {
-        if constexpr (EPI == kEpiStore && BN == 256) {
+        if constexpr (EPI == kEpiStoreRope && BN == 256) {
           // Q/K RMSNorm + RoPE on the fp32 accumulators (reference: attention.py:138-155): the
           // tile holds two heads of 128 columns; a thread owns a row, so the norm is a plain
           // per-thread sum and rotate-half pairs column j with j + 64 of the same thread.
@@ -539,83 +563,88 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
         }
       } else {
 #pragma unroll 1
-      for (int sub = 0; sub < nsub; ++sub) {
-        uint8_t* buf = stage0 + (sub & 1) * kEpiStageBytes;
+      for (int i = 0, sub = ehalf; sub < nsub; ++i, sub += kEpiHalves) {
+        uint8_t* buf = stage0 + (i & 1) * kEpiStageBytes;
         const int col0 = ocol_base + sub * kEpiCols;
-        if constexpr (EPI == kEpiStore) {
-          uint4 r2[8];
-          if (res2_row) {
+        if constexpr (kStore) {
+          // two rounds of 32 accumulator columns (keeps the register count of the
+          // eight-warp variants inside their budget)
+#pragma unroll 1
+          for (int hh = 0; hh < 2; ++hh) {
+            const int colh = col0 + hh * 32;
+            uint4 r2[4];
+            if (res2_row) {
 #pragma unroll
-            for (int q = 0; q < 8; ++q)
-              if (col0 + q * 8 < col_end) r2[q] = ld_nc_v4(res2_row + col0 + q * 8);
-          }
-          uint4 bb[8];
-          if (p.bias) {   // same for every row: issued before the TMEM loads, L1 hits
-#pragma unroll
-            for (int q = 0; q < 8; ++q)
-              if (col0 + q * 8 < col_end) bb[q] = *reinterpret_cast<const uint4*>(p.bias + col0 + q * 8);
-          }
-          uint32_t v[64];
-          tmem_ld32(t_row + sub * 64, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
-          tmem_ld32(t_row + sub * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
-          if (has_res) {
-            if (sub + 1 < nsub) cp_async_wait<1>(); else cp_async_wait<0>();
-            __syncwarp();
-          }
-          tmem_ld_wait();
-#pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            const int col = col0 + q * 8;
-            float f[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[q * 8 + j]);
-            uint8_t* slot = buf + own_off + ((q ^ (lane & 7)) << 4);
-            if (col < col_end) {
-              if (p.bias) {
-                const uint32_t bw[4] = {bb[q].x, bb[q].y, bb[q].z, bb[q].w};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  f[2 * j] += fminf(fmaxf(bf16_lo(bw[j]), p.bias_lo), p.bias_hi);
-                  f[2 * j + 1] += fminf(fmaxf(bf16_hi(bw[j]), p.bias_lo), p.bias_hi);
-                }
-              }
-              if (has_res && row_ok) {
-                const uint4 rr = *reinterpret_cast<const uint4*>(slot);
-                const uint32_t rw[4] = {rr.x, rr.y, rr.z, rr.w};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  f[2 * j] += bf16_lo(rw[j]);
-                  f[2 * j + 1] += bf16_hi(rw[j]);
-                }
-              }
-              if (res2_row) {
-                const uint32_t rw[4] = {r2[q].x, r2[q].y, r2[q].z, r2[q].w};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  f[2 * j] += bf16_lo(rw[j]);
-                  f[2 * j + 1] += bf16_hi(rw[j]);
-                }
-              }
-              if (p.do_clamp) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) f[j] = fminf(fmaxf(f[j], p.clamp_lo), p.clamp_hi);
-              }
+              for (int q = 0; q < 4; ++q)
+                if (colh + q * 8 < col_end) r2[q] = ld_nc_v4(res2_row + colh + q * 8);
             }
-            uint4 o;
-            o.x = pack_bf16x2(f[0], f[1]);
-            o.y = pack_bf16x2(f[2], f[3]);
-            o.z = pack_bf16x2(f[4], f[5]);
-            o.w = pack_bf16x2(f[6], f[7]);
-            *reinterpret_cast<uint4*>(slot) = o;
+            uint4 bb[4];
+            if (p.bias) {   // same for every row: issued before the TMEM loads, L1 hits
+#pragma unroll
+              for (int q = 0; q < 4; ++q)
+                if (colh + q * 8 < col_end) bb[q] = *reinterpret_cast<const uint4*>(p.bias + colh + q * 8);
+            }
+            uint32_t v[32];
+            tmem_ld32(t_row + sub * 64 + hh * 32, v);
+            if (has_res && hh == 0) {
+              if (sub + kEpiHalves < nsub) cp_async_wait<1>(); else cp_async_wait<0>();
+              __syncwarp();
+            }
+            tmem_ld_wait();
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int col = colh + q * 8;
+              float f[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[q * 8 + j]);
+              uint8_t* slot = buf + own_off + (((hh * 4 + q) ^ (lane & 7)) << 4);
+              if (col < col_end) {
+                if (p.bias) {
+                  const uint32_t bw[4] = {bb[q].x, bb[q].y, bb[q].z, bb[q].w};
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    f[2 * j] += fminf(fmaxf(bf16_lo(bw[j]), p.bias_lo), p.bias_hi);
+                    f[2 * j + 1] += fminf(fmaxf(bf16_hi(bw[j]), p.bias_lo), p.bias_hi);
+                  }
+                }
+                if (has_res && row_ok) {
+                  const uint4 rr = *reinterpret_cast<const uint4*>(slot);
+                  const uint32_t rw[4] = {rr.x, rr.y, rr.z, rr.w};
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    f[2 * j] += bf16_lo(rw[j]);
+                    f[2 * j + 1] += bf16_hi(rw[j]);
+                  }
+                }
+                if (res2_row) {
+                  const uint32_t rw[4] = {r2[q].x, r2[q].y, r2[q].z, r2[q].w};
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    f[2 * j] += bf16_lo(rw[j]);
+                    f[2 * j + 1] += bf16_hi(rw[j]);
+                  }
+                }
+                if (p.do_clamp) {
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) f[j] = fminf(fmaxf(f[j], p.clamp_lo), p.clamp_hi);
+                }
+              }
+              uint4 o;
+              o.x = pack_bf16x2(f[0], f[1]);
+              o.y = pack_bf16x2(f[2], f[3]);
+              o.z = pack_bf16x2(f[4], f[5]);
+              o.w = pack_bf16x2(f[6], f[7]);
+              *reinterpret_cast<uint4*>(slot) = o;
+            }
           }
         } else {
           // SwiGLU: accumulator columns [0, BN/2) hold gate, [BN/2, BN) hold up, for output
           // columns (n0 / 2) .. (n0 / 2) + BN / 2; 32 output columns per TMEM round trip.
           // narrow tiles (BN / 2 <= 32 output columns) need a single round trip; columns read
           // past the tile's own are never stored
-          constexpr int kHalves = (BN / 2 > 32) ? 2 : 1;
+          constexpr int kRounds = (BN / 2 > 32) ? 2 : 1;
 #pragma unroll
-          for (int half = 0; half < kHalves; ++half) {
+          for (int half = 0; half < kRounds; ++half) {
             uint32_t g[32], u[32];
             tmem_ld32(t_row + sub * 64 + half * 32, g);
             tmem_ld32(t_row + BN / 2 + sub * 64 + half * 32, u);
@@ -638,7 +667,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
         __syncwarp();
         copy_out(buf, col0);
         __syncwarp();  // the buffer may be refilled from here on
-        if (has_res && sub + 2 < nsub) fetch_residual(sub + 2);
+        if (has_res && sub + 2 * kEpiHalves < nsub) fetch_residual(i + 2);
       }
       }  // plain tiles
       // this warp is done reading the accumulator
