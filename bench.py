@@ -34,8 +34,8 @@ MODEL = dict(vocab_size=32000, hidden_size=2048, intermediate_size=5632, num_hid
              num_attention_heads=16, num_key_value_heads=8, num_experts=8)
 GLOBAL_BATCH, SEQ_LEN = 32, 2048
 # DRAM traffic of one cd_mu_qkv launch per token, from the ncu capture summarised in
-# profiles/gemm_bf16_sm100_1b_layer_small_case.md (562 + 182 MB at 24 576 tokens)
-MU_QKV_DRAM_BYTES_PER_TOKEN = 743.43e6 / 24576
+# profiles/gemm_bf16_sm100_1b_layer_small_case.md (555 + 182 MB at 24 576 tokens)
+MU_QKV_DRAM_BYTES_PER_TOKEN = 737.46e6 / 24576
 
 
 def zipf_probabilities(vocab_size: int, s: float) -> torch.Tensor:
@@ -318,7 +318,7 @@ def run_ours(args):
                     "traffic": (round(MU_QKV_DRAM_BYTES_PER_TOKEN * local_tokens)
                                 if dom == "mu_qkv" else None),
                     "traffic_source": "ncu dram__bytes_read+write of cd_mu_qkv_rope at 24576 tokens "
-                                      "(743 MB), scaled per token; profiles/"}
+                                      "(737 MB), scaled per token; profiles/"}
     gpu_launches = sum(v[2] for v in prof.values())
 
     line = {
