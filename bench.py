@@ -313,6 +313,9 @@ def run_ours(args):
         k = kernels[dom]
         roofline = {"bound": "tensor", "kernel": "gemm_bf16_sm100_kernel", "entry": dom, "achieved": k["tflops"], "peak": pk["bf16_tflops"],
                     "peak_source": pk["source"] + " burst", "unit": "TFLOP/s", "frac": k["frac"],
+                    "peak_sustained": pk["bf16_tflops_sustained"],
+                    "frac_sustained": (round(k["tflops"] / pk["bf16_tflops_sustained"], 4)
+                                       if pk["bf16_tflops_sustained"] else None),
                     "flop_per_launch": fl[dom] * local_tokens,
                     "ms_per_launch": round(k["ms_total"] / k["launches"], 4),
                     "traffic": (round(MU_QKV_DRAM_BYTES_PER_TOKEN * local_tokens)

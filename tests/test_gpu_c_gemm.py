@@ -273,3 +273,60 @@ def test_bounded_waits_report_a_stalled_pipeline_and_leave_the_device_usable():
     y = ops.linear(x.cuda(), w.cuda())
     _fetch()
     _close(y, x.float() @ w.float().t())
+
+
+# ------------------------------------------------------------------ per-row destinations
+@pytest.mark.parametrize("T,E,I_e,H", [(300, 4, 64, 256), (4500, 8, 704, 2048), (64, 8, 96, 512)])
+def test_moe_down_push_stores_rows_at_their_addresses(T, E, I_e, H):
+    """cd_moe_down_push: row j of the routed down projection lands at out_row_ptrs[j] — here
+    addresses inside two local buffers in a shuffled order (on several GPUs they point into
+    the peers' return buffers).  Covers the wide-tile epilogue (eight warps) and the narrow one."""
+    from complexity_deep_b200 import ops
+    g = torch.Generator().manual_seed(T + E)
+    counts = torch.multinomial(torch.ones(E), T, replacement=True, generator=g).bincount(minlength=E)
+    counts[1] = 0 if E > 2 else counts[1]                      # an expert without rows
+    counts[0] += T - int(counts.sum())
+    offsets = torch.zeros(E + 1, dtype=torch.int32)
+    offsets[1:] = counts.cumsum(0)
+    h = _rand(g, T, I_e)
+    wd = _rand(g, E, H, I_e, scale=0.05)
+    dest = torch.randperm(T, generator=g)                      # row j -> slot dest[j]
+    bufs = [torch.zeros(T, H, dtype=BF, device="cuda") for _ in range(2)]
+    ptrs = torch.tensor([bufs[int(d) % 2].data_ptr() + (int(d) // 2) * H * 2 for d in dest],
+                        dtype=torch.int64)
+    ops.moe_down_push(h.cuda(), wd.cuda(), offsets.cuda(), E, ptrs.cuda())
+    _fetch()
+    ref = torch.zeros(T, H)
+    for e in range(E):
+        lo, hi = int(offsets[e]), int(offsets[e + 1])
+        ref[lo:hi] = h[lo:hi].float() @ wd[e].float().t()
+    got = torch.stack([bufs[int(d) % 2][int(d) // 2] for d in dest]).cpu()
+    _close(got, ref)
+
+
+def test_push_rows_places_sorted_rows_in_owner_buffers():
+    """cd_push_rows with two 'ranks' whose receive buffers are local: every expert-sorted row
+    is copied, bit for bit, to row push_base[e] + (j - offsets[e]) of the buffer of the rank
+    that owns expert e."""
+    from complexity_deep_b200 import ops
+    T, E, H, per_rank = 1000, 8, 512, 4
+    g = torch.Generator().manual_seed(3)
+    eid = torch.sort(torch.randint(0, E, (T,), generator=g)).values
+    counts = eid.bincount(minlength=E)
+    offsets = torch.zeros(E + 1, dtype=torch.int32)
+    offsets[1:] = counts.cumsum(0)
+    x = _rand(g, T, H)
+    base = torch.zeros(E, dtype=torch.int32)                   # position inside the owner's buffer
+    for r in range(E // per_rank):
+        acc = 7 * r                                            # some rows already taken by other sources
+        for e in range(r * per_rank, (r + 1) * per_rank):
+            base[e] = acc
+            acc += int(counts[e])
+    bufs = [torch.full((T + 16, H), -1.0, dtype=BF, device="cuda") for _ in range(E // per_rank)]
+    peer = torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64, device="cuda")
+    ops.push_rows(x.cuda(), offsets.cuda(), base.cuda(), E, per_rank, peer.data_ptr())
+    torch.cuda.synchronize()
+    for e in range(E):
+        lo, hi = int(offsets[e]), int(offsets[e + 1])
+        got = bufs[e // per_rank][int(base[e]):int(base[e]) + hi - lo].cpu()
+        assert torch.equal(got, x[lo:hi]), e
