@@ -7,10 +7,13 @@ What changes is how q, k, v are produced:
   * one K-concatenated GEMM ``[x | mu_prev] @ [W ; W_mu]^T`` (cd_mu_qkv) reading x and
     mu_prev in place and the stacked weights from a cache, instead of a ``torch.cat`` of the
     activations, three ``torch.cat`` of the weights and three GEMMs per call (:120-127);
-  * Q/K RMSNorm and RoPE applied in place by one kernel (cd_qk_norm_rope) instead of
-    ~10 elementwise passes (:138-155);
+  * Q/K RMSNorm and RoPE applied in that GEMM's epilogue (cd_mu_qkv_rope, head size 128) or
+    in place by one kernel (cd_qk_norm_rope) instead of ~10 elementwise passes (:138-155);
   * grouped KV heads are handed to SDPA with ``enable_gqa`` instead of being copied by
-    ``repeat_interleave`` (:164-165) — the same arithmetic without the copies;
+    ``repeat_interleave`` (:164-165) — the same arithmetic without the copies; with one
+    query per sequence the cache is streamed once by cd_decode_attention;
+  * the KV cache grows in place instead of by ``torch.cat`` (:158-161), or lives in a
+    fixed-capacity ``StaticKVCache`` whose decode steps can be replayed from a CUDA graph;
   * ``o_proj`` runs on the tcgen05 GEMM, optionally with the residual add fused.
 """
 from __future__ import annotations

@@ -33,7 +33,7 @@ extern "C" {
 #define CD_ERR_UNSUPPORTED 3  /* shape outside what the kernels implement */
 #define CD_ERR_TIMEOUT 4      /* a kernel gave up on a bounded wait (reported by cd_status_fetch) */
 
-/* ABI version of this header (bumped on any signature change). */
+/* ABI version of this header (bumped on any signature change; currently 2). */
 int cd_version(void);
 /* Static text for a CD_* code. */
 const char* cd_error_string(int status);
