@@ -46,6 +46,13 @@ __host__ __device__ inline int chunk_rows(int L, int splits) {
   return (((L + splits - 1) / splits) + 15) / 16 * 16;
 }
 
+// programmatic dependent launch: wait for the previous kernel of the stream before touching
+// memory, then let the next kernel be scheduled (its launch hides under this one)
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
   const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
@@ -83,6 +90,8 @@ decode_attn_partial_kernel(const __nv_bfloat16* __restrict__ q, long long q_stri
   __shared__ __align__(16) unsigned char s_raw[kSmemBytes];
   __shared__ float s_m[16][G], s_l[16][G];
 
+  griddep_wait();
+  griddep_launch_dependents();
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int splits = gridDim.x;
   if (len_dev) {
@@ -254,6 +263,8 @@ __global__ void __launch_bounds__(128)
 decode_attn_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                            int splits, int D, __nv_bfloat16* __restrict__ out, int B, int hkv,
                            int L, const int* __restrict__ len_dev) {
+  griddep_wait();
+  griddep_launch_dependents();
   const long long row0 = static_cast<long long>(blockIdx.x) * splits;   // (b, h)
   if (len_dev) splits = choose_splits(B, hkv, max(0, min(L, __ldg(len_dev))));
   float m = -FLT_MAX;
@@ -278,9 +289,9 @@ cudaError_t launch_partial(int G, dim3 grid, cudaStream_t st, const __nv_bfloat1
                            float* pml, const int* len_dev) {
 #define CDEEP_ATTN_CASE(GG)                                                                     \
   case GG:                                                                                      \
-    decode_attn_partial_kernel<DPL, GG><<<grid, kAttnThreads, 0, st>>>(                         \
-        q, qsb, k, v, sb, sh, stt, mask, msb, scale, L, chunk, hq, pa, pml, len_dev);           \
-    break;
+    return launch_kernel(decode_attn_partial_kernel<DPL, GG>, grid, dim3(kAttnThreads), 0, st,  \
+                         q, qsb, k, v, sb, sh, stt, mask, msb, scale, L, chunk, hq, pa, pml,    \
+                         len_dev);
   switch (G) {
     CDEEP_ATTN_CASE(1)
     CDEEP_ATTN_CASE(2)
@@ -328,10 +339,8 @@ cudaError_t launch_decode_attention(const void* q, long long q_stride_b, const v
   else
     return cudaErrorInvalidValue;
   if (e != cudaSuccess) return e;
-  decode_attn_combine_kernel<<<B * hq, 128, 0, stream>>>(part_acc, part_ml, splits, D,
-                                                        static_cast<__nv_bfloat16*>(out), B, hkv,
-                                                        L, kv_len_dev);
-  return cudaGetLastError();
+  return launch_kernel(decode_attn_combine_kernel, dim3(B * hq), dim3(128), 0, stream, part_acc,
+                       part_ml, splits, D, static_cast<__nv_bfloat16*>(out), B, hkv, L, kv_len_dev);
 }
 
 }  // namespace cdeep

@@ -242,7 +242,12 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
       tmem_alloc(tmem_base_slot, kTmemCols);
       tmem_relinquish();
     }
-  } else if (warp == 2 && lane == 0) {
+  }
+  // Everything above touched only this CTA's shared memory, TMEM and the kernel parameters,
+  // so it may run while the previous kernel of the stream is still finishing.
+  griddep_wait();
+  griddep_launch_dependents();
+  if (warp == 2 && lane == 0) {
     int acc = 0;
     prefix[0] = 0;
     for (int g = 0; g < p.num_groups; ++g) {

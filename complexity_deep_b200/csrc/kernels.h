@@ -1,9 +1,37 @@
 // Internal launch functions shared by the translation units of libcdeep.so.
 #pragma once
 #include <cstddef>
+#include <cstdlib>
 #include <cuda_runtime.h>
 
 namespace cdeep {
+
+// Programmatic dependent launch is on unless CDEEP_PDL=0 (tuning / debugging aid).
+inline bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("CDEEP_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
+// <<<grid, block, smem, stream>>> with programmatic stream serialisation allowed (see
+// griddep_wait in ptx.cuh: every kernel waits for its predecessor before touching memory).
+template <typename... P, typename... A>
+inline cudaError_t launch_kernel(void (*kern)(P...), dim3 grid, dim3 block, size_t smem,
+                                 cudaStream_t stream, A&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<A&&>(args)...);
+}
 
 size_t route_workspace_bytes(int T, int E);
 cudaError_t launch_route(const long long* ids, const long long* table, int V, int E, int T,

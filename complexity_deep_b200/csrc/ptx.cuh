@@ -95,6 +95,18 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
   }
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// Every kernel of this library is launched with programmatic stream serialisation allowed:
+// it may be scheduled while the previous kernel of the stream is still running (its launch
+// latency and set-up then hide under that kernel's tail).  griddep_wait() blocks until the
+// previous kernel has completed and its writes are visible; it comes before the first access
+// to global memory.  griddep_launch_dependents() lets the NEXT kernel be scheduled; it is
+// called after the wait, so at most two consecutive kernels ever overlap.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ---------------------------------------------------------------- cp.async (16-byte)
 __device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gsrc) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc)

@@ -18,6 +18,13 @@ namespace cdeep {
 
 namespace {
 
+// programmatic dependent launch (same two instructions as in ptx.cuh, which this file does
+// not include): wait for the previous kernel of the stream, then let the next one be scheduled
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -40,6 +47,8 @@ rmsnorm_rows_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
                     const __nv_bfloat16* __restrict__ w, float eps,
                     __nv_bfloat16* __restrict__ sum_out, __nv_bfloat16* __restrict__ out,
                     const int* __restrict__ dst_rows, int T, int H) {
+  griddep_wait();               // the previous kernel's writes are visible from here
+  griddep_launch_dependents();  // the next kernel may be scheduled
   const int row = blockIdx.x * kNormWarps + (threadIdx.x >> 5);
   if (row >= T) return;
   const int lane = threadIdx.x & 31;
@@ -105,6 +114,8 @@ rmsnorm_generic_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
                        const __nv_bfloat16* __restrict__ w, float eps,
                        __nv_bfloat16* __restrict__ sum_out, __nv_bfloat16* __restrict__ out,
                        const int* __restrict__ dst_rows, int T, int H) {
+  griddep_wait();               // the previous kernel's writes are visible from here
+  griddep_launch_dependents();  // the next kernel may be scheduled
   __shared__ float s_part[4];
   const int row = blockIdx.x;
   const __nv_bfloat16* xr = x + static_cast<size_t>(row) * H;
@@ -136,6 +147,8 @@ rmsnorm_generic_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
 __global__ void __launch_bounds__(256)
 gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ src_rows,
                    __nv_bfloat16* __restrict__ out, int T, int H) {
+  griddep_wait();               // the previous kernel's writes are visible from here
+  griddep_launch_dependents();  // the next kernel may be scheduled
   const int warps_per_block = blockDim.x >> 5;
   const int j = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
   if (j >= T) return;
@@ -203,6 +216,8 @@ qk_norm_rope_kernel(__nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __rest
                     const __nv_bfloat16* __restrict__ k_w, const float* __restrict__ cos_t,
                     const float* __restrict__ sin_t, float eps, int T, int S, int pos0, int hq,
                     int hkv, int D, KvAppend app) {
+  griddep_wait();               // the previous kernel's writes are visible from here
+  griddep_launch_dependents();  // the next kernel may be scheduled
   const int heads = hq + hkv;
   const long long wid = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (wid >= static_cast<long long>(T) * heads) return;
@@ -271,6 +286,8 @@ qk_norm_rope_vec_kernel(__nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __
                         const __nv_bfloat16* __restrict__ k_w, const float* __restrict__ cos_t,
                         const float* __restrict__ sin_t, float eps, int T, int S, int pos0, int hq,
                         int hkv, int D, KvAppend app) {
+  griddep_wait();               // the previous kernel's writes are visible from here
+  griddep_launch_dependents();  // the next kernel may be scheduled
   const int heads = hq + hkv;
   const int half = D >> 1;
   const int lph = half >> 3;        // lanes per head
@@ -396,10 +413,11 @@ cudaError_t launch_rmsnorm(const void* x, const void* residual, const void* weig
   auto ob = static_cast<__nv_bfloat16*>(out);
   if ((H & 255) == 0 && H <= kMaxVec * 256) {
     const int blocks = (T + kNormWarps - 1) / kNormWarps;
-    rmsnorm_rows_kernel<<<blocks, kNormWarps * 32, 0, stream>>>(xb, rb, wb, eps, sb, ob, dst_rows,
-                                                               T, H);
+    return launch_kernel(rmsnorm_rows_kernel, dim3(blocks), dim3(kNormWarps * 32), 0, stream, xb, rb,
+                         wb, eps, sb, ob, dst_rows, T, H);
   } else {
-    rmsnorm_generic_kernel<<<T, 128, 0, stream>>>(xb, rb, wb, eps, sb, ob, dst_rows, T, H);
+    return launch_kernel(rmsnorm_generic_kernel, dim3(T), dim3(128), 0, stream, xb, rb, wb, eps, sb,
+                         ob, dst_rows, T, H);
   }
   return cudaGetLastError();
 }
@@ -408,9 +426,9 @@ cudaError_t launch_gather_rows(const void* x, const int* src_rows, void* out, in
                                cudaStream_t stream) {
   if (T == 0) return cudaSuccess;
   const int wpb = 8;
-  gather_rows_kernel<<<(T + wpb - 1) / wpb, wpb * 32, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(x), src_rows, static_cast<__nv_bfloat16*>(out), T, H);
-  return cudaGetLastError();
+  return launch_kernel(gather_rows_kernel, dim3((T + wpb - 1) / wpb), dim3(wpb * 32), 0, stream,
+                       static_cast<const __nv_bfloat16*>(x), src_rows,
+                       static_cast<__nv_bfloat16*>(out), T, H);
 }
 
 cudaError_t launch_push_rows(const void* x, const int* src_rows, const int* offsets,
@@ -448,20 +466,16 @@ cudaError_t launch_qk_norm_rope(void* qkv, const void* q_w, const void* k_w, con
   auto kw = static_cast<const __nv_bfloat16*>(k_w);
   if ((D & 15) == 0 && lph >= 1 && lph <= 32 && (lph & (lph - 1)) == 0 && aligned) {
     const unsigned nblocks = static_cast<unsigned>((T + 7) / 8);  // one warp per token
-    if (append)
-      qk_norm_rope_vec_kernel<true><<<nblocks, 256, 0, stream>>>(qb, qw, kw, cos_t, sin_t, eps, T,
-                                                                 S, pos0, hq, hkv, D, app);
-    else
-      qk_norm_rope_vec_kernel<false><<<nblocks, 256, 0, stream>>>(qb, qw, kw, cos_t, sin_t, eps, T,
-                                                                  S, pos0, hq, hkv, D, app);
-    return cudaGetLastError();
+    return append ? launch_kernel(qk_norm_rope_vec_kernel<true>, dim3(nblocks), dim3(256), 0, stream,
+                                  qb, qw, kw, cos_t, sin_t, eps, T, S, pos0, hq, hkv, D, app)
+                  : launch_kernel(qk_norm_rope_vec_kernel<false>, dim3(nblocks), dim3(256), 0, stream,
+                                  qb, qw, kw, cos_t, sin_t, eps, T, S, pos0, hq, hkv, D, app);
   }
   const long long warps = static_cast<long long>(T) * (hq + hkv);
   const int wpb = 8;
   const long long blocks = (warps + wpb - 1) / wpb;
-  qk_norm_rope_kernel<<<static_cast<unsigned>(blocks), wpb * 32, 0, stream>>>(
-      qb, qw, kw, cos_t, sin_t, eps, T, S, pos0, hq, hkv, D, app);
-  return cudaGetLastError();
+  return launch_kernel(qk_norm_rope_kernel, dim3(static_cast<unsigned>(blocks)), dim3(wpb * 32), 0,
+                       stream, qb, qw, kw, cos_t, sin_t, eps, T, S, pos0, hq, hkv, D, app);
 }
 
 }  // namespace cdeep
