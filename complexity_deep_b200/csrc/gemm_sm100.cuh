@@ -194,7 +194,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
   const int tstride = gridDim.x / CG;
   // Tiles up to 128 wide (few-row calls: an output tile is one chain of K/16 dependent MMA
   // instructions) accumulate even and odd K steps in two TMEM accumulators that the epilogue
-  // adds: two independent chains, measured 20 % less time per k-block.
+  // adds: two independent chains, measured 2-4 % less time per launch (K = 2048 ... 8192).
   constexpr int kChains = (BN <= 128 && CG == 1) ? 2 : 1;
   constexpr uint32_t kAccCols = kChains * BN;     // TMEM columns of one tile's accumulator(s)
   // two tiles in flight (main loop / epilogue); 32-wide tiles allocate more than they need
