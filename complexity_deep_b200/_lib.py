@@ -11,13 +11,14 @@ from ctypes import c_char_p, c_float, c_int, c_longlong, c_size_t, c_void_p
 
 LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libcdeep.so")
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 # name -> (restype, argtypes); mirrors include/cdeep.h one to one
 SIGNATURES = {
     "cd_version": (c_int, []),
     "cd_error_string": (c_char_p, [c_int]),
     "cd_last_cuda_error": (c_char_p, []),
+    "cd_max_groups": (c_int, []),
     "cd_status_fetch": (c_int, [ctypes.POINTER(c_int)]),
     "cd_selftest_wait_timeout": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "cd_route_workspace_bytes": (c_size_t, [c_int, c_int]),
@@ -28,6 +29,8 @@ SIGNATURES = {
                                 c_void_p, c_void_p, c_void_p, c_void_p]),
     "cd_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
                            c_int, c_int, c_void_p]),
+    "cd_rmsnorm_split": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int,
+                                 c_int, c_void_p]),
     "cd_gather_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "cd_qk_norm_rope": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int,
                                 c_int, c_int, c_int, c_int, c_int, c_void_p]),
@@ -42,14 +45,21 @@ SIGNATURES = {
     "cd_gate_up_packed_rows": (c_int, [c_int, c_int]),
     "cd_moe_up": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
                           c_int, c_void_p]),
+    "cd_moe_up_pair": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p,
+                               c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "cd_pack_gate_up": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                c_void_p]),
+    "cd_pack_down": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "cd_moe_down": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
-                            c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+                            c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                            c_void_p]),
     "cd_push_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int,
                              c_int, c_void_p]),
+    "cd_peer_barrier": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "cd_moe_down_push": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                  c_int, c_void_p]),
     "cd_moe_combine": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                               c_int, c_int, c_void_p]),
+                               c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "cd_mu_qkv": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                           c_void_p]),
     "cd_mu_qkv_rope_supported": (c_int, [c_int, c_int, c_int, c_int, c_int]),
@@ -58,7 +68,8 @@ SIGNATURES = {
                                c_int, c_int, c_int, c_void_p]),
     "cd_mu_proj": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_float, c_int, c_float, c_float,
                            c_void_p, c_int, c_int, c_void_p]),
-    "cd_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "cd_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                          c_int, c_int, c_void_p]),
 }
 
 _lib = None
@@ -92,5 +103,5 @@ def check(status: int, what: str) -> None:
     if status != 0:
         lib = load()
         msg = lib.cd_error_string(status).decode()
-        detail = lib.cd_last_cuda_error().decode() if status == 2 else ""
+        detail = lib.cd_last_cuda_error().decode() if status in (2, 3) else ""
         raise CdeepError(f"{what}: {msg}" + (f" ({detail})" if detail else ""))

@@ -12,7 +12,7 @@ import sys
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libcdeep.so")
-SOURCES = ["api.cu", "gemm.cu", "route.cu", "rowwise.cu", "attention_decode.cu"]
+SOURCES = ["api.cu", "gemm.cu", "route.cu", "rowwise.cu", "attention_decode.cu", "pack.cu"]
 HEADERS = ["ptx.cuh", "gemm_sm100.cuh", "kernels.h", os.path.join("..", "..", "include", "cdeep.h")]
 
 
@@ -31,24 +31,44 @@ def is_stale() -> bool:
     return any(os.path.exists(d) and os.path.getmtime(d) > built for d in deps)
 
 
+def _compile_one(nvcc: str, src: str, obj: str, verbose: bool):
+    cmd = [nvcc, "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
+           "-Xcompiler", "-fPIC", "-c", src, "-o", obj]
+    if verbose:
+        cmd[1:1] = ["-Xptxas", "-v"]
+    return src, subprocess.run(cmd, cwd=CSRC, capture_output=True, text=True)
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
-    """Compiles every CUDA source of the package into one shared library."""
+    """Compiles every CUDA source of the package (in parallel, one object per source, objects
+    of unchanged sources are re-used) and links them into one shared library."""
     if not force and not is_stale():
         return LIB_PATH
-    cmd = [
-        _nvcc(), "-O3", "-std=c++17",
-        "-gencode", "arch=compute_100a,code=sm_100a",
-        "-lineinfo", "-Xcompiler", "-fPIC", "-shared",
-        "-o", LIB_PATH,
-    ] + SOURCES
-    if verbose:
-        cmd.insert(1, "-Xptxas")
-        cmd.insert(2, "-v")
-    proc = subprocess.run(cmd, cwd=CSRC, capture_output=True, text=True)
-    if proc.returncode != 0:
-        raise RuntimeError("nvcc failed:\n" + proc.stdout + proc.stderr)
-    if verbose:
-        sys.stderr.write(proc.stderr)
+    from concurrent.futures import ThreadPoolExecutor
+    nvcc = _nvcc()
+    obj_dir = os.path.join(CSRC, "build")
+    os.makedirs(obj_dir, exist_ok=True)
+    headers = [os.path.join(CSRC, h) for h in HEADERS]
+    newest_header = max(os.path.getmtime(h) for h in headers if os.path.exists(h))
+    jobs, objs = [], []
+    for src in SOURCES:
+        obj = os.path.join(obj_dir, src.replace(".cu", ".o"))
+        objs.append(obj)
+        src_time = max(os.path.getmtime(os.path.join(CSRC, src)), newest_header)
+        if force or verbose or not os.path.exists(obj) or os.path.getmtime(obj) < src_time:
+            jobs.append((src, obj))
+    with ThreadPoolExecutor(max_workers=min(8, max(1, len(jobs)))) as pool:
+        results = list(pool.map(lambda j: _compile_one(nvcc, j[0], j[1], verbose), jobs))
+    for src, proc in results:
+        if proc.returncode != 0:
+            raise RuntimeError(f"nvcc failed on {src}:\n" + proc.stdout + proc.stderr)
+        if verbose:
+            sys.stderr.write(proc.stderr)
+    link = subprocess.run([nvcc, "-shared", "-Xcompiler", "-fPIC", "-gencode",
+                           "arch=compute_100a,code=sm_100a", "-o", LIB_PATH] + objs,
+                          cwd=CSRC, capture_output=True, text=True)
+    if link.returncode != 0:
+        raise RuntimeError("link failed:\n" + link.stdout + link.stderr)
     return LIB_PATH
 
 

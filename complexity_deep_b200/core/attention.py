@@ -268,10 +268,15 @@ class ComplexityAttention(nn.Module):
         return ops.linear(attn, self.o_proj.weight, tag="linear_o_proj").view(B, S, H), new_kv
 
     def forward_with_residual(self, hidden_states, residual, attention_mask=None,
-                              past_key_value=None, use_cache=False, mu_prev=None):
-        """Same as forward, returning ``residual + o_proj(attn)`` from the GEMM epilogue."""
+                              past_key_value=None, use_cache=False, mu_prev=None,
+                              residual_lo=None, want_lo=False):
+        """Same as forward, with ``residual (+ residual_lo) + o_proj(attn)`` computed in the GEMM
+        epilogue; returns (out, out_lo or None, new_kv) — out_lo is the low part of the
+        split-bf16 result when `want_lo`."""
         B, S, H = hidden_states.shape
         attn, new_kv = self._attend(hidden_states, attention_mask, past_key_value, use_cache,
                                     mu_prev)
-        out = ops.linear(attn, self.o_proj.weight, residual.reshape(B * S, H), tag="linear_o_proj")
-        return out.view(B, S, H), new_kv
+        out = ops.linear(attn, self.o_proj.weight, residual.reshape(B * S, H), tag="linear_o_proj",
+                         residual_lo=residual_lo, want_lo=want_lo)
+        out, out_lo = out if want_lo else (out, None)
+        return out.view(B, S, H), out_lo, new_kv

@@ -23,15 +23,16 @@ class SwiGLU(nn.Module):
         g, u = self.gate_proj.weight, self.up_proj.weight
         bn = ops.choose_block_n(g.shape[0])
         packed = self._derived.get(
-            "gate_up", (g, u), lambda: ops.pack_gate_up(g.detach()[None], u.detach()[None], bn))
+            "gate_up", (g, u),
+            lambda: ops.pack_gate_up(g.detach()[None].contiguous(), u.detach()[None].contiguous(), bn))
         return packed, bn
 
-    def _run(self, x2: torch.Tensor, residual=None) -> torch.Tensor:
+    def _run(self, x2: torch.Tensor, residual=None, residual_lo=None, want_lo: bool = False):
         packed, bn = self._packed()
         width = self.gate_proj.weight.shape[0]
         h = ops.moe_up(x2, None, 1, packed, width, bn)
         wd = self.down_proj.weight.detach()[None]  # [1, H, I]
-        return ops.moe_down(h, wd, None, None, None, 1, None, residual)
+        return ops.moe_down(h, wd, None, None, None, 1, None, residual, residual_lo, want_lo)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         ops.forward_only(x, "SwiGLU")

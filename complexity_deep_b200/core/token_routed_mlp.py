@@ -147,7 +147,8 @@ class TokenRoutedMLP(nn.Module):
         bn = ops.choose_block_n(self.expert_intermediate_size, rows, self.num_experts)
         packed = self._derived.get(
             f"routed_gate_up_{bn}", (g, u),
-            lambda: ops.pack_gate_up(g.detach().transpose(1, 2), u.detach().transpose(1, 2), bn))
+            lambda: ops.pack_gate_up(g.detach().contiguous(), u.detach().contiguous(), bn,
+                                     feature_major=False))
         return packed, bn
 
     def _packed_shared(self, rows: Optional[int] = None):
@@ -155,30 +156,41 @@ class TokenRoutedMLP(nn.Module):
         bn = ops.choose_block_n(g.shape[0], rows)
         packed = self._derived.get(
             f"shared_gate_up_{bn}", (g, u),
-            lambda: ops.pack_gate_up(g.detach()[None], u.detach()[None], bn))
+            lambda: ops.pack_gate_up(g.detach()[None].contiguous(), u.detach()[None].contiguous(), bn))
         return packed, bn
 
     def _down_routed(self) -> torch.Tensor:
         d = self.down_proj_w
         return self._derived.get("routed_down", (d,),
-                                 lambda: d.detach().transpose(1, 2).contiguous())  # [E, H, I_e]
+                                 lambda: ops.pack_down(d.detach().contiguous()))  # [E, H, I_e]
 
     # ------------------------------------------------------------------ compute
     def forward_sorted(self, x_sorted: torch.Tensor, routing: ops.Routing,
-                       residual: Optional[torch.Tensor]) -> torch.Tensor:
+                       residual: Optional[torch.Tensor],
+                       residual_lo: Optional[torch.Tensor] = None, want_lo: bool = False):
         """MoE on rows already grouped by expert; returns rows in ORIGINAL order,
-        ``out[perm[j]] = shared(x_j) + expert(x_j) (+ residual[perm[j]])``."""
+        ``out[perm[j]] = shared(x_j) + expert(x_j) (+ residual[perm[j]])``.  `residual_lo` /
+        `want_lo`: the residual stream as a split-bf16 pair (returns (out, out_lo))."""
         rows = x_sorted.shape[0]
+        if routing.perm.numel() != rows:
+            raise ValueError(f"token_ids has {routing.perm.numel()} entries for {rows} tokens")
         packed_r, bn_r = self._packed_routed(rows)
-        h_r = ops.moe_up(x_sorted, routing.offsets, self.num_experts, packed_r,
-                         self.expert_intermediate_size, bn_r)
         h_s = wd_s = None
         if self.use_shared_expert:
             packed_s, bn_s = self._packed_shared(rows)
-            h_s = ops.moe_up(x_sorted, None, 1, packed_s, self.shared_gate.weight.shape[0], bn_s)
             wd_s = self.shared_down.weight.detach()
+            I_s = self.shared_gate.weight.shape[0]
+        if self.use_shared_expert and bn_s == bn_r:
+            # routed and shared up-projections share one launch (one tail instead of two)
+            h_r, h_s = ops.moe_up_pair(x_sorted, routing.offsets, self.num_experts, packed_r,
+                                       self.expert_intermediate_size, packed_s, I_s, bn_r)
+        else:
+            h_r = ops.moe_up(x_sorted, routing.offsets, self.num_experts, packed_r,
+                             self.expert_intermediate_size, bn_r)
+            if self.use_shared_expert:
+                h_s = ops.moe_up(x_sorted, None, 1, packed_s, I_s, bn_s)
         return ops.moe_down(h_r, self._down_routed(), h_s, wd_s, routing.offsets,
-                            self.num_experts, routing.perm, residual)
+                            self.num_experts, routing.perm, residual, residual_lo, want_lo)
 
     def forward(self, hidden_states: torch.Tensor, token_ids: Optional[torch.Tensor] = None
                 ) -> torch.Tensor:
@@ -186,6 +198,8 @@ class TokenRoutedMLP(nn.Module):
         B, S, H = hidden_states.shape
         if token_ids is None:
             return self._forward_all_experts(hidden_states)
+        if token_ids.numel() != B * S:
+            raise ValueError(f"token_ids has {token_ids.numel()} entries for {B * S} tokens")
         routing = self.routing(token_ids)
         x2 = hidden_states.reshape(-1, H).contiguous()
         x_sorted = ops.gather_rows(x2, routing.perm)

@@ -20,7 +20,7 @@ static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t
 
 extern "C" {
 
-int cd_version(void) { return 2; }
+int cd_version(void) { return 3; }
 
 const char* cd_error_string(int status) {
   switch (status) {
@@ -34,6 +34,8 @@ const char* cd_error_string(int status) {
 }
 
 const char* cd_last_cuda_error(void) { return g_cuda_err; }
+
+int cd_max_groups(void) { return kMaxGroups; }
 
 int cd_status_fetch(int* h_status) {
   if (!h_status) return CD_ERR_INVALID;
@@ -92,11 +94,23 @@ int cd_rmsnorm(const void* x, const void* residual, const void* weight, float ep
                void* out, const int32_t* dst_rows, int T, int H, void* stream) {
   if (T < 0 || H < 1 || !weight) return CD_ERR_INVALID;
   if (T > 0 && (!x || !out)) return CD_ERR_INVALID;
+  if (sum_out && (!residual || sum_out == x)) return CD_ERR_INVALID;
   if ((H & 7) == 0 && !(aligned16(x) && aligned16(residual) && aligned16(weight) &&
                         aligned16(sum_out) && aligned16(out)))
     return CD_ERR_INVALID;
-  cudaError_t e =
-      launch_rmsnorm(x, residual, weight, eps, sum_out, out, dst_rows, T, H, as_stream(stream));
+  cudaError_t e = launch_rmsnorm(x, residual, weight, eps, sum_out, out, dst_rows, T, H,
+                                 as_stream(stream), false);
+  return e == cudaSuccess ? CD_OK : cuda_fail(e, "rmsnorm launch");
+}
+
+int cd_rmsnorm_split(const void* x_hi, const void* x_lo, const void* weight, float eps, void* out,
+                     const int32_t* dst_rows, int T, int H, void* stream) {
+  if (T < 0 || H < 1 || !weight) return CD_ERR_INVALID;
+  if (T > 0 && (!x_hi || !out)) return CD_ERR_INVALID;
+  if ((H & 7) == 0 && !(aligned16(x_hi) && aligned16(x_lo) && aligned16(weight) && aligned16(out)))
+    return CD_ERR_INVALID;
+  cudaError_t e = launch_rmsnorm(x_hi, x_lo, weight, eps, nullptr, out, dst_rows, T, H,
+                                 as_stream(stream), true);
   return e == cudaSuccess ? CD_OK : cuda_fail(e, "rmsnorm launch");
 }
 
@@ -166,6 +180,21 @@ int cd_gate_up_packed_rows(int I, int block_n) {
   return ((I + half - 1) / half) * block_n;
 }
 
+int cd_pack_gate_up(const void* gate, const void* up, void* packed, int G, int I, int H,
+                    int block_n, int feature_major, void* stream) {
+  if (G < 1 || I < 1 || H < 1 || !gate || !up || !packed) return CD_ERR_INVALID;
+  if (cd_gate_up_packed_rows(I, block_n) == 0 || 2 * G > 65535) return CD_ERR_INVALID;
+  cudaError_t e = launch_pack_gate_up(gate, up, packed, G, I, H, block_n, feature_major ? 1 : 0,
+                                      as_stream(stream));
+  return e == cudaSuccess ? CD_OK : cuda_fail(e, "pack_gate_up launch");
+}
+
+int cd_pack_down(const void* down, void* packed, int E, int I, int H, void* stream) {
+  if (E < 1 || E > 65535 || I < 1 || H < 1 || !down || !packed) return CD_ERR_INVALID;
+  cudaError_t e = launch_transpose(down, packed, E, I, H, as_stream(stream));
+  return e == cudaSuccess ? CD_OK : cuda_fail(e, "pack_down launch");
+}
+
 int cd_moe_up(const void* x_sorted, const int32_t* seg_offsets, int num_groups,
               const void* packed_w, void* h, int T, int H, int I, int block_n, void* stream) {
   if (T < 0 || H < 8 || I < 8 || (H & 7) || (I & 7) || num_groups < 1) return CD_ERR_INVALID;
@@ -188,10 +217,42 @@ int cd_moe_up(const void* x_sorted, const int32_t* seg_offsets, int num_groups,
                      as_stream(stream));
 }
 
+int cd_moe_up_pair(const void* x_sorted, const int32_t* seg_offsets, int num_groups,
+                   const void* packed_w, void* h, int I, const void* packed_shared, void* h_shared,
+                   int I_s, int T, int H, int block_n, void* stream) {
+  if (T < 0 || H < 8 || I < 8 || I_s < 8 || (H & 7) || (I & 7) || (I_s & 7) || num_groups < 1)
+    return CD_ERR_INVALID;
+  const int rows = cd_gate_up_packed_rows(I, block_n);
+  const int rows_s = cd_gate_up_packed_rows(I_s, block_n);
+  if (rows == 0 || rows_s == 0 || !packed_shared || !h_shared) return CD_ERR_INVALID;
+  GemmOperand op{};
+  op.a = x_sorted;
+  op.lda = H;
+  op.b = packed_w;
+  op.ldb = H;
+  op.b_rows = static_cast<long long>(rows) * num_groups;
+  op.b_group_rows = rows;
+  op.K = H;
+  GemmEpilogueArgs epi{};
+  epi.kind = kEpiSwiGLU;
+  epi.out = h;
+  epi.ldo = I;
+  epi.out_cols = I;
+  GemmSecond sec{};
+  sec.b = packed_shared;
+  sec.ldb = H;
+  sec.n_rows = rows_s;
+  sec.out = h_shared;
+  sec.ldo = I_s;
+  sec.out_cols = I_s;
+  return launch_gemm(T, rows, num_groups, seg_offsets, op, nullptr, epi, block_n,
+                     as_stream(stream), &sec);
+}
+
 int cd_moe_down(const void* h_routed, int I_e, const void* wd_routed, const void* h_shared,
                 int I_s, const void* wd_shared, const int32_t* seg_offsets, int E,
-                const int32_t* row_map, const void* residual, void* out, int T, int H,
-                void* stream) {
+                const int32_t* row_map, const void* residual, const void* residual_lo, void* out,
+                void* out_lo, int T, int H, void* stream) {
   if (T < 0 || H < 8 || (H & 7) || I_e < 8 || (I_e & 7) || E < 1) return CD_ERR_INVALID;
   if ((h_shared == nullptr) != (wd_shared == nullptr)) return CD_ERR_INVALID;
   if (h_shared && (I_s < 8 || (I_s & 7))) return CD_ERR_INVALID;
@@ -221,6 +282,8 @@ int cd_moe_down(const void* h_routed, int I_e, const void* wd_routed, const void
   epi.row_map = row_map;
   epi.residual = residual;
   epi.ldr = H;
+  epi.residual_lo = residual_lo;
+  epi.out_lo = out_lo;
   return launch_gemm(T, H, E, seg_offsets, op0, h_shared ? &op1 : nullptr, epi,
                      choose_store_block_n(T, H, E, current_sm_count()), as_stream(stream));
 }
@@ -236,6 +299,19 @@ int cd_push_rows(const void* x, const int32_t* src_rows, const int32_t* offsets,
                                    reinterpret_cast<const unsigned long long*>(peer_ptrs), T, H,
                                    as_stream(stream));
   return e == cudaSuccess ? CD_OK : cuda_fail(e, "push_rows launch");
+}
+
+int cd_peer_barrier(const uint64_t* peer_flags, int32_t* flags, int rank, int world, int limit_ms,
+                    void* stream) {
+  if (!peer_flags || !flags || world < 1 || world > 64 || rank < 0 || rank >= world ||
+      limit_ms < 1 || limit_ms > 60000)
+    return CD_ERR_INVALID;
+  int* status = device_status_word();
+  if (!status) return CD_ERR_CUDA;
+  cudaError_t e = launch_peer_barrier(reinterpret_cast<const unsigned long long*>(peer_flags), flags,
+                                      rank, world, static_cast<unsigned long long>(limit_ms) * 1000000ull,
+                                      status, as_stream(stream));
+  return e == cudaSuccess ? CD_OK : cuda_fail(e, "peer_barrier launch");
 }
 
 int cd_moe_down_push(const void* h_routed, int I_e, const void* wd_routed,
@@ -262,8 +338,8 @@ int cd_moe_down_push(const void* h_routed, int I_e, const void* wd_routed,
 }
 
 int cd_moe_combine(const void* h_shared, int I_s, const void* wd_shared, const void* routed_sorted,
-                   const int32_t* row_map, const void* residual, void* out, int T, int H,
-                   void* stream) {
+                   const int32_t* row_map, const void* residual, const void* residual_lo, void* out,
+                   void* out_lo, int T, int H, void* stream) {
   if (T < 0 || H < 8 || (H & 7) || I_s < 8 || (I_s & 7)) return CD_ERR_INVALID;
   if (!h_shared || !wd_shared) return CD_ERR_INVALID;
   GemmOperand op0{};
@@ -281,6 +357,8 @@ int cd_moe_combine(const void* h_shared, int I_s, const void* wd_shared, const v
   epi.row_map = row_map;
   epi.residual = residual;
   epi.ldr = H;
+  epi.residual_lo = residual_lo;
+  epi.out_lo = out_lo;
   epi.residual2 = routed_sorted;
   epi.ldr2 = H;
   return launch_gemm(T, H, 1, nullptr, op0, nullptr, epi,
@@ -391,8 +469,8 @@ int cd_mu_proj(const void* h, const void* w, const void* mu_param, float mu_min,
                      choose_store_block_n(T, H, 1, current_sm_count()), as_stream(stream));
 }
 
-int cd_linear(const void* x, const void* w, const void* residual, void* out, int T, int K, int N,
-              void* stream) {
+int cd_linear(const void* x, const void* w, const void* residual, const void* residual_lo,
+              void* out, void* out_lo, int T, int K, int N, void* stream) {
   if (T < 0 || K < 8 || (K & 7) || N < 8 || (N & 7)) return CD_ERR_INVALID;
   GemmOperand op0{};
   op0.a = x;
@@ -408,6 +486,8 @@ int cd_linear(const void* x, const void* w, const void* residual, void* out, int
   epi.out_cols = N;
   epi.residual = residual;
   epi.ldr = N;
+  epi.residual_lo = residual_lo;
+  epi.out_lo = out_lo;
   return launch_gemm(T, N, 1, nullptr, op0, nullptr, epi,
                      choose_store_block_n(T, N, 1, current_sm_count()), as_stream(stream));
 }

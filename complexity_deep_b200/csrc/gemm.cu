@@ -52,7 +52,7 @@ bool make_map(CUtensorMap* m, const void* base, long long rows, long long cols, 
 
 struct DeviceInfo {
   int sm_count = 0;
-  bool attr_set[4][3][2] = {};  // [BN 32/64/128/256][epilogue][CTA group 1/2]
+  bool attr_set[4][4][2] = {};  // [BN 32/64/128/256][epilogue][CTA group 1/2]
   int* status = nullptr;
 };
 constexpr int kMaxDevices = 64;
@@ -97,10 +97,19 @@ cudaError_t launch_any(int block_n, int kind, int grid, const CUtensorMap& a0,
                        const GemmParams& p, DeviceInfo& di, cudaStream_t stream) {
   if (block_n == 256) {
     if (kind == kEpiStoreRope) return launch_one<256, kEpiStoreRope, CG>(grid, a0, b0, a1, b1, p, di, stream);
+    if (kind == kEpiStoreSplit) return launch_one<256, kEpiStoreSplit, CG>(grid, a0, b0, a1, b1, p, di, stream);
     return kind == kEpiSwiGLU ? launch_one<256, kEpiSwiGLU, CG>(grid, a0, b0, a1, b1, p, di, stream)
                               : launch_one<256, kEpiStore, CG>(grid, a0, b0, a1, b1, p, di, stream);
   }
   if (kind == kEpiStoreRope) return cudaErrorInvalidValue;
+  if (kind == kEpiStoreSplit) {
+    if (block_n == 128) return launch_one<128, kEpiStoreSplit, CG>(grid, a0, b0, a1, b1, p, di, stream);
+    if constexpr (CG == 1) {
+      if (block_n == 64) return launch_one<64, kEpiStoreSplit, 1>(grid, a0, b0, a1, b1, p, di, stream);
+      if (block_n == 32) return launch_one<32, kEpiStoreSplit, 1>(grid, a0, b0, a1, b1, p, di, stream);
+    }
+    return cudaErrorInvalidValue;
+  }
   if (block_n == 128)
     return kind == kEpiSwiGLU ? launch_one<128, kEpiSwiGLU, CG>(grid, a0, b0, a1, b1, p, di, stream)
                               : launch_one<128, kEpiStore, CG>(grid, a0, b0, a1, b1, p, di, stream);
@@ -207,8 +216,13 @@ int* device_status_word() {
 
 int launch_gemm(int M, int N, int num_groups, const int* seg_offsets, const GemmOperand& op0,
                 const GemmOperand* op1, const GemmEpilogueArgs& epi, int block_n,
-                cudaStream_t stream) {
-  if (M < 0 || N <= 0 || num_groups < 1 || num_groups > kMaxGroups) return CD_ERR_INVALID;
+                cudaStream_t stream, const GemmSecond* second) {
+  if (M < 0 || N <= 0 || num_groups < 1) return CD_ERR_INVALID;
+  if (num_groups > kMaxGroups) {
+    snprintf(g_cuda_err, sizeof(g_cuda_err), "grouped GEMM: %d row groups, at most %d are supported",
+             num_groups, kMaxGroups);
+    return CD_ERR_UNSUPPORTED;
+  }
   if (block_n != 32 && block_n != 64 && block_n != 128 && block_n != 256) return CD_ERR_INVALID;
   if (num_groups > 1 && !seg_offsets) return CD_ERR_INVALID;
   if (op0.K <= 0 || (op0.K & 7) || (op0.lda & 7) || (op0.ldb & 7)) return CD_ERR_INVALID;
@@ -224,8 +238,17 @@ int launch_gemm(int M, int N, int num_groups, const int* seg_offsets, const Gemm
   if (op1 && (!op1->a || !op1->b || !aligned16(op1->a) || !aligned16(op1->b)))
     return CD_ERR_INVALID;
   if (epi.rope_cos && (block_n != 256 || epi.kind != kEpiStore || epi.residual || epi.bias ||
-                       epi.residual2 || epi.row_map))
+                       epi.residual2 || epi.row_map || epi.out_lo))
     return CD_ERR_UNSUPPORTED;
+  // split-bf16 output: plain store epilogue into `out`, no per-row addresses
+  if ((epi.out_lo || epi.residual_lo) &&
+      (epi.kind != kEpiStore || epi.out_row_ptrs || !epi.out || !aligned16(epi.out_lo) ||
+       !aligned16(epi.residual_lo) || (epi.residual_lo && !epi.residual)))
+    return CD_ERR_INVALID;
+  if (second && (epi.kind != kEpiSwiGLU || op1 || !second->b || !second->out || second->n_rows <= 0 ||
+                 (second->ldb & 7) || (second->ldo & 7) || (second->out_cols & 7) ||
+                 !aligned16(second->b) || !aligned16(second->out)))
+    return CD_ERR_INVALID;
   if (M == 0) return CD_OK;
 
   int st;
@@ -244,6 +267,12 @@ int launch_gemm(int M, int N, int num_groups, const int* seg_offsets, const Gemm
     if (!make_map(&a1, op1->a, M, op1->K, op1->lda, kBlockM) ||
         !make_map(&b1, op1->b, op1->b_rows, op1->K, op1->ldb, b_box)) {
       snprintf(g_cuda_err, sizeof(g_cuda_err), "cuTensorMapEncodeTiled failed (operand 1)");
+      return CD_ERR_CUDA;
+    }
+  } else if (second) {
+    a1 = a0;
+    if (!make_map(&b1, second->b, second->n_rows, op0.K, second->ldb, b_box)) {
+      snprintf(g_cuda_err, sizeof(g_cuda_err), "cuTensorMapEncodeTiled failed (second problem)");
       return CD_ERR_CUDA;
     }
   } else {
@@ -269,6 +298,14 @@ int launch_gemm(int M, int N, int num_groups, const int* seg_offsets, const Gemm
   p.out_row_ptrs = epi.out_row_ptrs;
   p.residual = static_cast<const __nv_bfloat16*>(epi.residual);
   p.ldr = epi.ldr;
+  p.residual_lo = static_cast<const __nv_bfloat16*>(epi.residual_lo);
+  p.out_lo = static_cast<__nv_bfloat16*>(epi.out_lo);
+  if (second) {
+    p.N2 = second->n_rows;
+    p.out2 = static_cast<__nv_bfloat16*>(second->out);
+    p.ldo2 = second->ldo;
+    p.out_cols2 = second->out_cols;
+  }
   p.residual2 = static_cast<const __nv_bfloat16*>(epi.residual2);
   p.ldr2 = epi.ldr2;
   p.bias = static_cast<const __nv_bfloat16*>(epi.bias);
@@ -296,13 +333,15 @@ int launch_gemm(int M, int N, int num_groups, const int* seg_offsets, const Gemm
   const long long n_tiles = (N + block_n - 1) / block_n;
   const long long m_tiles_max = (M + tile_m - 1) / tile_m + (num_groups > 1 ? num_groups : 0);
   long long units = m_tiles_max * n_tiles;           // CTAs (cg = 1) or CTA pairs (cg = 2)
+  if (second) units += ((M + tile_m - 1) / tile_m) * ((second->n_rows + block_n - 1) / block_n);
   if (units > di->sm_count / cg) units = di->sm_count / cg;
   if (units < 1) units = 1;
   const int grid = static_cast<int>(units) * cg;
 
   cudaError_t e;
   std::lock_guard<std::mutex> lk(g_mu);
-  const int kind = epi.rope_cos ? static_cast<int>(kEpiStoreRope) : epi.kind;
+  const int kind = epi.rope_cos ? static_cast<int>(kEpiStoreRope)
+                   : (epi.out_lo || epi.residual_lo) ? static_cast<int>(kEpiStoreSplit) : epi.kind;
   e = (cg == 2) ? launch_any<2>(block_n, kind, grid, a0, b0, a1, b1, p, *di, stream)
                 : launch_any<1>(block_n, kind, grid, a0, b0, a1, b1, p, *di, stream);
   if (e != cudaSuccess) return cuda_fail(e, "gemm launch");

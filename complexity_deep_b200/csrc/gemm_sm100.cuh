@@ -39,6 +39,8 @@ enum GemmEpilogue : int {
   kEpiStore = 0,      // out[row_map(r), n] = clamp(acc + bias[n] + residual[row_map(r), n])
   kEpiSwiGLU = 1,     // out[r, j] = silu(acc[r, gate(j)]) * acc[r, up(j)]
   kEpiStoreRope = 2,  // store with per-head RMSNorm + rotary embedding (256-wide tiles only)
+  kEpiStoreSplit = 3, // store of a split-bf16 value: out = bf16(v), out_lo = bf16(v - out); the
+                      // residual may be split the same way (residual + residual_lo)
 };
 
 // Warp roles: warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2 .. 2 + EW - 1
@@ -75,6 +77,16 @@ struct GemmParams {
                                   // row_map; rows may live in another GPU's peer-mapped memory)
   const __nv_bfloat16* residual;  // indexed like out (nullptr = none)
   int ldr;
+  // split-bf16 residual stream (kEpiStoreSplit): the value carried between kernels is
+  // hi + lo with hi = bf16(v), lo = bf16(v - hi) (16 significant bits instead of 8)
+  const __nv_bfloat16* residual_lo;  // low part of the residual, indexed like residual (nullptr = none)
+  __nv_bfloat16* out_lo;             // low part of the result, indexed like out (nullptr = not stored)
+  // optional second problem over the same A rows (SwiGLU epilogue, one K segment): a dense
+  // [M, N2] product against B1 whose tiles follow the grouped ones in the same launch
+  int N2;                  // accumulator columns of the second problem (0 = none)
+  __nv_bfloat16* out2;
+  int ldo2;
+  int out_cols2;
   const __nv_bfloat16* residual2;  // second addend, indexed by the tile row itself (nullptr = none)
   int ldr2;
   const __nv_bfloat16* bias;      // per output column, clamped to [bias_lo, bias_hi] (nullptr = none)
@@ -120,7 +132,7 @@ struct GemmSmem {
   static constexpr int kNumBars = 2 * kStages + 4;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
   static constexpr int kPrefixOff = kMiscOff + 16;
-  static constexpr int kSegOff = kPrefixOff + (kMaxGroups + 1) * 4;
+  static constexpr int kSegOff = kPrefixOff + (kMaxGroups + 2) * 4;
   static constexpr int kTotal = kSegOff + (kMaxGroups + 1) * 4;
   static constexpr int kDynamic = kTotal + 1024;  // slack for 1024-byte alignment
 };
@@ -134,15 +146,19 @@ struct TileCoord {
 
 // Maps a linear tile index to its coordinates.  Within a group, tiles are ordered in bands
 // of `band` m-tiles; inside a band the m index runs fastest, so the CTAs that run together
-// share a small set of B tiles while the A band stays in L2.
+// share a small set of B tiles while the A band stays in L2.  Group index `num_groups` is the
+// optional second problem: all M rows as one segment, `n_tiles2` tiles wide.
 __device__ __forceinline__ TileCoord decode_tile(int t, int& gcur, const int* prefix,
-                                                 const int* seg, int n_tiles, int band,
+                                                 const int* seg, int num_groups, int M,
+                                                 int n_tiles, int n_tiles2, int band,
                                                  int bn, int block_m) {
   while (t >= prefix[gcur + 1]) ++gcur;
+  const bool second = gcur >= num_groups;
   const int local = t - prefix[gcur];
-  const int lo = seg[gcur], hi = seg[gcur + 1];
+  const int lo = second ? 0 : seg[gcur], hi = second ? M : seg[gcur + 1];
+  const int nt = second ? n_tiles2 : n_tiles;
   const int m_tiles = (hi - lo + block_m - 1) / block_m;
-  const int per_band = band * n_tiles;
+  const int per_band = band * nt;
   const int b = local / per_band;
   const int within = local - b * per_band;
   const int m_first = b * band;
@@ -185,7 +201,8 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
                        const __grid_constant__ CUtensorMap tmB1, const GemmParams p) {
   constexpr int EW = gemm_epi_warps<BN, EPI>();
   constexpr int kEpiHalves = EW / 4;               // epilogue warps per TMEM lane quarter
-  constexpr bool kStore = (EPI == kEpiStore || EPI == kEpiStoreRope);
+  constexpr bool kStore = (EPI == kEpiStore || EPI == kEpiStoreRope || EPI == kEpiStoreSplit);
+  constexpr bool kSplit = (EPI == kEpiStoreSplit);
   using L = GemmSmem<BN, CG, EW>;
   constexpr int S = L::kStages;
   constexpr int kTileM = kBlockM * CG;             // rows per tile (per CTA pair when CG = 2)
@@ -218,6 +235,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int n_tiles = (p.N + BN - 1) / BN;
+  const int n_tiles2 = (p.N2 + BN - 1) / BN;   // 0 without a second problem
   const int kb0 = (p.K0 + kBlockK - 1) / kBlockK;
   const int kb1 = (p.K1 + kBlockK - 1) / kBlockK;
   const int kb_total = kb0 + kb1;
@@ -237,10 +255,8 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
     fence_barrier_init();
     tma_prefetch_desc(&tmA0);
     tma_prefetch_desc(&tmB0);
-    if (p.K1 > 0) {
-      tma_prefetch_desc(&tmA1);
-      tma_prefetch_desc(&tmB1);
-    }
+    if (p.K1 > 0) tma_prefetch_desc(&tmA1);
+    if (p.K1 > 0 || p.N2 > 0) tma_prefetch_desc(&tmB1);
   } else if (warp == 1) {
     if constexpr (CG == 2) {
       tmem_alloc_pair(tmem_base_slot, kTmemCols);
@@ -265,6 +281,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
       acc += ((hi - lo + kTileM - 1) / kTileM) * n_tiles;
       prefix[g + 1] = acc;
     }
+    if (p.N2 > 0) prefix[p.num_groups + 1] = acc + ((p.M + kTileM - 1) / kTileM) * n_tiles2;
   }
   tc_fence_before();
   __syncthreads();
@@ -272,7 +289,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
   tc_fence_after();
 
   const uint32_t tmem_base = *tmem_base_slot;
-  const int total_tiles = prefix[p.num_groups];
+  const int total_tiles = prefix[p.num_groups + (p.N2 > 0 ? 1 : 0)];
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -281,10 +298,13 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
       int gcur = 0;
       bool ok = true;
       for (int t = tile0; t < total_tiles && ok; t += tstride) {
-        const TileCoord c = decode_tile(t, gcur, prefix, seg, n_tiles, p.band, BN, kTileM);
+        const TileCoord c = decode_tile(t, gcur, prefix, seg, p.num_groups, p.M, n_tiles, n_tiles2,
+                                        p.band, BN, kTileM);
+        const bool second = c.group >= p.num_groups;   // dense problem against B1, K segment 0 only
         const int a_row = c.m0 + static_cast<int>(crank) * kBlockM;
         const int b0_row = c.group * p.b0_group_rows + c.n0 + static_cast<int>(crank) * (BN / CG);
-        const int b1_row = c.group * p.b1_group_rows + c.n0 + static_cast<int>(crank) * (BN / CG);
+        const int b1_row = (second ? 0 : c.group * p.b1_group_rows) + c.n0 +
+                           static_cast<int>(crank) * (BN / CG);
         for (int kb = 0; kb < kb_total; ++kb, ++it) {
           const uint32_t s = it % S;
           const uint32_t ph = (it / S) & 1u;
@@ -299,7 +319,10 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
             // the leader's barrier collects the bytes of both CTAs
             if (crank == 0) mbar_arrive_expect_tx(&full_bar[s], 2 * L::kStageBytes);
             const uint32_t bar = map_to_cta(smem_u32(&full_bar[s]), 0);
-            if (kb < kb0) {
+            if (second) {
+              tma_load_2d_pair(a_dst, &tmA0, bar, kb * kBlockK, a_row);
+              tma_load_2d_pair(b_dst, &tmB1, bar, kb * kBlockK, b1_row);
+            } else if (kb < kb0) {
               tma_load_2d_pair(a_dst, &tmA0, bar, kb * kBlockK, a_row);
               tma_load_2d_pair(b_dst, &tmB0, bar, kb * kBlockK, b0_row);
             } else {
@@ -308,7 +331,10 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
             }
           } else {
             mbar_arrive_expect_tx(&full_bar[s], L::kStageBytes);
-            if (kb < kb0) {
+            if (second) {
+              tma_load_2d(a_dst, &tmA0, &full_bar[s], kb * kBlockK, a_row);
+              tma_load_2d(b_dst, &tmB1, &full_bar[s], kb * kBlockK, b1_row);
+            } else if (kb < kb0) {
               tma_load_2d(a_dst, &tmA0, &full_bar[s], kb * kBlockK, a_row);
               tma_load_2d(b_dst, &tmB0, &full_bar[s], kb * kBlockK, b0_row);
             } else {
@@ -394,7 +420,12 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
     int gcur = 0;
     bool ok = true;
     for (int t = tile0; t < total_tiles && ok; t += tstride, ++tcount) {
-      const TileCoord c = decode_tile(t, gcur, prefix, seg, n_tiles, p.band, BN, kTileM);
+      const TileCoord c = decode_tile(t, gcur, prefix, seg, p.num_groups, p.M, n_tiles, n_tiles2,
+                                      p.band, BN, kTileM);
+      const bool second = c.group >= p.num_groups;
+      __nv_bfloat16* const out_base = second ? p.out2 : p.out;
+      const int out_ld = second ? p.ldo2 : p.ldo;
+      const int out_cols = second ? p.out_cols2 : p.out_cols;
       const uint32_t acc = tcount & 1u;
       const uint32_t acc_ph = (tcount >> 1) & 1u;
       const int r = c.m0 + static_cast<int>(crank) * kBlockM + quarter * 32 + lane;
@@ -425,25 +456,30 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
           cptr[it] = static_cast<long long>((static_cast<unsigned long long>(hi) << 32) | lo);
         }
       }
-      // output columns of this tile and the number of 64-column sub-tiles
+      // output columns of this tile and the number of sub-tiles (64 columns; 32 for the split
+      // store, whose staged rows hold 64 bytes of high parts followed by 64 bytes of low parts)
+      constexpr int kSubCols = kSplit ? 32 : kEpiCols;
       const int ocol_base = kStore ? c.n0 : c.n0 / 2;
       const int ocol_span = kStore ? BN : BN / 2;
-      const int ocols = min(ocol_span, p.out_cols - ocol_base);
-      const int nsub = (ocols + kEpiCols - 1) / kEpiCols;
+      const int ocols = min(ocol_span, out_cols - ocol_base);
+      const int nsub = (ocols + kSubCols - 1) / kSubCols;
       const int col_end = ocol_base + ocols;   // one past the last output column of this tile
       const bool has_res = kStore && p.residual != nullptr;
 
       // i-th sub-tile of THIS warp (sub-tile index ehalf + i * kEpiHalves of the tile)
       auto fetch_residual = [&](int i) {
         uint8_t* buf = stage0 + (i & 1) * kEpiStageBytes;
-        const int col = ocol_base + (ehalf + i * kEpiHalves) * kEpiCols + cchunk * 8;
-        if (col < col_end) {
+        // split store: chunks 0-3 of a staged row come from the high part, 4-7 from the low part
+        const __nv_bfloat16* src = (kSplit && cchunk >= 4) ? p.residual_lo : p.residual;
+        const int col = ocol_base + (ehalf + i * kEpiHalves) * kSubCols +
+                        (kSplit ? (cchunk & 3) : cchunk) * 8;
+        if (col < col_end && src != nullptr) {
 #pragma unroll
           for (int it = 0; it < 8; ++it) {
             if ((cvalid >> it) & 1u) {
               const int rr = it * 4 + crow_l;
               cp_async_16(buf + rr * 128 + ((cchunk ^ (rr & 7)) << 4),
-                          p.residual + static_cast<long long>(crow[it]) * p.ldr + col);
+                          src + static_cast<long long>(crow[it]) * p.ldr + col);
             }
           }
         }
@@ -471,15 +507,18 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
 
       // coalesced copy-out of one staged 32 x 64 sub-tile: 4 rows x 128 bytes per warp instruction
       auto copy_out = [&](const uint8_t* buf, int col0) {
-        const int col = col0 + cchunk * 8;
-        if (col < col_end) {
+        // split store: lanes with chunks 0-3 write the high parts to `out`, 4-7 the low parts to
+        // `out_lo` (64 bytes per row and destination)
+        __nv_bfloat16* base = (kSplit && cchunk >= 4) ? p.out_lo : out_base;
+        const int col = col0 + (kSplit ? (cchunk & 3) : cchunk) * 8;
+        if (col < col_end && base != nullptr) {
 #pragma unroll
           for (int it = 0; it < 8; ++it) {
             if ((cvalid >> it) & 1u) {
               const int rr = it * 4 + crow_l;
               const uint4 o = *reinterpret_cast<const uint4*>(buf + rr * 128 + ((cchunk ^ (rr & 7)) << 4));
               __nv_bfloat16* drow = use_ptrs ? reinterpret_cast<__nv_bfloat16*>(cptr[it])
-                                             : p.out + static_cast<long long>(crow[it]) * p.ldo;
+                                             : base + static_cast<long long>(crow[it]) * out_ld;
               *reinterpret_cast<uint4*>(drow + col) = o;
             }
           }
@@ -578,8 +617,99 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
 #pragma unroll 1
       for (int i = 0, sub = ehalf; sub < nsub; ++i, sub += kEpiHalves) {
         uint8_t* buf = stage0 + (i & 1) * kEpiStageBytes;
-        const int col0 = ocol_base + sub * kEpiCols;
-        if constexpr (kStore) {
+        const int col0 = ocol_base + sub * kSubCols;
+        if constexpr (kSplit) {
+          // one round of 32 accumulator columns: v = acc + bias + residual (high + low) + residual2,
+          // stored as hi = bf16(v) and lo = bf16(v - hi)
+          uint4 r2[4];
+          if (res2_row) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              if (col0 + q * 8 < col_end) r2[q] = ld_nc_v4(res2_row + col0 + q * 8);
+          }
+          uint4 bb[4];
+          if (p.bias) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              if (col0 + q * 8 < col_end) bb[q] = *reinterpret_cast<const uint4*>(p.bias + col0 + q * 8);
+          }
+          uint32_t v[32];
+          tmem_ld32(t_row + sub * 32, v);
+          if constexpr (kChains == 2) {
+            uint32_t v2[32];
+            tmem_ld32(t_row + BN + sub * 32, v2);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(v2[j]));
+          }
+          if (has_res) {
+            if (sub + kEpiHalves < nsub) cp_async_wait<1>(); else cp_async_wait<0>();
+            __syncwarp();
+          }
+          tmem_ld_wait();
+          const bool has_lo = p.residual_lo != nullptr;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int col = col0 + q * 8;
+            float f[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[q * 8 + j]);
+            uint8_t* slot_hi = buf + own_off + ((q ^ (lane & 7)) << 4);
+            uint8_t* slot_lo = buf + own_off + (((4 + q) ^ (lane & 7)) << 4);
+            if (col < col_end) {
+              if (p.bias) {
+                const uint32_t bw[4] = {bb[q].x, bb[q].y, bb[q].z, bb[q].w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  f[2 * j] += fminf(fmaxf(bf16_lo(bw[j]), p.bias_lo), p.bias_hi);
+                  f[2 * j + 1] += fminf(fmaxf(bf16_hi(bw[j]), p.bias_lo), p.bias_hi);
+                }
+              }
+              if (has_res && row_ok) {
+                const uint4 rr = *reinterpret_cast<const uint4*>(slot_hi);
+                const uint32_t rw[4] = {rr.x, rr.y, rr.z, rr.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  f[2 * j] += bf16_lo(rw[j]);
+                  f[2 * j + 1] += bf16_hi(rw[j]);
+                }
+                if (has_lo) {
+                  const uint4 rl = *reinterpret_cast<const uint4*>(slot_lo);
+                  const uint32_t lw[4] = {rl.x, rl.y, rl.z, rl.w};
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    f[2 * j] += bf16_lo(lw[j]);
+                    f[2 * j + 1] += bf16_hi(lw[j]);
+                  }
+                }
+              }
+              if (res2_row) {
+                const uint32_t rw[4] = {r2[q].x, r2[q].y, r2[q].z, r2[q].w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  f[2 * j] += bf16_lo(rw[j]);
+                  f[2 * j + 1] += bf16_hi(rw[j]);
+                }
+              }
+              if (p.do_clamp) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] = fminf(fmaxf(f[j], p.clamp_lo), p.clamp_hi);
+              }
+            }
+            uint4 o, l;
+            o.x = pack_bf16x2(f[0], f[1]);
+            o.y = pack_bf16x2(f[2], f[3]);
+            o.z = pack_bf16x2(f[4], f[5]);
+            o.w = pack_bf16x2(f[6], f[7]);
+            l.x = pack_bf16x2(f[0] - bf16_lo(o.x), f[1] - bf16_hi(o.x));
+            l.y = pack_bf16x2(f[2] - bf16_lo(o.y), f[3] - bf16_hi(o.y));
+            l.z = pack_bf16x2(f[4] - bf16_lo(o.z), f[5] - bf16_hi(o.z));
+            l.w = pack_bf16x2(f[6] - bf16_lo(o.w), f[7] - bf16_hi(o.w));
+            *reinterpret_cast<uint4*>(slot_hi) = o;
+            *reinterpret_cast<uint4*>(slot_lo) = l;
+          }
+        } else if constexpr (kStore) {
           // two rounds of 32 accumulator columns (keeps the register count of the
           // eight-warp variants inside their budget)
 #pragma unroll 1

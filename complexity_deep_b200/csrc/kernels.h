@@ -38,15 +38,19 @@ cudaError_t launch_route(const long long* ids, const long long* table, int V, in
                          int* expert_ids, int* counts, int* offsets, int* perm, int* inv_perm,
                          int* block_hist, cudaStream_t stream);
 
+// split = false: h = bf16(x + residual) as the reference's bf16 residual add; split = true:
+// `residual` is the low part of a split-bf16 value and h = x + residual is kept in fp32.
 cudaError_t launch_rmsnorm(const void* x, const void* residual, const void* weight, float eps,
                            void* sum_out, void* out, const int* dst_rows, int T, int H,
-                           cudaStream_t stream);
+                           cudaStream_t stream, bool split);
 cudaError_t launch_gather_rows(const void* x, const int* src_rows, void* out, int T, int H,
                                cudaStream_t stream);
 cudaError_t launch_push_rows(const void* x, const int* src_rows, const int* offsets,
                              const int* push_base, int E, int experts_per_rank,
                              const unsigned long long* peer_ptrs, int T, int H,
                              cudaStream_t stream);
+cudaError_t launch_peer_barrier(const unsigned long long* peer_flags, int* flags, int rank, int world,
+                                unsigned long long limit_ns, int* status, cudaStream_t stream);
 // pos_dev / k_cache / v_cache: decode-step form (position from device memory, rotated k and v
 // also written to the cache at that position); all null for the plain in-place form.
 cudaError_t launch_qk_norm_rope(void* qkv, const void* q_w, const void* k_w, const float* cos_t,
@@ -55,6 +59,11 @@ cudaError_t launch_qk_norm_rope(void* qkv, const void* q_w, const void* k_w, con
                                 void* k_cache = nullptr, void* v_cache = nullptr,
                                 long long kv_stride_b = 0, long long kv_stride_h = 0,
                                 long long kv_stride_t = 0, int capacity = 0);
+
+// weight layout transforms (pack.cu)
+cudaError_t launch_pack_gate_up(const void* gate, const void* up, void* packed, int G, int I, int H,
+                                int block_n, int feature_major, cudaStream_t stream);
+cudaError_t launch_transpose(const void* in, void* out, int G, int R, int C, cudaStream_t stream);
 
 size_t decode_attention_workspace_bytes(int B, int hq, int hkv, int L, int D);
 cudaError_t launch_decode_attention(const void* q, long long q_stride_b, const void* k,
@@ -84,6 +93,8 @@ struct GemmEpilogueArgs {
   const long long* out_row_ptrs;  // per sorted row: address of its destination row (may be peer memory)
   const void* residual;
   int ldr;
+  const void* residual_lo;  // low part of a split-bf16 residual (same indexing as residual)
+  void* out_lo;             // low part of the result (same indexing as out); selects the split epilogue
   const void* residual2;   // indexed by the un-mapped row
   int ldr2;
   const void* bias;
@@ -102,10 +113,21 @@ struct GemmEpilogueArgs {
   int rope_S, rope_pos0, rope_q_cols, rope_cols;
 };
 
+// Optional second, dense problem of a SwiGLU launch: h2[M, :cols] from the same A rows against
+// its own packed gate/up weights; its tiles run in the same launch after the grouped ones.
+struct GemmSecond {
+  const void* b;      // [n_rows, K] packed gate/up rows (K = the first operand's K, leading dimension ldb)
+  long long ldb;
+  int n_rows;         // accumulator columns
+  void* out;
+  int ldo;
+  int out_cols;
+};
+
 // Returns a CD_* status code.
 int launch_gemm(int M, int N, int num_groups, const int* seg_offsets, const GemmOperand& op0,
                 const GemmOperand* op1, const GemmEpilogueArgs& epi, int block_n,
-                cudaStream_t stream);
+                cudaStream_t stream, const GemmSecond* second = nullptr);
 
 int choose_store_block_n(int M, int N, int num_groups, int sm_count);  // SM count of the current device
 int current_sm_count();

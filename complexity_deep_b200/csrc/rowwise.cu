@@ -41,7 +41,9 @@ constexpr int kNormWarps = 4;
 constexpr int kMaxVec = 16;  // register path: H <= 16 * 256 = 4096, H % 256 == 0
 
 // One warp per row; the row lives in registers between the reduction and the scaling, so
-// x is read from HBM exactly once.
+// x is read from HBM exactly once.  kSplit: `res` is the low part of a split-bf16 value
+// (x + res carries 16 significant bits); the sum then stays in fp32 and nothing is written back.
+template <bool kSplit>
 __global__ void __launch_bounds__(kNormWarps * 32)
 rmsnorm_rows_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
                     const __nv_bfloat16* __restrict__ w, float eps,
@@ -57,10 +59,15 @@ rmsnorm_rows_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
   const uint4* rr = res ? reinterpret_cast<const uint4*>(res + static_cast<size_t>(row) * H)
                         : nullptr;
   uint4 buf[kMaxVec];
+  uint4 low[kSplit ? kMaxVec : 1];
 #pragma unroll
   for (int v = 0; v < kMaxVec; ++v)
     if (v < nv) buf[v] = xr[v * 32 + lane];
-  if (rr) {
+  if constexpr (kSplit) {
+#pragma unroll
+    for (int v = 0; v < kMaxVec; ++v)
+      if (v < nv) low[v] = rr ? rr[v * 32 + lane] : make_uint4(0, 0, 0, 0);
+  } else if (rr) {
 #pragma unroll
     for (int v = 0; v < kMaxVec; ++v)
       if (v < nv) {
@@ -82,9 +89,14 @@ rmsnorm_rows_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
   for (int v = 0; v < kMaxVec; ++v)
     if (v < nv) {
       const uint32_t* a = reinterpret_cast<const uint32_t*>(&buf[v]);
+      const uint32_t* b = reinterpret_cast<const uint32_t*>(&low[kSplit ? v : 0]);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const float l = lo_f(a[j]), h = hi_f(a[j]);
+        float l = lo_f(a[j]), h = hi_f(a[j]);
+        if constexpr (kSplit) {
+          l += lo_f(b[j]);
+          h += hi_f(b[j]);
+        }
         ss += l * l + h * h;
       }
     }
@@ -99,11 +111,18 @@ rmsnorm_rows_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
       const uint4 wv = wr[v * 32 + lane];
       const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
       const uint32_t* a = reinterpret_cast<const uint32_t*>(&buf[v]);
+      const uint32_t* b = reinterpret_cast<const uint32_t*>(&low[kSplit ? v : 0]);
       uint4 o;
       uint32_t* oo = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
-        oo[j] = pack2(lo_f(ww[j]) * (lo_f(a[j]) * rstd), hi_f(ww[j]) * (hi_f(a[j]) * rstd));
+      for (int j = 0; j < 4; ++j) {
+        float l = lo_f(a[j]), h = hi_f(a[j]);
+        if constexpr (kSplit) {
+          l += lo_f(b[j]);
+          h += hi_f(b[j]);
+        }
+        oo[j] = pack2(lo_f(ww[j]) * (l * rstd), hi_f(ww[j]) * (h * rstd));
+      }
       orw[v * 32 + lane] = o;
     }
 }
@@ -113,7 +132,7 @@ __global__ void __launch_bounds__(128)
 rmsnorm_generic_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
                        const __nv_bfloat16* __restrict__ w, float eps,
                        __nv_bfloat16* __restrict__ sum_out, __nv_bfloat16* __restrict__ out,
-                       const int* __restrict__ dst_rows, int T, int H) {
+                       const int* __restrict__ dst_rows, int T, int H, int split) {
   griddep_wait();               // the previous kernel's writes are visible from here
   griddep_launch_dependents();  // the next kernel may be scheduled
   __shared__ float s_part[4];
@@ -123,7 +142,9 @@ rmsnorm_generic_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
   float ss = 0.f;
   for (int c = threadIdx.x; c < H; c += blockDim.x) {
     float v = __bfloat162float(xr[c]);
-    if (rr) {
+    if (rr && split) {
+      v += __bfloat162float(rr[c]);
+    } else if (rr) {
       const __nv_bfloat16 s = __float2bfloat16_rn(v + __bfloat162float(rr[c]));
       if (sum_out) sum_out[static_cast<size_t>(row) * H + c] = s;
       v = __bfloat162float(s);
@@ -138,7 +159,8 @@ rmsnorm_generic_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
   const int orow = dst_rows ? dst_rows[row] : row;
   for (int c = threadIdx.x; c < H; c += blockDim.x) {
     float v = __bfloat162float(xr[c]);
-    if (rr) v = __bfloat162float(__float2bfloat16_rn(v + __bfloat162float(rr[c])));
+    if (rr && split) v += __bfloat162float(rr[c]);
+    else if (rr) v = __bfloat162float(__float2bfloat16_rn(v + __bfloat162float(rr[c])));
     out[static_cast<size_t>(orow) * H + c] = __float2bfloat16_rn(__bfloat162float(w[c]) * (v * rstd));
   }
 }
@@ -193,6 +215,49 @@ push_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ sr
   const uint4* s4 = reinterpret_cast<const uint4*>(src);
   uint4* d4 = reinterpret_cast<uint4*>(dst);
   for (int c = lane; c < (H >> 3); c += 32) d4[c] = s4[c];
+}
+
+// Barrier across the GPUs of an expert-parallel group, between two phases of the exchange by
+// peer stores.  flags: this GPU's signal pad, int32 [1 + world]: flags[0] is this GPU's own
+// barrier count (advanced here, so the launch arguments never change and the launch can sit
+// in a CUDA graph), flags[1 + r] the last count GPU r announced.  Thread r announces this
+// GPU's new count in GPU r's pad (a release store at system scope: every store this GPU issued
+// before the barrier kernel, peer stores included, is visible to whoever acquires the flag) and
+// then waits for GPU r's announcement of the same count.  The wait is bounded: after limit_ns
+// the kernel raises the status word and returns, it never spins forever on a GPU that left.
+__global__ void __launch_bounds__(64)
+peer_barrier_kernel(const unsigned long long* __restrict__ peer_flags, int* flags, int rank,
+                    int world, unsigned long long limit_ns, int* status) {
+  __shared__ int s_epoch;
+  if (threadIdx.x == 0) {
+    s_epoch = flags[0] + 1;
+    flags[0] = s_epoch;
+  }
+  __syncthreads();
+  const int epoch = s_epoch;
+  const int r = threadIdx.x;
+  if (r >= world) return;
+  __threadfence_system();
+  int* remote = reinterpret_cast<int*>(peer_flags[r]) + 1 + rank;
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+  const int* mine = flags + 1 + r;
+  unsigned long long t0 = 0;
+  unsigned spins = 0;
+  while (true) {
+    int seen;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+    if (seen - epoch >= 0) break;
+    if ((++spins & 0xffu) == 0) {
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > limit_ns) {
+        if (status) atomicExch(status, 2);
+        break;
+      }
+    }
+  }
 }
 
 // One warp per (token, head) over the q and k heads of the fused [T, (hq + 2 hkv) * D]
@@ -404,7 +469,7 @@ qk_norm_rope_vec_kernel(__nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __
 
 cudaError_t launch_rmsnorm(const void* x, const void* residual, const void* weight, float eps,
                            void* sum_out, void* out, const int* dst_rows, int T, int H,
-                           cudaStream_t stream) {
+                           cudaStream_t stream, bool split) {
   if (T == 0) return cudaSuccess;
   auto xb = static_cast<const __nv_bfloat16*>(x);
   auto rb = static_cast<const __nv_bfloat16*>(residual);
@@ -413,11 +478,13 @@ cudaError_t launch_rmsnorm(const void* x, const void* residual, const void* weig
   auto ob = static_cast<__nv_bfloat16*>(out);
   if ((H & 255) == 0 && H <= kMaxVec * 256) {
     const int blocks = (T + kNormWarps - 1) / kNormWarps;
-    return launch_kernel(rmsnorm_rows_kernel, dim3(blocks), dim3(kNormWarps * 32), 0, stream, xb, rb,
-                         wb, eps, sb, ob, dst_rows, T, H);
+    return split ? launch_kernel(rmsnorm_rows_kernel<true>, dim3(blocks), dim3(kNormWarps * 32), 0,
+                                 stream, xb, rb, wb, eps, sb, ob, dst_rows, T, H)
+                 : launch_kernel(rmsnorm_rows_kernel<false>, dim3(blocks), dim3(kNormWarps * 32), 0,
+                                 stream, xb, rb, wb, eps, sb, ob, dst_rows, T, H);
   } else {
     return launch_kernel(rmsnorm_generic_kernel, dim3(T), dim3(128), 0, stream, xb, rb, wb, eps, sb,
-                         ob, dst_rows, T, H);
+                         ob, dst_rows, T, H, split ? 1 : 0);
   }
   return cudaGetLastError();
 }
@@ -440,6 +507,12 @@ cudaError_t launch_push_rows(const void* x, const int* src_rows, const int* offs
   push_rows_kernel<<<(T + wpb - 1) / wpb, wpb * 32, (2 * E + 1) * sizeof(int), stream>>>(
       static_cast<const __nv_bfloat16*>(x), src_rows, offsets, push_base, E, experts_per_rank,
       peer_ptrs, T, H);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_peer_barrier(const unsigned long long* peer_flags, int* flags, int rank, int world,
+                                unsigned long long limit_ns, int* status, cudaStream_t stream) {
+  peer_barrier_kernel<<<1, 64, 0, stream>>>(peer_flags, flags, rank, world, limit_ns, status);
   return cudaGetLastError();
 }
 

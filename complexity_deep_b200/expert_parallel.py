@@ -170,6 +170,8 @@ class _PeerContext:
     def __init__(self):
         self.buffers = None      # (recv, ret, recv_handle, ret_handle)
         self.ret_ptrs = None
+        self.flags = None        # this rank's barrier signal pad, int32 [1 + world] (symmetric)
+        self.flag_ptrs = None    # int64 [world]: every rank's pad as seen from this GPU
         self.plans = {}
 
     @classmethod
@@ -197,13 +199,14 @@ class ExpertParallelMoE:
         `exchange`: "nccl" — two all_to_all_single per call; "peer" — the rows are stored
         straight into the other GPUs' buffers (symmetric memory over NVLink) by the kernels
         that produce them: a push kernel for the dispatch, the down-projection's epilogue for
-        the way back, with a cross-GPU barrier between the phases and no NCCL call on the
-        data path.  "peer" needs `max_tokens_per_rank` (same on every rank) to size the
+        the way back, with a cross-GPU barrier kernel of this library (bounded wait)
+        between the phases and no NCCL call on the data path.  "peer" needs `max_tokens_per_rank` (same on every rank) to size the
         buffers once."""
         if exchange not in ("nccl", "peer"):
             raise ValueError("exchange must be 'nccl' or 'peer'")
         self.exchange = exchange
         self.max_tokens = int(max_tokens_per_rank)
+        self.barrier_limit_ms = 2000
         self._peer = None
         self.group = group
         self.rank = dist.get_rank(group)
@@ -222,9 +225,9 @@ class ExpertParallelMoE:
         self.block_n = ops.choose_block_n(I_e)
         with torch.no_grad():
             self.packed_local = ops.pack_gate_up(
-                mlp.gate_proj_w.detach().index_select(0, mine).transpose(1, 2),
-                mlp.up_proj_w.detach().index_select(0, mine).transpose(1, 2), self.block_n)
-            self.down_local = mlp.down_proj_w.detach().index_select(0, mine).transpose(1, 2).contiguous()
+                mlp.gate_proj_w.detach().index_select(0, mine),
+                mlp.up_proj_w.detach().index_select(0, mine), self.block_n, feature_major=False)
+            self.down_local = ops.pack_down(mlp.down_proj_w.detach().index_select(0, mine))
         self._relabel = None
         if expert_load is not None:
             new_of_old = [0] * E
@@ -294,10 +297,26 @@ class ExpertParallelMoE:
             ret = symm_mem.empty(self.max_tokens, H, dtype=torch.bfloat16, device=device)
             recv_h = symm_mem.rendezvous(recv, group=group)
             ret_h = symm_mem.rendezvous(ret, group=group)
+            flags = symm_mem.empty(64, dtype=torch.int32, device=device)
+            flags.zero_()
+            flags_h = symm_mem.rendezvous(flags, group=group)
             ctx.buffers = (recv, ret, recv_h, ret_h)
             ctx.ret_ptrs = torch.tensor([int(p) for p in ret_h.buffer_ptrs], dtype=torch.int64,
                                         device=device)
+            ctx.flags, ctx.flags_handle = flags, flags_h
+            ctx.flag_ptrs = torch.tensor([int(p) for p in flags_h.buffer_ptrs], dtype=torch.int64,
+                                         device=device)
+            # every pad is zeroed before any rank's first barrier kernel can write into it
+            torch.cuda.synchronize(device)
+            dist.barrier(group=group)
         return ctx.buffers
+
+    def _barrier(self, H: int) -> None:
+        """Cross-GPU barrier between two phases of the peer exchange (cd_peer_barrier): a
+        bounded device-side wait that raises the library's status word instead of spinning
+        forever when a rank never arrives."""
+        ctx = self._peer_context(H)
+        ops.peer_barrier(ctx.flag_ptrs, ctx.flags, self.rank, self.world, self.barrier_limit_ms)
 
     def peer_plan_for(self, routing: ops.Routing, H: int):
         """Exchange plan of a routed batch for the peer-store exchange, computed on the device
@@ -320,13 +339,27 @@ class ExpertParallelMoE:
         ctx.plans[key] = (routing,) + out
         return out
 
-    def _forward_sorted_peer(self, x_sorted, routing, residual):
+    def _check_batch(self, x_sorted: torch.Tensor, routing: ops.Routing) -> None:
+        """Host-side checks of one call, made BEFORE any collective or launch of that call, so a
+        rank that raises has nothing in flight and no peer buffer can be overrun (a rank never
+        sends more than max_tokens rows, so no rank receives more than its buffer holds)."""
+        T = x_sorted.shape[0]
+        if routing.perm.numel() != T:
+            raise ValueError(f"token_ids has {routing.perm.numel()} entries for {T} tokens")
+        if routing.num_experts != self.mlp.num_experts:
+            raise ValueError("routing was computed for another expert count")
+        if self.exchange == "peer":
+            if self.max_tokens <= 0:
+                raise ValueError("exchange='peer' needs max_tokens_per_rank")
+            if T > self.max_tokens:
+                raise ValueError(f"{T} tokens on this rank, but the exchange buffers were sized "
+                                 f"for max_tokens_per_rank={self.max_tokens}")
+
+    def _forward_sorted_peer(self, x_sorted, routing, residual, residual_lo, want_lo):
         mlp = self.mlp
         T, H = x_sorted.shape
         recv, ret, recv_h, ret_h = self._peer_buffers(H, x_sorted.device)
         push_base, seg, row_ptrs = self.peer_plan_for(routing, H)
-        if T > self.max_tokens:
-            raise ValueError("more tokens than max_tokens_per_rank")
         # dispatch: every row goes straight into its expert's GPU
         ops.push_rows(x_sorted, routing.offsets, push_base, mlp.num_experts,
                       self.experts_per_rank, recv_h.buffer_ptrs_dev)
@@ -335,7 +368,7 @@ class ExpertParallelMoE:
             packed_s, bn_s = mlp._packed_shared(T)
             h_s = ops.moe_up(x_sorted, None, 1, packed_s, mlp.shared_gate.weight.shape[0], bn_s)
             wd_s = mlp.shared_down.weight.detach()
-        recv_h.barrier(channel=0)          # all pushes visible; also: peers are done reading `ret`
+        self._barrier(H)                   # all pushes visible; also: peers are done reading `ret`
         # The number of received rows is only known on the device: the GEMMs are launched over
         # the whole buffer and schedule tiles from `seg` (device), so rows past the last segment
         # are never touched.
@@ -343,20 +376,34 @@ class ExpertParallelMoE:
                          mlp.expert_intermediate_size, self.block_n)
         # the epilogue stores every finished row in its home GPU's return buffer
         ops.moe_down_push(h_r, self.down_local, seg, self.experts_per_rank, row_ptrs)
-        ret_h.barrier(channel=0)           # all routed rows are home; peers are done reading `recv`
+        self._barrier(H)                   # all routed rows are home; peers are done reading `recv`
         y_sorted = ret[:T]
         if h_s is not None:
-            return ops.moe_combine(h_s, wd_s, y_sorted, routing.perm, residual)
+            return ops.moe_combine(h_s, wd_s, y_sorted, routing.perm, residual, residual_lo, want_lo)
+        return self._unpermute_only(y_sorted, routing, residual, residual_lo, want_lo)
+
+    @staticmethod
+    def _unpermute_only(y_sorted, routing, residual, residual_lo, want_lo):
+        """No shared expert: un-permute the routed rows (+ residual) with PyTorch operators."""
         out = ops.gather_rows(y_sorted, routing.inv_perm)
-        return out if residual is None else out + residual.reshape(out.shape)
+        if residual is None:
+            return (out, None) if want_lo else out
+        total = out.float() + residual.reshape(out.shape).float()
+        if residual_lo is not None:
+            total = total + residual_lo.reshape(out.shape).float()
+        hi = total.to(out.dtype)
+        return (hi, (total - hi.float()).to(out.dtype)) if want_lo else hi
 
     # ------------------------------------------------------------------ forward
     def forward_sorted(self, x_sorted: torch.Tensor, routing: ops.Routing,
-                       residual: Optional[torch.Tensor]) -> torch.Tensor:
+                       residual: Optional[torch.Tensor],
+                       residual_lo: Optional[torch.Tensor] = None, want_lo: bool = False):
         """x_sorted: this rank's rows in expert-sorted order [T_local, H]; returns rows in
-        ORIGINAL order with shared + routed (+ residual) combined in fp32."""
+        ORIGINAL order with shared + routed (+ residual) combined in fp32.  `residual_lo` /
+        `want_lo`: split-bf16 residual stream as in TokenRoutedMLP.forward_sorted."""
+        self._check_batch(x_sorted, routing)
         if self.exchange == "peer":
-            return self._forward_sorted_peer(x_sorted, routing, residual)
+            return self._forward_sorted_peer(x_sorted, routing, residual, residual_lo, want_lo)
         mlp = self.mlp
         H = x_sorted.shape[1]
         plan, seg, gidx = self.plan_for(routing)
@@ -383,15 +430,16 @@ class ExpertParallelMoE:
         dist.all_to_all_single(y_sorted, y_recv, plan.in_splits, plan.out_splits,
                                group=self.group)
         if h_s is not None:
-            return ops.moe_combine(h_s, wd_s, y_sorted, routing.perm, residual)
-        # no shared expert: un-permute (+ residual) only
-        out = ops.gather_rows(y_sorted, routing.inv_perm)
-        return out if residual is None else out + residual.reshape(out.shape)
+            return ops.moe_combine(h_s, wd_s, y_sorted, routing.perm, residual, residual_lo, want_lo)
+        return self._unpermute_only(y_sorted, routing, residual, residual_lo, want_lo)
 
     def forward(self, hidden_states: torch.Tensor, token_ids: torch.Tensor) -> torch.Tensor:
         """Drop-in for ``TokenRoutedMLP.forward`` on this rank's tokens."""
         shape = hidden_states.shape
         H = shape[-1]
+        if token_ids.numel() != hidden_states.numel() // H:
+            raise ValueError(f"token_ids has {token_ids.numel()} entries for "
+                             f"{hidden_states.numel() // H} tokens")
         routing = self.routing(token_ids)
         x_sorted = ops.gather_rows(hidden_states.reshape(-1, H).contiguous(), routing.perm)
         return self.forward_sorted(x_sorted, routing, None).view(shape)

@@ -142,10 +142,11 @@ def route(token_ids: torch.Tensor, table: torch.Tensor, num_experts: int) -> Rou
 # --------------------------------------------------------------------------- row-wise
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float,
             residual: Optional[torch.Tensor] = None, dst_rows: Optional[torch.Tensor] = None,
-            want_sum: bool = False):
+            want_sum: bool = False, x_lo: Optional[torch.Tensor] = None):
     """``norm(x (+ residual)) * weight``; returns ``out`` or ``(sum, out)`` when want_sum.
 
-    With ``dst_rows`` row i of the result is written to row ``dst_rows[i]``.
+    With ``dst_rows`` row i of the result is written to row ``dst_rows[i]``.  With ``x_lo``
+    (the low part of a split-bf16 value, see ``SplitStream``) the input is ``x + x_lo`` in fp32.
     """
     lib = _lib.load()
     H = x.shape[-1]
@@ -153,12 +154,31 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float,
     _need(x2, "x")
     _need(weight, "weight")
     T = x2.shape[0]
+    if x_lo is not None:
+        if residual is not None or want_sum:
+            raise RuntimeError("x_lo cannot be combined with residual / want_sum")
+        lo2 = x_lo.reshape(-1, H)
+        _need(lo2, "x_lo")
+        if lo2.shape[0] != T:
+            raise RuntimeError("x_lo does not match x")
+        if dst_rows is not None:
+            _need(dst_rows, "dst_rows", torch.int32)
+            if dst_rows.numel() != T:
+                raise RuntimeError("dst_rows must have one entry per row")
+        out = torch.empty_like(x2)
+        with _Span("rmsnorm"):
+            _lib.check(lib.cd_rmsnorm_split(x2.data_ptr(), lo2.data_ptr(), weight.data_ptr(),
+                                            float(eps), out.data_ptr(), _ptr(dst_rows), T, H,
+                                            _stream()), "cd_rmsnorm_split")
+        return out.view(x.shape)
     res2 = None
     if residual is not None:
         res2 = residual.reshape(-1, H)
         _need(res2, "residual")
     if dst_rows is not None:
         _need(dst_rows, "dst_rows", torch.int32)
+        if dst_rows.numel() != T:
+            raise RuntimeError("dst_rows must have one entry per row")
     out = torch.empty_like(x2)
     s = torch.empty_like(x2) if (want_sum and res2 is not None) else None
     with _Span("rmsnorm"):
@@ -307,24 +327,39 @@ def choose_block_n(width: int, rows: Optional[int] = None, groups: int = 1,
     return 256 if (padded - width) / width <= 0.25 else 128
 
 
-def pack_gate_up(gate: torch.Tensor, up: torch.Tensor, block_n: int) -> torch.Tensor:
-    """Interleaves gate and up rows per accumulator tile.
+def pack_gate_up(gate: torch.Tensor, up: torch.Tensor, block_n: int,
+                 feature_major: bool = True) -> torch.Tensor:
+    """Interleaves gate and up rows per accumulator tile (cd_pack_gate_up).
 
-    gate, up: [G, I, H] (one output feature per row, H contiguous).  Result
+    feature_major: gate, up are [G, I, H] (one output feature per row, nn.Linear layout);
+    otherwise [G, H, I] (the reference's routed-expert layout ``x @ W[e]``).  Result
     [G, ceil(I / half) * block_n, H] with, for each tile, `half` gate rows then `half` up rows
     (half = block_n / 2); rows past I are zero.
     """
-    G, I, H = gate.shape
-    half = block_n // 2
-    chunks = -(-I // half)
-    pad = chunks * half - I
-    if pad:
-        z = gate.new_zeros(G, pad, H)
-        gate = torch.cat([gate, z], dim=1)
-        up = torch.cat([up, z], dim=1)
-    g = gate.reshape(G, chunks, 1, half, H)
-    u = up.reshape(G, chunks, 1, half, H)
-    return torch.cat([g, u], dim=2).reshape(G, chunks * block_n, H).contiguous()
+    lib = _lib.load()
+    _need(gate, "gate weights")
+    _need(up, "up weights")
+    if gate.shape != up.shape or gate.dim() != 3:
+        raise RuntimeError("gate and up must be 3-D tensors of the same shape")
+    G = gate.shape[0]
+    I, H = (gate.shape[1], gate.shape[2]) if feature_major else (gate.shape[2], gate.shape[1])
+    rows = lib.cd_gate_up_packed_rows(I, block_n)
+    packed = torch.empty(G, rows, H, dtype=BF16, device=gate.device)
+    _lib.check(lib.cd_pack_gate_up(gate.data_ptr(), up.data_ptr(), packed.data_ptr(), G, I, H,
+                                   block_n, 1 if feature_major else 0, _stream()),
+               "cd_pack_gate_up")
+    return packed
+
+
+def pack_down(down: torch.Tensor) -> torch.Tensor:
+    """[E, I, H] (``h @ W[e]``) -> [E, H, I] (one output feature per row) (cd_pack_down)."""
+    lib = _lib.load()
+    _need(down, "down weights")
+    E, I, H = down.shape
+    out = torch.empty(E, H, I, dtype=BF16, device=down.device)
+    _lib.check(lib.cd_pack_down(down.data_ptr(), out.data_ptr(), E, I, H, _stream()),
+               "cd_pack_down")
+    return out
 
 
 # --------------------------------------------------------------------------- GEMMs
@@ -348,11 +383,52 @@ def moe_up(x_sorted: torch.Tensor, seg_offsets: Optional[torch.Tensor], num_grou
     return h
 
 
+def moe_up_pair(x_sorted: torch.Tensor, seg_offsets: torch.Tensor, num_groups: int,
+                packed_w: torch.Tensor, width: int, packed_shared: torch.Tensor,
+                width_shared: int, block_n: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Routed (grouped) and shared (dense) SwiGLU up-projections of the same rows in one
+    launch; returns (h_routed [T, width], h_shared [T, width_shared])."""
+    lib = _lib.load()
+    _need(x_sorted, "x_sorted")
+    _need(packed_w, "packed gate/up weights")
+    _need(packed_shared, "packed shared gate/up weights")
+    _need(seg_offsets, "seg_offsets", torch.int32)
+    T, H = x_sorted.shape
+    rows = lib.cd_gate_up_packed_rows(width, block_n)
+    rows_s = lib.cd_gate_up_packed_rows(width_shared, block_n)
+    if tuple(packed_w.shape) != (num_groups, rows, H) or tuple(packed_shared.shape) != (1, rows_s, H):
+        raise RuntimeError("packed weights do not match the widths / tile width")
+    h = torch.empty(T, width, dtype=BF16, device=x_sorted.device)
+    h_s = torch.empty(T, width_shared, dtype=BF16, device=x_sorted.device)
+    with _Span("moe_up_pair"):
+        _lib.check(lib.cd_moe_up_pair(x_sorted.data_ptr(), seg_offsets.data_ptr(), num_groups,
+                                      packed_w.data_ptr(), h.data_ptr(), width,
+                                      packed_shared.data_ptr(), h_s.data_ptr(), width_shared, T, H,
+                                      block_n, _stream()), "cd_moe_up_pair")
+    return h, h_s
+
+
+def _split_args(residual, residual_lo, T, H, want_lo, device):
+    """Checks the low part of a split residual and allocates the low part of the output."""
+    lo2 = None
+    if residual_lo is not None:
+        if residual is None:
+            raise RuntimeError("residual_lo without residual")
+        lo2 = residual_lo.reshape(-1, H)
+        _need(lo2, "residual_lo")
+        if lo2.shape[0] != T:
+            raise RuntimeError("residual_lo rows do not match")
+    out_lo = torch.empty(T, H, dtype=BF16, device=device) if want_lo else None
+    return lo2, out_lo
+
+
 def moe_down(h_routed: torch.Tensor, wd_routed: torch.Tensor, h_shared: Optional[torch.Tensor],
              wd_shared: Optional[torch.Tensor], seg_offsets: Optional[torch.Tensor],
              num_experts: int, row_map: Optional[torch.Tensor],
-             residual: Optional[torch.Tensor]) -> torch.Tensor:
-    """wd_routed: [E, H, I_e] (feature rows, I_e contiguous); wd_shared: [H, I_s]."""
+             residual: Optional[torch.Tensor], residual_lo: Optional[torch.Tensor] = None,
+             want_lo: bool = False):
+    """wd_routed: [E, H, I_e] (feature rows, I_e contiguous); wd_shared: [H, I_s].
+    `residual_lo` / `want_lo`: split-bf16 residual stream; with want_lo returns (out, out_lo)."""
     lib = _lib.load()
     _need(h_routed, "h_routed")
     _need(wd_routed, "routed down weights")
@@ -377,12 +453,16 @@ def moe_down(h_routed: torch.Tensor, wd_routed: torch.Tensor, h_shared: Optional
         _need(res2, "residual")
         if res2.shape[0] != T:
             raise RuntimeError("residual rows do not match")
+    if row_map is not None and row_map.numel() != T:
+        raise RuntimeError("row_map must have one entry per row")
+    lo2, out_lo = _split_args(res2, residual_lo, T, H, want_lo, h_routed.device)
     out = torch.empty(T, H, dtype=BF16, device=h_routed.device)
     with _Span("moe_down"):
         _lib.check(lib.cd_moe_down(h_routed.data_ptr(), I_e, wd_routed.data_ptr(), _ptr(h_shared),
                                    I_s, _ptr(wd_shared), _ptr(seg_offsets), E, _ptr(row_map),
-                                   _ptr(res2), out.data_ptr(), T, H, _stream()), "cd_moe_down")
-    return out
+                                   _ptr(res2), _ptr(lo2), out.data_ptr(), _ptr(out_lo), T, H,
+                                   _stream()), "cd_moe_down")
+    return (out, out_lo) if want_lo else out
 
 
 def push_rows(x_sorted: torch.Tensor, offsets: torch.Tensor, push_base: torch.Tensor,
@@ -398,6 +478,20 @@ def push_rows(x_sorted: torch.Tensor, offsets: torch.Tensor, push_base: torch.Te
         _lib.check(lib.cd_push_rows(x_sorted.data_ptr(), None, offsets.data_ptr(),
                                     push_base.data_ptr(), num_experts, experts_per_rank,
                                     peer_ptrs_dev, T, H, _stream()), "cd_push_rows")
+
+
+def peer_barrier(flag_ptrs: torch.Tensor, flags: torch.Tensor, rank: int, world: int,
+                 limit_ms: int = 2000) -> None:
+    """Cross-GPU barrier kernel (cd_peer_barrier); `flag_ptrs` int64 [world] addresses of the
+    ranks' signal pads, `flags` this rank's pad (int32 [>= 1 + world])."""
+    lib = _lib.load()
+    _need(flag_ptrs, "flag_ptrs", torch.int64)
+    _need(flags, "flags", torch.int32)
+    if flag_ptrs.numel() != world or flags.numel() < 1 + world:
+        raise RuntimeError("signal pad too small for the group")
+    with _Span("peer_barrier"):
+        _lib.check(lib.cd_peer_barrier(flag_ptrs.data_ptr(), flags.data_ptr(), rank, world,
+                                       int(limit_ms), _stream()), "cd_peer_barrier")
 
 
 def moe_down_push(h_routed: torch.Tensor, wd_routed: torch.Tensor, seg_offsets: torch.Tensor,
@@ -420,8 +514,10 @@ def moe_down_push(h_routed: torch.Tensor, wd_routed: torch.Tensor, seg_offsets: 
 
 def moe_combine(h_shared: torch.Tensor, wd_shared: torch.Tensor,
                 routed_sorted: Optional[torch.Tensor], row_map: Optional[torch.Tensor],
-                residual: Optional[torch.Tensor]) -> torch.Tensor:
-    """Shared down projection + routed part (sorted order, from the expert GPUs) + residual."""
+                residual: Optional[torch.Tensor], residual_lo: Optional[torch.Tensor] = None,
+                want_lo: bool = False):
+    """Shared down projection + routed part (sorted order, from the expert GPUs) + residual.
+    `residual_lo` / `want_lo` as in moe_down."""
     lib = _lib.load()
     _need(h_shared, "h_shared")
     _need(wd_shared, "shared down weight")
@@ -439,12 +535,14 @@ def moe_combine(h_shared: torch.Tensor, wd_shared: torch.Tensor,
     if residual is not None:
         res2 = residual.reshape(-1, H)
         _need(res2, "residual")
+    lo2, out_lo = _split_args(res2, residual_lo, T, H, want_lo, h_shared.device)
     out = torch.empty(T, H, dtype=BF16, device=h_shared.device)
     with _Span("moe_combine"):
         _lib.check(lib.cd_moe_combine(h_shared.data_ptr(), I_s, wd_shared.data_ptr(),
-                                      _ptr(routed_sorted), _ptr(row_map), _ptr(res2),
-                                      out.data_ptr(), T, H, _stream()), "cd_moe_combine")
-    return out
+                                      _ptr(routed_sorted), _ptr(row_map), _ptr(res2), _ptr(lo2),
+                                      out.data_ptr(), _ptr(out_lo), T, H, _stream()),
+                   "cd_moe_combine")
+    return (out, out_lo) if want_lo else out
 
 
 def mu_qkv(x: torch.Tensor, mu_prev: Optional[torch.Tensor], w: torch.Tensor,
@@ -519,7 +617,10 @@ def mu_proj(h: torch.Tensor, w: torch.Tensor, mu_param: torch.Tensor, mu_min: fl
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = None,
-           tag: str = "linear") -> torch.Tensor:
+           tag: str = "linear", residual_lo: Optional[torch.Tensor] = None,
+           want_lo: bool = False):
+    """``x @ w^T (+ residual)``.  `residual_lo` / `want_lo`: split-bf16 residual stream; with
+    want_lo returns (out, out_lo)."""
     lib = _lib.load()
     _need(x, "x")
     _need(w, "weight")
@@ -531,7 +632,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = 
         # rows of the output must stay 16-byte aligned: compute into a padded buffer against
         # zero-padded weight rows and hand back the first N columns (e.g. an lm_head whose
         # vocabulary size is not a multiple of 8)
-        if residual is not None:
+        if residual is not None or want_lo:
             raise RuntimeError("residual with an output width that is not a multiple of 8")
         pad = 8 - N % 8
         w_pad = torch.cat([w, w.new_zeros(pad, K)], dim=0)
@@ -540,8 +641,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = 
         _need(residual, "residual")
         if tuple(residual.shape) != (T, N):
             raise RuntimeError("residual does not match the output")
+    lo2, out_lo = _split_args(residual, residual_lo, T, N, want_lo, x.device)
     out = torch.empty(T, N, dtype=BF16, device=x.device)
     with _Span(tag):
-        _lib.check(lib.cd_linear(x.data_ptr(), w.data_ptr(), _ptr(residual), out.data_ptr(), T, K,
-                                 N, _stream()), "cd_linear")
-    return out
+        _lib.check(lib.cd_linear(x.data_ptr(), w.data_ptr(), _ptr(residual), _ptr(lo2),
+                                 out.data_ptr(), _ptr(out_lo), T, K, N, _stream()), "cd_linear")
+    return (out, out_lo) if want_lo else out

@@ -33,12 +33,16 @@ extern "C" {
 #define CD_ERR_UNSUPPORTED 3  /* shape outside what the kernels implement */
 #define CD_ERR_TIMEOUT 4      /* a kernel gave up on a bounded wait (reported by cd_status_fetch) */
 
-/* ABI version of this header (bumped on any signature change; currently 2). */
+/* ABI version of this header (bumped on any signature change; currently 3). */
 int cd_version(void);
 /* Static text for a CD_* code. */
 const char* cd_error_string(int status);
 /* Text of the last CUDA error seen by the calling thread's last failing call. */
 const char* cd_last_cuda_error(void);
+/* Largest number of row groups (experts) one grouped GEMM launch accepts; cd_moe_up,
+ * cd_moe_up_pair, cd_moe_down and cd_moe_down_push return CD_ERR_UNSUPPORTED (text in
+ * cd_last_cuda_error) beyond it.  The dispatch entry points accept up to 256 experts. */
+int cd_max_groups(void);
 /* Synchronises the current device, copies the kernels' status word to *h_status
  * (0 = every bounded wait completed) and clears it. */
 int cd_status_fetch(int* h_status);
@@ -93,9 +97,19 @@ int cd_route_static(const int64_t* ids, const int64_t* table, int V, int E, int 
  * token_routed_mlp.py:170).
  *   h = x (+ residual, rounded to bf16);  sum_out = h (if non-null)
  *   out[dst_rows ? dst_rows[i] : i, :] = weight * h[i] * rsqrt(mean(h[i]^2) + eps)
- * residual, sum_out, dst_rows may be NULL. */
+ * residual, sum_out, dst_rows may be NULL.  sum_out is only written together with a residual
+ * (without one h is x itself) and must not alias x: both cases return CD_ERR_INVALID. */
 int cd_rmsnorm(const void* x, const void* residual, const void* weight, float eps, void* sum_out,
                void* out, const int32_t* dst_rows, int T, int H, void* stream);
+
+/* RMSNorm of a split-bf16 residual stream.  Between the kernels of a block the residual stream
+ * (complexity_deep/core/layer.py:174, :183) is carried as two bf16 tensors, hi = bf16(v) and
+ * lo = bf16(v - hi) — 16 significant bits, so the 2 * num_layers additions into the stream do
+ * not each cost a bf16 rounding of the whole stream (what keeps the logits of an 18-layer
+ * model inside mean |err| <= 2e-3 of the fp32 reference):
+ *   h = x_hi + x_lo in fp32 (x_lo may be NULL = 0);  out as in cd_rmsnorm. */
+int cd_rmsnorm_split(const void* x_hi, const void* x_lo, const void* weight, float eps, void* out,
+                     const int32_t* dst_rows, int T, int H, void* stream);
 
 /* out[j, :] = x[src_rows[j], :] — the gather `flat_x[mask]` of token_routed_mlp.py:170 for
  * all experts at once, used when the MoE layer is called without the fused norm. */
@@ -163,6 +177,29 @@ int cd_gate_up_packed_rows(int I, int block_n);
 int cd_moe_up(const void* x_sorted, const int32_t* seg_offsets, int num_groups,
               const void* packed_w, void* h, int T, int H, int I, int block_n, void* stream);
 
+/* Routed AND shared up-projections in ONE launch (token_routed_mlp.py:171-173 and :157-160):
+ * cd_moe_up over the groups, followed in the same persistent tile schedule by the dense
+ * product of the same T rows against the shared expert's packed gate/up rows
+ * (packed_shared: [cd_gate_up_packed_rows(I_s, block_n), H]) into h_shared [T, I_s].  One launch
+ * has one tail instead of two, which matters when a GPU holds few rows (small data-parallel
+ * shards).  Both weight sets are packed for the same block_n. */
+int cd_moe_up_pair(const void* x_sorted, const int32_t* seg_offsets, int num_groups,
+                   const void* packed_w, void* h, int I, const void* packed_shared, void* h_shared,
+                   int I_s, int T, int H, int block_n, void* stream);
+
+/* ---- one-off weight layout transforms ------------------------------------------------------
+ * What a host has to do once per weight version to get from the reference's parameter layouts
+ * (token_routed_mlp.py:62-77) to the operands of the entry points above; outputs go to
+ * caller-owned buffers.
+ * cd_pack_gate_up: packed [G, cd_gate_up_packed_rows(I, block_n), H] from gate and up.
+ *   feature_major = 0: gate / up are [G, H, I] (gate_proj_w / up_proj_w, used as x @ W[e]);
+ *   feature_major = 1: gate / up are [G, I, H] (nn.Linear weights, G = 1 for the shared expert).
+ * cd_pack_down: packed [E, H, I] from down_proj_w [E, I, H] (the wd_routed operand of
+ *   cd_moe_down).  The shared expert's down weight [H, I_s] is used as it is. */
+int cd_pack_gate_up(const void* gate, const void* up, void* packed, int G, int I, int H,
+                    int block_n, int feature_major, void* stream);
+int cd_pack_down(const void* down, void* packed, int E, int I, int H, void* stream);
+
 /* ---- expert down-projection, combine, un-permute, residual -------------------------------
  * Replaces the routed down GEMM and scatter (token_routed_mlp.py:174), the shared down GEMM
  * (:157-160), `routed_out + shared_out` (:177) and the block's residual add
@@ -171,11 +208,14 @@ int cd_moe_up(const void* x_sorted, const int32_t* seg_offsets, int num_groups,
  * h_routed [T, I_e], h_shared [T, I_s] (NULL = no shared expert), rows in sorted order;
  * wd_routed [E * H, I_e] (for expert e rows e*H..: one output feature per row, I_e
  * contiguous); wd_shared [H, I_s]; row_map = perm (NULL = identity); residual (NULL = none)
- * and out are [T, H] in ORIGINAL row order.  I_e % 8 == 0, I_s % 8 == 0, H % 8 == 0. */
+ * and out are [T, H] in ORIGINAL row order.  I_e % 8 == 0, I_s % 8 == 0, H % 8 == 0.
+ * Split-bf16 residual stream (see cd_rmsnorm_split): residual_lo (NULL = 0, needs residual) is
+ * the low part of the residual and is added too; with out_lo non-NULL the fp32 result v is
+ * stored as out = bf16(v), out_lo = bf16(v - out).  Both are indexed like residual / out. */
 int cd_moe_down(const void* h_routed, int I_e, const void* wd_routed, const void* h_shared,
                 int I_s, const void* wd_shared, const int32_t* seg_offsets, int E,
-                const int32_t* row_map, const void* residual, void* out, int T, int H,
-                void* stream);
+                const int32_t* row_map, const void* residual, const void* residual_lo, void* out,
+                void* out_lo, int T, int H, void* stream);
 
 /* ---- expert-parallel combine ---------------------------------------------------------------
  * Home-GPU half of the layer when the routed experts live on other GPUs: the shared expert's
@@ -184,10 +224,10 @@ int cd_moe_down(const void* h_routed, int I_e, const void* wd_routed, const void
  * from the expert GPUs (already down-projected there with cd_moe_down, h_shared = NULL):
  *   out[row_map[r], :] = h_shared[r] @ Sd^T + routed_sorted[r, :] + residual[row_map[r], :]
  * h_shared [T, I_s] and routed_sorted [T, H] in sorted order (routed_sorted may be NULL);
- * row_map / residual as in cd_moe_down. */
+ * row_map / residual / residual_lo / out_lo as in cd_moe_down. */
 int cd_moe_combine(const void* h_shared, int I_s, const void* wd_shared, const void* routed_sorted,
-                   const int32_t* row_map, const void* residual, void* out, int T, int H,
-                   void* stream);
+                   const int32_t* row_map, const void* residual, const void* residual_lo, void* out,
+                   void* out_lo, int T, int H, void* stream);
 
 /* ---- expert-parallel exchange by peer stores --------------------------------------------------
  * (The reference has no distributed code; these two entry points replace the NCCL all-to-alls
@@ -203,7 +243,19 @@ int cd_moe_combine(const void* h_shared, int I_s, const void* wd_shared, const v
  * cd_moe_down_push: the routed down projection of cd_moe_down (no shared expert, no residual)
  * whose epilogue writes sorted row r to the ADDRESS out_row_ptrs[r] (device array, one per row;
  * rows may live in another GPU's memory), so each finished tile leaves for its home GPU while
- * the next one is being computed. */
+ * the next one is being computed.
+ *
+ * cd_peer_barrier: the barrier between the phases.  Every GPU of the group owns a signal pad of
+ * 1 + world int32 (zero-initialised, peer-mapped); peer_flags is a device array of the world
+ * pads' addresses as seen from this GPU, flags this GPU's own pad.  The kernel (one block)
+ * advances this GPU's barrier count in flags[0], announces it in every pad and waits until every
+ * GPU has announced the same count.  All stores issued on this GPU before the barrier are then
+ * visible to the kernels the other GPUs launch after theirs.  The wait gives up after limit_ms
+ * (1..60000): the status word is raised (cd_status_fetch reports it) and the kernel returns, so a
+ * GPU that left the group cannot leave the others spinning.  All GPUs must call it the same
+ * number of times; the launch arguments never change, so it can be captured in a CUDA graph. */
+int cd_peer_barrier(const uint64_t* peer_flags, int32_t* flags, int rank, int world, int limit_ms,
+                    void* stream);
 int cd_push_rows(const void* x, const int32_t* src_rows, const int32_t* offsets,
                  const int32_t* push_base, int E, int experts_per_rank, const uint64_t* peer_ptrs,
                  int T, int H, void* stream);
@@ -245,9 +297,10 @@ int cd_mu_proj(const void* h, const void* w, const void* mu_param, float mu_min,
 /* ---- plain projection with optional residual ---------------------------------------------
  * out[t, :N] = x[t, :K] @ w^T (+ residual[t, :N]);  w = nn.Linear weight [N, K].
  * Replaces o_proj + residual (complexity_deep/core/attention.py:181 with layer.py:174) and
- * lm_head (complexity_deep/models/modeling.py:206).  K % 8 == 0, N % 8 == 0. */
-int cd_linear(const void* x, const void* w, const void* residual, void* out, int T, int K, int N,
-              void* stream);
+ * lm_head (complexity_deep/models/modeling.py:206).  K % 8 == 0, N % 8 == 0.
+ * residual_lo / out_lo: split-bf16 residual stream as in cd_moe_down (both may be NULL). */
+int cd_linear(const void* x, const void* w, const void* residual, const void* residual_lo,
+              void* out, void* out_lo, int T, int K, int N, void* stream);
 
 #ifdef __cplusplus
 }

@@ -43,6 +43,10 @@ def test_argument_checks_need_no_gpu():
     lib = _lib.load()
     # invalid sizes are rejected before any CUDA call
     assert lib.cd_route(None, None, 0, 8, 16, None, None, None, None, None, None, 0, None) == 1
-    assert lib.cd_linear(None, None, None, None, 16, 12, 64, None) == 1      # K % 8 != 0
+    assert lib.cd_linear(None, None, None, None, None, None, 16, 12, 64, None) == 1  # K % 8 != 0
     assert lib.cd_moe_up(None, None, 1, None, None, 16, 64, 48, 100, None) == 1  # block_n
     assert lib.cd_gate_up_packed_rows(704, 32) == 1408
+    assert lib.cd_max_groups() == 128
+    # sum_out without a residual / aliasing x is refused (the header's contract)
+    assert lib.cd_rmsnorm(64, None, 64, 1e-6, 128, 192, None, 4, 8, None) == 1
+    assert lib.cd_rmsnorm(64, 64, 64, 1e-6, 64, 192, None, 4, 8, None) == 1

@@ -98,6 +98,39 @@ def _swiglu_ref(x, gate, up):
     return F.silu(x.float() @ gate.float().t()) * (x.float() @ up.float().t())
 
 
+def _pack_ref(gate, up, block_n):
+    """Layout cd_pack_gate_up must produce, from [G, I, H] sources: per tile of block_n / 2
+    output features, the gate rows then the up rows; zero rows pad the last tile."""
+    G, I, H = gate.shape
+    half = block_n // 2
+    chunks = -(-I // half)
+    pad = chunks * half - I
+    if pad:
+        z = gate.new_zeros(G, pad, H)
+        gate, up = torch.cat([gate, z], 1), torch.cat([up, z], 1)
+    g = gate.reshape(G, chunks, 1, half, H)
+    u = up.reshape(G, chunks, 1, half, H)
+    return torch.cat([g, u], dim=2).reshape(G, chunks * block_n, H)
+
+
+@pytest.mark.parametrize("G,I,H,bn", [(2, 40, 8, 128), (1, 200, 8, 256), (3, 72, 136, 64),
+                                      (8, 704, 256, 256), (1, 33, 40, 32)])
+def test_pack_kernels_match_layout(G, I, H, bn):
+    """cd_pack_gate_up (both source layouts) and cd_pack_down, bit-exact."""
+    from complexity_deep_b200 import ops
+    g = torch.Generator().manual_seed(3)
+    gate, up = _rand(g, G, I, H), _rand(g, G, I, H)
+    want = _pack_ref(gate, up, bn)
+    got = ops.pack_gate_up(gate.cuda(), up.cuda(), bn)
+    assert got.shape == want.shape and torch.equal(got.cpu(), want)
+    got_t = ops.pack_gate_up(gate.transpose(1, 2).contiguous().cuda(),
+                             up.transpose(1, 2).contiguous().cuda(), bn, feature_major=False)
+    assert torch.equal(got_t.cpu(), want)
+    down = _rand(g, G, I, H)
+    assert torch.equal(ops.pack_down(down.cuda()).cpu(), down.transpose(1, 2).contiguous())
+    _fetch()
+
+
 @pytest.mark.parametrize("T,H,I,bn", [(128, 64, 128, 256), (200, 128, 64, 128), (77, 256, 40, 128),
                                       (1000, 768, 512, 256), (512, 2048, 704, 128),
                                       (512, 2048, 704, 256), (300, 512, 200, 256),

@@ -117,19 +117,7 @@ def test_config_presets_and_serialisation():
     assert len(m.layers) == 1 and m.config.vocab_size == 128
 
 
-def test_pack_gate_up_layout():
-    G, I, H = 2, 40, 8
-    gate = torch.arange(G * I * H, dtype=torch.float32).view(G, I, H)
-    up = -gate
-    packed = ops.pack_gate_up(gate, up, 128)          # half = 64 -> one tile, 24 zero rows
-    assert packed.shape == (G, 128, H)
-    assert torch.equal(packed[:, :40], gate) and torch.equal(packed[:, 64:104], up)
-    assert torch.all(packed[:, 40:64] == 0) and torch.all(packed[:, 104:] == 0)
-    gate2 = torch.randn(1, 200, 8)
-    packed2 = ops.pack_gate_up(gate2, 2 * gate2, 256)  # half = 128 -> two tiles
-    assert packed2.shape == (1, 512, 8)
-    assert torch.equal(packed2[0, 256:256 + 72], gate2[0, 128:])
-    assert torch.equal(packed2[0, 384:384 + 72], 2 * gate2[0, 128:])
+def test_choose_block_n():
     assert ops.choose_block_n(5632) == 256 and ops.choose_block_n(704) == 256
     assert ops.choose_block_n(64) == 128 and ops.choose_block_n(48) == 128
     assert ops.choose_block_n(704, rows=4096) == 256
