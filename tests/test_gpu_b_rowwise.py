@@ -95,3 +95,38 @@ def test_qk_norm_rope(hq, hkv, D, S, pos0, norm):
     _close(got[:, : hq * D], q.reshape(B * S, -1))
     _close(got[:, hq * D:(hq + hkv) * D], k.reshape(B * S, -1))
     assert torch.equal(got[:, (hq + hkv) * D:], qkv[:, (hq + hkv) * D:])   # V untouched
+
+
+@pytest.mark.parametrize("T,H,scatter", [(50, 64, False), (300, 768, True), (257, 2048, True),
+                                         (9, 4096, False), (5, 100, True)])
+def test_rmsnorm_split_stream(T, H, scatter):
+    """cd_rmsnorm_split: the norm of hi + lo in fp32 (a value carried as a split-bf16 pair) —
+    against the oracle on the exact fp32 sum, at a tolerance a bf16-rounded input cannot meet:
+    the result may differ from the fp32 answer only by its own final rounding."""
+    from complexity_deep_b200 import ops
+    g = torch.Generator().manual_seed(T + H)
+    v = torch.randn(T, H, generator=g)
+    hi = v.to(BF)
+    lo = (v - hi.float()).to(BF)
+    w = (torch.randn(H, generator=g) * 0.1 + 1).to(BF)
+    dst = torch.randperm(T, generator=g).to(torch.int32) if scatter else None
+    out = ops.rmsnorm(hi.cuda(), w.cuda(), 1e-6, x_lo=lo.cuda(),
+                      dst_rows=dst.cuda() if scatter else None)
+    want = oracle.rmsnorm(hi.float() + lo.float(), w.float(), 1e-6)
+    if scatter:
+        scattered = torch.empty_like(want)
+        scattered[dst.long()] = want
+        want = scattered
+    # equal to the correctly rounded bf16 of the fp32 result up to one ulp on a few elements
+    assert (out.cpu() == want.to(BF)).float().mean() > 0.98
+    _close(out, want)
+    # and measurably closer to the fp32 norm of v than the norm of hi alone
+    plain = ops.rmsnorm(hi.cuda(), w.cuda(), 1e-6, dst_rows=dst.cuda() if scatter else None)
+    ref = oracle.rmsnorm(v, w.float(), 1e-6)
+    if scatter:
+        r2 = torch.empty_like(ref)
+        r2[dst.long()] = ref
+        ref = r2
+    e_split = (out.float().cpu() - ref).abs().mean()
+    e_plain = (plain.float().cpu() - ref).abs().mean()
+    assert e_split < e_plain

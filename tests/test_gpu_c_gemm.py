@@ -363,3 +363,101 @@ def test_push_rows_places_sorted_rows_in_owner_buffers():
         lo, hi = int(offsets[e]), int(offsets[e + 1])
         got = bufs[e // per_rank][int(base[e]):int(base[e]) + hi - lo].cpu()
         assert torch.equal(got, x[lo:hi]), e
+
+
+def _split(v):
+    """fp32 -> (hi, lo) bf16 pair with hi = bf16(v), lo = bf16(v - hi)."""
+    hi = v.to(BF)
+    return hi, (v - hi.float()).to(BF)
+
+
+@pytest.mark.parametrize("T,K,N", [(128, 64, 256), (300, 128, 264), (1000, 768, 1024),
+                                   (4096, 2048, 2048), (40, 256, 96), (129, 1032, 520)])
+@pytest.mark.parametrize("res_lo", [False, True])
+def test_linear_split_residual_stream(T, K, N, res_lo):
+    """cd_linear with the residual as a split-bf16 pair and the result stored as one: hi must be
+    the correctly rounded fp32 result (up to accumulation-order noise) and hi + lo must be
+    closer to it by two orders of magnitude than a bf16 tensor can be."""
+    from complexity_deep_b200 import ops
+    g = torch.Generator().manual_seed(T + K + N)
+    x, w = _rand(g, T, K), _rand(g, N, K, scale=0.05)
+    r_hi, r_lo = _split(torch.randn(T, N, generator=g))
+    out, out_lo = ops.linear(x.cuda(), w.cuda(), r_hi.cuda(), residual_lo=r_lo.cuda() if res_lo else None,
+                             want_lo=True)
+    _fetch()
+    ref = x.float() @ w.float().t() + r_hi.float() + (r_lo.float() if res_lo else 0)
+    _close(out, ref)
+    both = out.float().cpu() + out_lo.float().cpu()
+    rms = float(ref.pow(2).mean().sqrt())
+    err_pair = float((both - ref).abs().mean())
+    err_hi = float((out.float().cpu() - ref).abs().mean())
+    assert err_pair <= 2e-5 * max(1.0, rms), (err_pair, rms)      # fp32 accumulation-order noise
+    assert err_pair * 20 < err_hi
+
+
+@pytest.mark.parametrize("T,H,Ie,Is,E", [(300, 64, 64, 64, 4), (2048, 768, 512, 512, 4),
+                                         (130, 264, 40, 200, 3), (5000, 256, 136, 72, 8)])
+def test_moe_down_split_residual_stream(T, H, Ie, Is, E):
+    from complexity_deep_b200 import ops
+    g = torch.Generator().manual_seed(23)
+    hr, wd = _rand(g, T, Ie), _rand(g, E, H, Ie, scale=0.05)
+    hs, ws = _rand(g, T, Is), _rand(g, H, Is, scale=0.05)
+    seg = _segments(g, T, E, (1,) if E > 3 else ())
+    pm = torch.randperm(T, generator=g).to(torch.int32)
+    r_hi, r_lo = _split(torch.randn(T, H, generator=g))
+    out, out_lo = ops.moe_down(hr.cuda(), wd.cuda(), hs.cuda(), ws.cuda(), seg.cuda(), E, pm.cuda(),
+                               r_hi.cuda(), r_lo.cuda(), True)
+    _fetch()
+    acc = torch.empty(T, H)
+    for e in range(E):
+        lo, hi = int(seg[e]), int(seg[e + 1])
+        acc[lo:hi] = hr[lo:hi].float() @ wd[e].float().t()
+    acc += hs.float() @ ws.float().t()
+    ref = torch.empty(T, H)
+    ref[pm.long()] = acc
+    ref = ref + r_hi.float() + r_lo.float()
+    _close(out, ref)
+    rms = float(ref.pow(2).mean().sqrt())
+    err_pair = float((out.float().cpu() + out_lo.float().cpu() - ref).abs().mean())
+    assert err_pair <= 2e-5 * max(1.0, rms), (err_pair, rms)
+
+
+def test_moe_combine_split_residual_stream():
+    from complexity_deep_b200 import ops
+    g = torch.Generator().manual_seed(29)
+    T, H, Is = 777, 512, 264
+    hs, ws, yr = _rand(g, T, Is), _rand(g, H, Is, scale=0.05), _rand(g, T, H)
+    pm = torch.randperm(T, generator=g).to(torch.int32)
+    r_hi, r_lo = _split(torch.randn(T, H, generator=g))
+    out, out_lo = ops.moe_combine(hs.cuda(), ws.cuda(), yr.cuda(), pm.cuda(), r_hi.cuda(), r_lo.cuda(),
+                                  True)
+    _fetch()
+    ref = torch.empty(T, H)
+    ref[pm.long()] = hs.float() @ ws.float().t() + yr.float()
+    ref = ref + r_hi.float() + r_lo.float()
+    _close(out, ref)
+    err_pair = float((out.float().cpu() + out_lo.float().cpu() - ref).abs().mean())
+    assert err_pair <= 2e-5 * max(1.0, float(ref.pow(2).mean().sqrt()))
+
+
+@pytest.mark.parametrize("T,H,I,Is,E,bn,empty", [
+    (300, 64, 64, 64, 4, 128, ()), (1000, 128, 136, 200, 8, 256, (2,)),
+    (4096, 768, 512, 512, 4, 256, ()), (517, 256, 72, 40, 32, 128, (0, 31)),
+    (8192, 2048, 704, 704, 8, 256, ()), (256, 256, 88, 88, 8, 32, (3,)), (40, 128, 48, 112, 4, 64, ())])
+def test_moe_up_pair_routed_and_shared_one_launch(T, H, I, Is, E, bn, empty):
+    """cd_moe_up_pair = cd_moe_up over the groups + cd_moe_up of the shared expert, same bits."""
+    from complexity_deep_b200 import ops
+    g = torch.Generator().manual_seed(31)
+    x = _rand(g, T, H)
+    gate, up = _rand(g, E, I, H, scale=0.05), _rand(g, E, I, H, scale=0.05)
+    sg, su = _rand(g, 1, Is, H, scale=0.05), _rand(g, 1, Is, H, scale=0.05)
+    seg = _segments(g, T, E, empty).cuda()
+    packed = ops.pack_gate_up(gate.cuda(), up.cuda(), bn)
+    packed_s = ops.pack_gate_up(sg.cuda(), su.cuda(), bn)
+    xc = x.cuda()
+    h, hs = ops.moe_up_pair(xc, seg, E, packed, I, packed_s, Is, bn)
+    h1 = ops.moe_up(xc, seg, E, packed, I, bn)
+    hs1 = ops.moe_up(xc, None, 1, packed_s, Is, bn)
+    _fetch()
+    assert torch.equal(h, h1) and torch.equal(hs, hs1)
+    _close(hs, _swiglu_ref(x, sg[0], su[0]))

@@ -5,7 +5,7 @@ Tolerance: max|y - ref| / max|ref| <= 2e-2 and mean|y - ref| <= 2e-3 * max(1, rm
 import pytest
 import torch
 
-from conftest import load_golden
+from conftest import assert_close, load_golden
 from oracle import complexity_oracle as oracle
 
 pytestmark = pytest.mark.gpu
@@ -13,12 +13,7 @@ BF = torch.bfloat16
 
 
 def _close(got, ref, max_rel=2e-2, mean_abs=2e-3):
-    got, ref = got.float().cpu(), ref.float().cpu()
-    assert got.shape == ref.shape
-    assert torch.isfinite(got).all()
-    mr, ma = oracle.error_metrics(got, ref)
-    rms = float(ref.double().pow(2).mean().sqrt())
-    assert mr <= max_rel and ma <= mean_abs * max(1.0, rms), (mr, ma, rms)
+    assert_close(got, ref, max_rel, mean_abs)
 
 
 def _bf16_state(sd):
@@ -213,3 +208,23 @@ def test_prefill_layer_full_size_row_permutation_equivariance():
     mr, ma = oracle.error_metrics(out[rows.cuda()].float().cpu(), ref)
     rms = float(ref.pow(2).mean().sqrt())
     assert mr <= 2e-2 and ma <= 2e-3 * max(1.0, rms), (mr, ma, rms)
+
+
+def test_scale_out_layer_shape_sampled_rows():
+    """The expert-parallel scale-out layer's shape on one GPU: hidden 4096, 32 experts of width
+    2816, shared expert of width 11008 (wider than a routed expert: I_s != I_e), vocab 100000,
+    Zipf(1.0) ids, bin-packed table, x ~ N(0, 1); 8192 tokens (one GPU's share of the 65 536).
+    Sampled rows against the fp32 oracle, tolerance as written."""
+    from conftest import build_wide_shared_layer
+    from complexity_deep_b200 import ops
+    H, E, I_e, I_s, V, T = 4096, 32, 2816, 11008, 100000, 8192
+    mlp, sd, _ = build_wide_shared_layer(H, E, I_e, I_s, V, 1.0)
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(T, H, generator=g).to(BF)
+    ids = oracle.zipf_token_ids(V, 1.0, T, seed=3)
+    out = mlp(x.cuda().view(4, T // 4, H), ids.cuda().view(4, T // 4)).view(T, H)
+    ops.status_fetch()
+    assert torch.isfinite(out).all()
+    rows = torch.randperm(T, generator=g)[:256]
+    ref = oracle.token_routed_mlp(sd, "", x[rows].float()[None], ids[rows][None])[0]
+    assert_close(out[rows.cuda()], ref, what="scale-out layer shape (H 4096, I_e 2816, I_s 11008)")

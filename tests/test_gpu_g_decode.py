@@ -5,6 +5,8 @@ max(1, rms(ref)) (outputs are rounded to bf16 once)."""
 import pytest
 import torch
 
+from conftest import assert_close
+
 from oracle import complexity_oracle as oracle
 
 pytestmark = pytest.mark.gpu
@@ -12,11 +14,7 @@ BF = torch.bfloat16
 
 
 def _close(got, ref, max_rel=2e-2, mean_abs=2e-3):
-    got, ref = got.float().cpu(), ref.float().cpu()
-    assert got.shape == ref.shape and torch.isfinite(got).all()
-    mr, ma = oracle.error_metrics(got, ref)
-    rms = float(ref.double().pow(2).mean().sqrt())
-    assert mr <= max_rel and ma <= mean_abs * max(1.0, rms), (mr, ma, rms)
+    assert_close(got, ref, max_rel, mean_abs)
 
 
 @pytest.mark.parametrize("B,hq,hkv,D,L", [(3, 4, 2, 64, 1), (2, 4, 2, 128, 7), (3, 16, 8, 128, 300),

@@ -237,3 +237,30 @@ def test_rotary_tables_grow_geometrically():
     assert torch.equal(cos_b[:16], cos_a)
     ref = RotaryEmbedding(16, max_seq_len=32)
     assert torch.equal(ref.cos_cached, cos_b) and torch.equal(ref.sin_cached, sin_b)
+
+
+def test_expert_parallel_rejects_oversized_batch_before_any_collective(monkeypatch):
+    """A rank whose batch does not fit the exchange buffers must raise before it enters any
+    collective or launches anything: it then has nothing in flight, and since no rank ever
+    sends more than max_tokens_per_rank rows no receive buffer can be overrun."""
+    from types import SimpleNamespace
+    from complexity_deep_b200 import expert_parallel as epm
+    ep = epm.ExpertParallelMoE.__new__(epm.ExpertParallelMoE)
+    ep.exchange, ep.max_tokens = "peer", 8
+    ep.mlp = SimpleNamespace(num_experts=4)
+
+    def reached(*a, **k):
+        raise AssertionError("a collective / launch was reached before the size check")
+    monkeypatch.setattr(ep, "peer_plan_for", reached, raising=False)
+    monkeypatch.setattr(ep, "_peer_buffers", reached, raising=False)
+    monkeypatch.setattr(epm.dist, "all_gather_into_tensor", reached)
+    routing = SimpleNamespace(perm=torch.zeros(9, dtype=torch.int32), num_experts=4)
+    with pytest.raises(ValueError, match="max_tokens_per_rank"):
+        ep.forward_sorted(torch.zeros(9, 4), routing, None)
+    short = SimpleNamespace(perm=torch.zeros(5, dtype=torch.int32), num_experts=4)
+    with pytest.raises(ValueError, match="token_ids"):
+        ep.forward_sorted(torch.zeros(8, 4), short, None)
+    ep.max_tokens = 0
+    ok = SimpleNamespace(perm=torch.zeros(8, dtype=torch.int32), num_experts=4)
+    with pytest.raises(ValueError, match="needs max_tokens_per_rank"):
+        ep.forward_sorted(torch.zeros(8, 4), ok, None)

@@ -32,10 +32,13 @@ def _both(lib, ids, table, E):
     _lib.check(lib.cd_route(ids.data_ptr(), table.data_ptr(), V, E, T, *[t.data_ptr() for t in a],
                             ws.data_ptr(), ws.numel(), stream), "cd_route")
     b = _outputs(T, E, dev)
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info(dev)
     _lib.check(lib.cd_route_static(ids.data_ptr(), table.data_ptr(), V, E, T,
                                    *[t.data_ptr() for t in b], stream), "cd_route_static")
     torch.cuda.synchronize()
-    return a, b
+    free_after, _ = torch.cuda.mem_get_info(dev)
+    return a, b, free_before - free_after
 
 
 def test_static_scratch_dispatch_matches_cd_route_twice():
@@ -46,12 +49,23 @@ def test_static_scratch_dispatch_matches_cd_route_twice():
     # call 1: many blocks, 32 experts; call 2: fewer tokens, 8 experts, skewed ids
     cases = [(50000, 4096, 32, torch.randint(-10, 4200, (50000,), generator=g)),
              (3001, 1000, 8, (torch.randint(0, 1000, (3001,), generator=g) ** 2) // 1000)]
-    for T, V, E, ids in cases:
+    from oracle import complexity_oracle as oracle
+    for n, (T, V, E, ids) in enumerate(cases):
         table = (torch.arange(V) * 7 + 3) % E
-        a, b = _both(lib, ids.to(dev), table.to(dev), E)
+        a, b, grew = _both(lib, ids.to(dev), table.to(dev), E)
         names = ["expert_ids", "counts", "offsets", "perm", "inv_perm"]
-        for name, x, y in zip(names, a, b):
+        want = oracle.route(ids.numpy(), table.numpy(), E)     # the CPU oracle, directly
+        for name, x, y, w in zip(names, a, b, want):
             assert torch.equal(x, y), name        # integer artefacts: bit-exact
+            assert np.array_equal(y.cpu().numpy(), w), name
+        if n > 0:   # (the first call on a device may load the library's kernels)
+            # free device memory as the driver reports it, before and after the call; repeated a
+            # few times so that an unrelated process on the same GPU cannot fail the check
+            for _ in range(3):
+                if grew <= 0:
+                    break
+                grew = _both(lib, ids.to(dev), table.to(dev), E)[2]
+            assert grew <= 0, f"device memory in use grew by {grew} bytes across the call"
         assert int(b[2][-1]) == T and int(b[1].sum()) == T
         assert np.array_equal(np.sort(b[3].cpu().numpy()), np.arange(T))
 
