@@ -33,8 +33,8 @@ WORKLOAD = "1B-class prefill: hidden 2048, 24 layers, 16Q/8KV (D 128), intermedi
 MODEL = dict(vocab_size=32000, hidden_size=2048, intermediate_size=5632, num_hidden_layers=24,
              num_attention_heads=16, num_key_value_heads=8, num_experts=8)
 GLOBAL_BATCH, SEQ_LEN = 32, 2048
-# DRAM traffic of one cd_mu_qkv launch per token, from the ncu capture summarised in
-# profiles/gemm_bf16_sm100_1b_layer_small_case.md (555 + 182 MB at 24 576 tokens)
+# DRAM traffic of one cd_mu_qkv launch per token, from an ncu small-case capture of the kernel
+# (dram__bytes_read + dram__bytes_write = 555 + 182 MB at 24 576 tokens)
 MU_QKV_DRAM_BYTES_PER_TOKEN = 737.46e6 / 24576
 
 
@@ -320,8 +320,8 @@ def run_ours(args):
                     "ms_per_launch": round(k["ms_total"] / k["launches"], 4),
                     "traffic": (round(MU_QKV_DRAM_BYTES_PER_TOKEN * local_tokens)
                                 if dom == "mu_qkv" else None),
-                    "traffic_source": "ncu dram__bytes_read+write of cd_mu_qkv_rope at 24576 tokens "
-                                      "(737 MB), scaled per token; profiles/"}
+                    "traffic_source": "ncu small-case capture: dram__bytes_read+write of "
+                                      "cd_mu_qkv_rope at 24576 tokens (737 MB), scaled per token"}
     gpu_launches = sum(v[2] for v in prof.values())
 
     line = {
@@ -350,8 +350,22 @@ def run_ours(args):
                                  "moe_down", "mu_proj", "attention")) * fl["layers"]
              + fl["linear_lm_head"]) * value / world / 1e12 / pk["bf16_tflops"], 4),
     }
+    if rank == 0 and world == 1 and not args.no_parity:
+        line["parity"] = model_parity(model)
+    # free the model before the layer workloads below
+    del graph, model
+    torch.cuda.empty_cache()
+    if not args.no_layer_records:
+        # second half of the metric, in the same run and process group: the isolated MoE layer on
+        # one GPU, the expert-parallel scale-out layer (peer-store exchange) on several
+        if world == 1:
+            rec = layer_record(args, "moe_layer", dist, dev, rank, world, local_rank)
+            line["moe_layer"] = compact_layer_record(rec)
+        elif LAYER_CONFIGS["ep_layer"]["E"] % world == 0:
+            rec = layer_record(args, "ep_layer", dist, dev, rank, world, local_rank)
+            line["ep_layer"] = compact_layer_record(rec)
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        line["cpu_baseline"] = cpu_baseline(sample_tokens=args.cpu_tokens, steps=1, warmup=0)
+        line["cpu_baseline"] = cpu_baseline(sample_tokens=args.cpu_tokens, steps=2, warmup=1)
     if rank == 0:
         print(json.dumps(line), flush=True)
     if dist is not None:
@@ -359,32 +373,118 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def compact_layer_record(rec: dict) -> dict:
+    """The figures of a layer workload that travel inside the prefill line."""
+    keep = ("value", "unit", "ms_per_step", "ms_per_step_routing_cached", "tflops_routing_cached",
+            "frac_of_peak", "frac_of_peak_routing_cached", "peak_source", "tokens_per_s", "parity",
+            "rows_received_per_gpu", "kernels")
+    out = {k: rec[k] for k in keep if rec.get(k) is not None}
+    out["config"] = {k: rec["config"][k] for k in ("workload", "T", "H", "E", "I_e", "I_s",
+                                                   "parallelism", "tokens_per_gpu", "flop_per_step")}
+    return out
+
+
+@torch.no_grad()
+def model_parity(model, tokens: int = 512) -> dict:
+    """Logits of the benchmarked model itself (all 24 layers, its own weights) on one sequence
+    of `tokens` Zipf ids against the fp32 oracle on the same bf16-rounded weights — a bounded
+    sample the CPU finishes in seconds; causal attention makes a shorter sequence a sub-problem
+    of the full one.  Figures only; the tests assert."""
+    from complexity_deep_b200 import ops
+    from oracle import complexity_oracle as oracle
+    dev = next(model.parameters()).device
+    ids = zipf_token_ids(MODEL["vocab_size"], 1.1, tokens, seed=12345).view(1, tokens)
+    logits = model(ids.to(dev)).logits.float().cpu()
+    ops.status_fetch()
+    sd = {k: (v.float().cpu() if v.is_floating_point() else v.cpu())
+          for k, v in model.state_dict().items()}
+    ref, _ = oracle.model_forward(sd, MODEL, ids)
+    del sd
+    max_rel, mean_abs = oracle.error_metrics(logits, ref)
+    return {"max_rel": float(f"{max_rel:.3e}"), "mean_abs": float(f"{mean_abs:.3e}"),
+            "argmax_agreement": round(float((logits.argmax(-1) == ref.argmax(-1)).float().mean()), 4),
+            "rms_ref": round(float(ref.pow(2).mean().sqrt()), 3),
+            "bf16_rounding_of_exact_logits_mean_abs": float(
+                f"{float((ref.to(torch.bfloat16).float() - ref).abs().mean()):.3e}"),
+            "sample": f"logits of 1 x {tokens} tokens through all {MODEL['num_hidden_layers']} layers",
+            "against": "fp32 oracle (CPU) on the same bf16-rounded weights",
+            "tolerance": "max_rel <= 2e-2, mean_abs <= 2e-3"}
+
+
 # ------------------------------------------------------------------------------- CPU arm
+REF_DIR = os.path.join(ROOT, "oracle", "_ref")
+
+
+def load_reference_package():
+    """The reference's own `complexity_deep` package from oracle/_ref (placed there, unmodified,
+    by oracle/make_ref.py), or None.  It must win over this repository's import-name shim of
+    the same name, so it goes first on the path and any earlier import is dropped."""
+    if not os.path.isfile(os.path.join(REF_DIR, "complexity_deep", "__init__.py")):
+        return None
+    for name in [n for n in sys.modules if n == "complexity_deep" or n.startswith("complexity_deep.")]:
+        del sys.modules[name]
+    sys.path.insert(0, REF_DIR)
+    try:
+        import complexity_deep as ref
+        if os.path.dirname(os.path.abspath(ref.__file__)) != os.path.join(REF_DIR, "complexity_deep"):
+            return None
+        return ref
+    except Exception as exc:  # noqa: BLE001
+        print(f"[bench] reference package in oracle/_ref failed to import ({exc})", file=sys.stderr)
+        return None
+    finally:
+        sys.path.remove(REF_DIR)
+
+
+def reference_model(ref, device, dtype):
+    """The reference's ComplexityModel for the bench workload: its own constructor and
+    initialisation under manual_seed(0), the bin-packed Zipf table copied into every layer."""
+    from oracle import complexity_oracle as oracle
+    torch.manual_seed(0)
+    with torch.device(device):
+        model = ref.ComplexityModel(ref.ComplexityConfig(**MODEL))
+    model = model.to(dtype=dtype).eval()
+    p = oracle.zipf_probabilities(MODEL["vocab_size"], 1.1).float()
+    table = torch.from_numpy(oracle.build_token_mapping(MODEL["vocab_size"], MODEL["num_experts"], p))
+    with torch.no_grad():
+        for layer in model.layers:
+            layer.mlp.token_to_expert.copy_(table)
+    return model
+
+
 def cpu_baseline(sample_tokens: int, steps: int, warmup: int) -> dict:
-    """Times the oracle port (a restatement of the reference's PyTorch forward) on the host
-    cores, fp32, on one sequence of `sample_tokens` tokens of the same workload."""
+    """Times the reference's forward on the host cores, fp32, all threads, on one sequence of
+    `sample_tokens` tokens of the same workload: the reference's own modules when oracle/_ref
+    holds them (kind "reference"), else the oracle port (kind "port")."""
     from oracle import complexity_oracle as oracle
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     cfg = dict(MODEL)
-    p = oracle.zipf_probabilities(cfg["vocab_size"], 1.1).float()
-    from complexity_deep_b200 import TokenRoutedMLP  # host-side table builder (bit-exact, fast)
-    cfg["token_to_expert"] = TokenRoutedMLP._build_token_mapping(cfg["vocab_size"],
-                                                                 cfg["num_experts"], p)
-    sd = oracle.random_model_state(cfg, seed=0, dtype=torch.float32)
+    ref = load_reference_package()
+    if ref is not None:
+        model = reference_model(ref, "cpu", torch.float32)
+        forward = lambda ids: model(ids).logits                      # noqa: E731
+        kind, what = "reference", "the reference's own ComplexityModel (oracle/_ref, unmodified)"
+    else:
+        p = oracle.zipf_probabilities(cfg["vocab_size"], 1.1).float()
+        cfg["token_to_expert"] = torch.from_numpy(
+            oracle.build_token_mapping(cfg["vocab_size"], cfg["num_experts"], p))
+        sd = oracle.random_model_state(cfg, seed=0, dtype=torch.float32)
+        forward = lambda ids: oracle.model_forward(sd, cfg, ids)[0]  # noqa: E731
+        kind, what = "port", "oracle port of the reference's PyTorch forward"
     times = []
     with torch.no_grad():
         for i in range(warmup + steps):
             ids = oracle.zipf_token_ids(cfg["vocab_size"], 1.1, sample_tokens, seed=i).view(1, -1)
             t = time.perf_counter()
-            oracle.model_forward(sd, cfg, ids)
+            forward(ids)
             if i >= warmup:
                 times.append(time.perf_counter() - t)
     total = sum(times)
     return {"value": round(sample_tokens * len(times) / total, 1), "unit": UNIT, "cores": cores,
-            "kind": "port", "dtype": "f32", "seconds_per_step": round(total / len(times), 3),
+            "kind": kind, "dtype": "f32", "seconds_per_step": round(total / len(times), 3),
             "sample": f"1 sequence x {sample_tokens} tokens of the same model (all 24 layers + lm_head), "
-                      f"oracle port of the reference's PyTorch forward, {cores} threads"}
+                      f"{what}, {cores} threads"}
 
 
 def run_reference(args):
@@ -407,6 +507,43 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def run_reference_gpu(args):
+    """Not part of the driver's contract: the UNMODIFIED reference (oracle/_ref) on one GPU in
+    bf16, same workload and ids, CUDA events — the like-for-like figure for the kernels here."""
+    ref = load_reference_package()
+    if ref is None:
+        print(json.dumps({"impl": "reference-gpu", "unavailable": "oracle/_ref is not populated "
+                          "(run oracle/make_ref.py where the reference checkout is)"}), flush=True)
+        return
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    model = reference_model(ref, dev, torch.bfloat16)
+    batch = args.batch or GLOBAL_BATCH
+    steps_total = args.warmup + args.steps
+    ids = [zipf_token_ids(MODEL["vocab_size"], 1.1, batch * SEQ_LEN, seed=s).view(batch, SEQ_LEN).to(dev)
+           for s in range(steps_total)]
+    with torch.no_grad():
+        for i in range(args.warmup):
+            model(ids[i])
+        torch.cuda.synchronize()
+        sampler = ClockSampler(0)
+        sampler.start()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for i in range(args.warmup, steps_total):
+            model(ids[i])
+        t1.record()
+        torch.cuda.synchronize()
+    ms = t0.elapsed_time(t1)
+    print(json.dumps({
+        "metric": METRIC, "value": round(batch * SEQ_LEN * args.steps / (ms / 1e3), 1), "unit": UNIT,
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms / args.steps, 3), "higher_is_better": True, "dtype": "bf16",
+        "data": "synthetic", "impl": "reference-gpu",
+        "config": {"workload": WORKLOAD, "global_batch": batch, "seq_len": SEQ_LEN,
+                   "parallelism": "1 GPU, the reference's stock PyTorch path"},
+        "clocks": sampler.stop()}), flush=True)
+
 
 # ------------------------------------------------------------------------------- layer modes
 LAYER_CONFIGS = {
@@ -417,27 +554,26 @@ LAYER_CONFIGS = {
 }
 
 
-def run_layer(args):
-    """MoE-layer TFLOP/s: the isolated layer (1 GPU) or the expert-parallel layer (N GPUs, the
-    T tokens split across ranks, experts sharded E/N per rank, NCCL all-to-all both ways)."""
+def init_dist(dev, rank, world, force=False):
+    """torch.distributed over NCCL, one process per GPU (None on a single GPU unless forced)."""
+    if world == 1 and not force:
+        return None
+    import torch.distributed as dist
+    if not dist.is_initialized():
+        if "MASTER_ADDR" not in os.environ:
+            os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT="29577")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    return dist
+
+
+def layer_record(args, workload, dist, dev, rank, world, local_rank):
+    """Times one MoE-layer workload for args.steps steps and checks sampled rows of every
+    rank's output against the fp32 oracle of the unsharded layer.  Returns the record."""
     import torch.nn as nn
     from complexity_deep_b200 import TokenRoutedMLP, ops
     from complexity_deep_b200.expert_parallel import ExpertParallelMoE
-    cfg = LAYER_CONFIGS[args.workload]
-    rank = int(os.environ.get("RANK", 0))
-    local_rank = int(os.environ.get("LOCAL_RANK", 0))
-    world = int(os.environ.get("WORLD_SIZE", 1))
-    if world != args.gpus:
-        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun")
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    dist = None
-    if world > 1 or args.workload == "ep_layer":
-        import torch.distributed as dist
-        if not dist.is_initialized():
-            if "MASTER_ADDR" not in os.environ:
-                os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT="29577")
-            dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from oracle import complexity_oracle as oracle
+    cfg = LAYER_CONFIGS[workload]
     T, H, E, I_e, I_s, V = (cfg[k] for k in ("T", "H", "E", "I_e", "I_s", "V"))
     lo, hi = shard_batch(T, world, rank)
     t_loc = hi - lo
@@ -455,7 +591,7 @@ def run_layer(args):
     with torch.no_grad():
         mlp.token_to_expert.copy_(table)
     ep = None
-    if args.workload == "ep_layer":
+    if workload == "ep_layer":
         # expected rows per expert from the token frequencies, for the balanced placement
         load = torch.bincount(table, weights=p.double(), minlength=E)
         ep = ExpertParallelMoE(mlp, expert_load=load if args.ep_placement == "balanced" else None,
@@ -501,7 +637,7 @@ def run_layer(args):
     ops.PROFILE.reset(enabled=False)
     # the same layer on an id batch whose dispatch (and exchange plan) is already cached, as
     # layers 2..L of a forward pass see it
-    step(steps_total - 1)
+    y = step(steps_total - 1)
     barrier()
     t0.record()
     for _ in range(args.steps):
@@ -510,17 +646,37 @@ def run_layer(args):
     barrier()
     ms_cached = aggregate_ms(t0.elapsed_time(t1), dist, dev)
     ops.status_fetch()
+
+    # parity: sampled rows of THIS rank's output against the fp32 oracle of the unsharded layer
+    # on the same bf16-rounded weights and inputs; the worst rank is reported
+    rows = torch.randperm(t_loc, generator=torch.Generator().manual_seed(7 + rank))[:96]
+    sd = {k: v.detach().float().cpu() for k, v in mlp.named_parameters()}
+    sd["token_to_expert"] = table
+    with torch.no_grad():
+        ref = oracle.token_routed_mlp(sd, "", x[rows.to(dev)].float().cpu()[None],
+                                      ids[-1][rows.to(dev)].cpu()[None])[0]
+    del sd
+    max_rel, mean_abs = oracle.error_metrics(y.view(t_loc, H)[rows.to(dev)].float().cpu(), ref)
+    worst = torch.tensor([max_rel, mean_abs], dtype=torch.float64, device=dev)
+    if dist is not None:
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+    parity = {"max_rel": float(f"{worst[0].item():.3e}"), "mean_abs": float(f"{worst[1].item():.3e}"),
+              "rows_per_gpu": int(rows.numel()), "rms_ref": round(float(ref.pow(2).mean().sqrt()), 3),
+              "against": "fp32 oracle of the unsharded layer, worst rank",
+              "within_tolerance": bool(worst[0].item() <= 2e-2 and worst[1].item() <= 2e-3 * max(
+                  1.0, float(ref.pow(2).mean().sqrt())))}
+
     flop = 6 * T * H * I_e + 6 * T * H * I_s + (2 * T * 2 * H * cfg["qkv"] if cfg["qkv"] else 0)
     tflops = flop * args.steps / (ms / 1e3) / 1e12
     pk = peaks()
     received = None
     if ep is not None:
-        rows = torch.tensor([ep.plan_for(ep.routing(ids[-1].view(1, t_loc)))[0].received],
-                            device=dev)
-        gathered = [torch.empty_like(rows) for _ in range(world)]
-        dist.all_gather(gathered, rows)
+        rows_t = torch.tensor([ep.plan_for(ep.routing(ids[-1].view(1, t_loc)))[0].received],
+                              device=dev)
+        gathered = [torch.empty_like(rows_t) for _ in range(world)]
+        dist.all_gather(gathered, rows_t)
         received = [int(r) for r in gathered]
-    line = {
+    return {
         "metric": "MoE-layer TFLOP/s (bf16)", "value": round(tflops, 1), "unit": "TFLOP/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms / args.steps, 4),
@@ -528,18 +684,36 @@ def run_layer(args):
         "tflops_routing_cached": round(flop * args.steps / (ms_cached / 1e3) / 1e12, 1),
         "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "b200",
-        "config": {"workload": args.workload, **{k: v for k, v in cfg.items()},
+        "config": {"workload": workload, **{k: v for k, v in cfg.items()},
                    "parallelism": (f"ep{world}: {E // world} experts per GPU ({args.ep_placement} "
                                    f"placement, {args.ep_exchange} exchange), tokens dp{world}"
                                    if ep is not None else "1 GPU"),
                    "tokens_per_gpu": t_loc, "flop_per_step": flop},
         "tokens_per_s": round(T * args.steps / (ms / 1e3), 1),
         "frac_of_peak": round(tflops / world / pk["bf16_tflops"], 4),
+        "frac_of_peak_routing_cached": round(flop * args.steps / (ms_cached / 1e3) / 1e12 / world
+                                             / pk["bf16_tflops"], 4),
         "peak": pk["bf16_tflops"], "peak_source": pk["source"] + " burst, per GPU",
+        "parity": parity,
         "rows_received_per_gpu": received, "clocks": clocks,
         "gpu_launches": sum(v[2] for v in prof.values()),
         "kernels": {k: {"launches": v[0], "ms_total": round(v[1], 3)} for k, v in prof.items()},
     }
+
+
+def run_layer(args):
+    """MoE-layer TFLOP/s: the isolated layer (1 GPU) or the expert-parallel layer (N GPUs, the
+    T tokens split across ranks, experts sharded E/N per rank, exchange by peer stores or NCCL
+    all-to-all)."""
+    rank = int(os.environ.get("RANK", 0))
+    local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = init_dist(dev, rank, world, force=args.workload == "ep_layer")
+    line = layer_record(args, args.workload, dist, dev, rank, world, local_rank)
     if rank == 0:
         print(json.dumps(line), flush=True)
     if dist is not None:
@@ -691,11 +865,14 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=8)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference", "reference-gpu"])
     ap.add_argument("--batch", type=int, default=0, help="global batch override (debug only)")
-    ap.add_argument("--cpu-tokens", type=int, default=1024,
+    ap.add_argument("--cpu-tokens", type=int, default=2048,
                     help="tokens of the bounded CPU sample (one sequence)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="skip the in-run oracle check of the logits")
+    ap.add_argument("--no-layer-records", action="store_true",
+                    help="prefill_1b: skip the MoE-layer (1 GPU) / expert-parallel layer (N GPUs) sub-record")
     ap.add_argument("--graph", dest="graph", action="store_true", default=True,
                     help="prefill_1b: the end-to-end loop replays a CUDA graph of the forward (default)")
     ap.add_argument("--no-graph", dest="graph", action="store_false")
@@ -713,6 +890,8 @@ def main():
         args.warmup = 3
     if args.impl == "reference":
         run_reference(args)
+    elif args.impl == "reference-gpu":
+        run_reference_gpu(args)
     elif args.workload == "decode_1b":
         run_decode(args)
     elif args.workload != "prefill_1b":

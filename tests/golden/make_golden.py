@@ -15,8 +15,9 @@ import sys
 import numpy as np
 import torch
 
-REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("COMPLEXITY_DEEP_REFERENCE",
-                                                          "/root/reference")
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("COMPLEXITY_DEEP_REFERENCE")
+if not REF:
+    raise SystemExit("usage: make_golden.py <reference checkout> (or set COMPLEXITY_DEEP_REFERENCE)")
 sys.path.insert(0, REF)
 from complexity_deep.core.attention import ComplexityAttention  # noqa: E402
 from complexity_deep.core.layer import MuGuidance, TransformerBlock  # noqa: E402

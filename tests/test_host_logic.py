@@ -264,3 +264,36 @@ def test_expert_parallel_rejects_oversized_batch_before_any_collective(monkeypat
     ok = SimpleNamespace(perm=torch.zeros(8, dtype=torch.int32), num_experts=4)
     with pytest.raises(ValueError, match="needs max_tokens_per_rank"):
         ep.forward_sorted(torch.zeros(8, 4), ok, None)
+
+
+def test_reference_import_lines_resolve_to_this_package():
+    """The reference's own import lines, verbatim, in a fresh interpreter with only this
+    repository on the path: they must resolve to the classes of complexity_deep_b200."""
+    import subprocess
+    import sys
+    from conftest import ROOT
+    code = """
+from complexity_deep import (RMSNorm, RotaryEmbedding, ComplexityAttention, SwiGLU,
+                             TokenRoutedMLP, TransformerBlock, MuGuidance)
+from complexity_deep import ComplexityConfig, ComplexityModel, create_complexity_model, count_parameters
+from complexity_deep.models import (ComplexityConfig, ComplexityModel, CausalLMOutput, ModelOutput,
+                                    create_complexity_model, count_parameters)
+from complexity_deep.core import (RMSNorm, RotaryEmbedding, apply_rotary_pos_emb, ComplexityAttention,
+                                  SwiGLU, TokenRoutedMLP, TransformerBlock, MuGuidance)
+from complexity_deep.core.token_routed_mlp import TokenRoutedMLP as T2
+from complexity_deep.core.layer import TransformerBlock as B2, MuGuidance as M2
+from complexity_deep.core.attention import ComplexityAttention as A2
+from complexity_deep.core.normalization import RMSNorm as N2
+from complexity_deep.models.modeling import ComplexityModel as CM2
+from complexity_deep.models.config import ComplexityConfig as CC2
+import complexity_deep, complexity_deep_b200 as impl
+assert TokenRoutedMLP is impl.TokenRoutedMLP is T2 and ComplexityModel is impl.ComplexityModel is CM2
+assert TransformerBlock is B2 and MuGuidance is M2 and ComplexityAttention is A2 and RMSNorm is N2
+assert ComplexityConfig is CC2 and complexity_deep.__version__ == "1.0.0"
+m = create_complexity_model("tiny", vocab_size=64, num_hidden_layers=1)
+assert type(m).__module__ == "complexity_deep_b200.models.modeling"
+print("ok")
+"""
+    proc = subprocess.run([sys.executable, "-c", code], cwd=ROOT, capture_output=True, text=True,
+                          env={**__import__("os").environ, "PYTHONPATH": ROOT})
+    assert proc.returncode == 0 and proc.stdout.strip() == "ok", proc.stderr
