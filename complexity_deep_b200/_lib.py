@@ -42,6 +42,9 @@ SIGNATURES = {
                                     c_longlong, c_longlong, c_void_p, c_longlong, c_float, c_int,
                                     c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                     c_size_t, c_void_p]),
+    "cd_attention_prefill_supported": (c_int, [c_int, c_int, c_int, c_int, c_int]),
+    "cd_attention_prefill": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                                     c_void_p]),
     "cd_gate_up_packed_rows": (c_int, [c_int, c_int]),
     "cd_moe_up": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
                           c_int, c_void_p]),

@@ -12,7 +12,7 @@ import sys
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libcdeep.so")
-SOURCES = ["api.cu", "gemm.cu", "route.cu", "rowwise.cu", "attention_decode.cu", "pack.cu"]
+SOURCES = ["api.cu", "gemm.cu", "route.cu", "rowwise.cu", "attention_decode.cu", "attention_prefill.cu", "pack.cu"]
 HEADERS = ["ptx.cuh", "gemm_sm100.cuh", "kernels.h", os.path.join("..", "..", "include", "cdeep.h")]
 
 

@@ -18,6 +18,7 @@ What changes is how q, k, v are produced:
 """
 from __future__ import annotations
 
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -27,6 +28,11 @@ import torch.nn.functional as F
 from .. import ops
 from ._cache import DerivedCache
 from .rotary import RotaryEmbedding
+
+
+# CDEEP_PREFILL_ATTENTION=sdpa sends prompts through torch's scaled_dot_product_attention instead
+# of cd_attention_prefill (comparison / debugging aid)
+_PREFILL_KERNEL = os.environ.get("CDEEP_PREFILL_ATTENTION", "kernel") != "sdpa"
 
 
 class _KVBuffer:
@@ -210,6 +216,11 @@ class ComplexityAttention(nn.Module):
                 kk, vv, mask = k, v, attention_mask
             return ops.decode_attention(qkv, kk, vv, mask, hq, hkv, D), new_kv
 
+        if self._prefill_kernel_applies(B, S, attention_mask, past_key_value):
+            # a prompt with nothing cached and no mask: causal attention on the library's
+            # tcgen05 kernel, reading q / k / v in place from the projection buffer
+            return ops.attention_prefill(qkv, B, S, hq, hkv, D), new_kv
+
         with ops._Span("sdpa", kernels=0):  # PyTorch operator, timed for the breakdown only
             attn = F.scaled_dot_product_attention(
                 q, k, v,
@@ -240,6 +251,14 @@ class ComplexityAttention(nn.Module):
                                hq, hkv, D, past.k, past.v, cache.state[0:1])
         return ops.decode_attention(qkv, past.k, past.v, None, hq, hkv, D,
                                     kv_len_dev=cache.state[1:2])
+
+    def _prefill_kernel_applies(self, B, S, attention_mask, past_key_value) -> bool:
+        if attention_mask is not None or past_key_value is not None or not _PREFILL_KERNEL:
+            return False
+        if self.training and self.attention_dropout > 0:
+            return False
+        return ops.attention_prefill_supported(B, S, self.num_heads, self.num_kv_heads,
+                                               self.head_dim)
 
     def _decode_kernel_applies(self, S, attention_mask, k, v) -> bool:
         if S != 1 or self.head_dim not in (64, 128) or self.num_kv_groups > 4:

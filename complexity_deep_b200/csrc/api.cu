@@ -174,6 +174,25 @@ int cd_decode_attention(const void* q, long long q_stride_b, const void* k, cons
   return e == cudaSuccess ? CD_OK : cuda_fail(e, "decode attention launch");
 }
 
+int cd_attention_prefill_supported(int B, int S, int hq, int hkv, int D) {
+  if (B < 1 || S < 1 || hq < 1 || hkv < 1 || hq % hkv) return 0;
+  if (D != 64 && D != 128) return 0;
+  if (hq > 65535 || B > 65535) return 0;                         // grid dimensions y / z
+  if (static_cast<long long>(B) * S > 0x7fffffffLL - 256) return 0;   // token rows are 32-bit TMA coordinates
+  return 1;
+}
+
+int cd_attention_prefill(const void* qkv, void* out, int B, int S, int hq, int hkv, int D,
+                         float scale, void* stream) {
+  if (!cd_attention_prefill_supported(B, S, hq, hkv, D)) return CD_ERR_UNSUPPORTED;
+  if (!qkv || !out || !aligned16(qkv) || !aligned16(out) || !(scale > 0.f)) return CD_ERR_INVALID;
+  int* status = device_status_word();
+  if (!status) return CD_ERR_CUDA;
+  cudaError_t e = launch_attention_prefill(qkv, out, B, S, hq, hkv, D, scale, status,
+                                           as_stream(stream));
+  return e == cudaSuccess ? CD_OK : cuda_fail(e, "prefill attention launch");
+}
+
 int cd_gate_up_packed_rows(int I, int block_n) {
   if (I < 1 || (block_n != 32 && block_n != 64 && block_n != 128 && block_n != 256)) return 0;
   const int half = block_n / 2;

@@ -169,6 +169,11 @@ int choose_cta_group(int M, int block_n, int sm_count) {
 
 }  // namespace
 
+bool encode_map_2d(void* map_out, const void* base, long long rows, long long cols, long long ld,
+                   int box_rows) {
+  return make_map(static_cast<CUtensorMap*>(map_out), base, rows, cols, ld, box_rows);
+}
+
 static DeviceInfo* device_info(int* status_out) {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);

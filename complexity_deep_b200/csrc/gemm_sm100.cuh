@@ -511,7 +511,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
         // `out_lo` (64 bytes per row and destination)
         __nv_bfloat16* base = (kSplit && cchunk >= 4) ? p.out_lo : out_base;
         const int col = col0 + (kSplit ? (cchunk & 3) : cchunk) * 8;
-        if (col < col_end && base != nullptr) {
+        if (col < col_end && (use_ptrs || base != nullptr)) {
 #pragma unroll
           for (int it = 0; it < 8; ++it) {
             if ((cvalid >> it) & 1u) {

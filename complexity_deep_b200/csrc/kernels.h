@@ -60,6 +60,15 @@ cudaError_t launch_qk_norm_rope(void* qkv, const void* q_w, const void* k_w, con
                                 long long kv_stride_b = 0, long long kv_stride_h = 0,
                                 long long kv_stride_t = 0, int capacity = 0);
 
+// Encodes a CUtensorMap (passed as void*) for a 2-D bf16 tensor [rows, cols] with `ld` elements
+// between rows, boxes of [box_rows, 64 columns], 128-byte swizzle, zero fill out of bounds.
+bool encode_map_2d(void* map_out, const void* base, long long rows, long long cols, long long ld,
+                   int box_rows);
+
+// causal prefill attention over the fused projection buffer (attention_prefill.cu)
+cudaError_t launch_attention_prefill(const void* qkv, void* out, int B, int S, int hq, int hkv, int D,
+                                     float scale, int* status, cudaStream_t stream);
+
 // weight layout transforms (pack.cu)
 cudaError_t launch_pack_gate_up(const void* gate, const void* up, void* packed, int G, int I, int H,
                                 int block_n, int feature_major, cudaStream_t stream);

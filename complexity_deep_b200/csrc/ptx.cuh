@@ -193,6 +193,47 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+// Each lane of the warp writes 16 / 32 consecutive 32-bit columns of its own TMEM lane.
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      :
+      : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+        "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]),
+        "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      :
+      : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+        "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]),
+        "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
+        "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+        "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem desc]: the A operand is read from tensor memory (lane = row,
+// every 32-bit column holds two consecutive bf16 elements of K), issued by ONE thread.
+__device__ __forceinline__ void umma_bf16_tmem_a(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b,
+                                                 uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      "}\n"
+      :
+      : "r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 
 // ---------------------------------------------------------------- CTA pairs (cta_group::2)
 // Two CTAs of a cluster of 2 act as one 256-row tile: the even CTA (the leader) issues the
@@ -279,11 +320,28 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr) {
   return d;
 }
 
-// Instruction descriptor for kind::f16 with bf16 A and B (both K-major), fp32 D.
-__host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n) {
+// Shared-memory matrix descriptor for an MN-major bf16 operand written by TMA with the
+// 128-byte swizzle as boxes of [K rows, 64 elements of N] (128 bytes per row): 64 elements of
+// N are contiguous, 8 rows of K form one 1024-byte swizzle atom (stride byte offset = distance
+// between 8-row groups = 1024), the next 64 elements of N live `n_chunk_bytes` further (leading
+// byte offset = the size of one box).
+__device__ __forceinline__ uint64_t make_smem_desc_mn_sw128(uint32_t smem_addr, uint32_t n_chunk_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3ffffu) >> 4);       // start address
+  d |= static_cast<uint64_t>((n_chunk_bytes >> 4) & 0x3fffu) << 16;   // leading byte offset >> 4
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;                   // stride byte offset >> 4
+  d |= static_cast<uint64_t>(1) << 46;                           // descriptor version
+  d |= static_cast<uint64_t>(2) << 61;                           // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor for kind::f16 with bf16 A and B, fp32 D.  A is K-major; B is K-major
+// unless b_mn_major (then N is the contiguous dimension of B in shared memory).
+__host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n, bool b_mn_major = false) {
   return (1u << 4)                               // D format: f32
          | (1u << 7)                             // A format: bf16
          | (1u << 10)                            // B format: bf16
+         | (b_mn_major ? (1u << 16) : 0u)        // B major-ness
          | (static_cast<uint32_t>(n >> 3) << 17) // N / 8
          | (static_cast<uint32_t>(m >> 4) << 24);// M / 16
 }

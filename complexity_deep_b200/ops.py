@@ -300,6 +300,26 @@ def decode_attention(qkv: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
     return out
 
 
+def attention_prefill_supported(B: int, S: int, hq: int, hkv: int, head_dim: int) -> bool:
+    return bool(_lib.load().cd_attention_prefill_supported(B, S, hq, hkv, head_dim))
+
+
+def attention_prefill(qkv: torch.Tensor, batch: int, seq_len: int, hq: int, hkv: int,
+                      head_dim: int) -> torch.Tensor:
+    """Causal self-attention of a prompt: qkv [B * S, (hq + 2 hkv) * D] (after Q/K norm + RoPE)
+    -> [B * S, hq * D]; softmax scale D ** -0.5 as scaled_dot_product_attention's default."""
+    lib = _lib.load()
+    _need(qkv, "qkv")
+    if tuple(qkv.shape) != (batch * seq_len, (hq + 2 * hkv) * head_dim):
+        raise RuntimeError("qkv shape does not match batch / sequence / head layout")
+    out = torch.empty(batch * seq_len, hq * head_dim, dtype=BF16, device=qkv.device)
+    with _Span("attention_prefill"):
+        _lib.check(lib.cd_attention_prefill(qkv.data_ptr(), out.data_ptr(), batch, seq_len, hq, hkv,
+                                            head_dim, float(head_dim) ** -0.5, _stream()),
+                   "cd_attention_prefill")
+    return out
+
+
 # --------------------------------------------------------------------------- weights
 def choose_block_n(width: int, rows: Optional[int] = None, groups: int = 1,
                    sm_count: Optional[int] = None) -> int:

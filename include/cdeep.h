@@ -162,6 +162,22 @@ int cd_decode_attention(const void* q, long long q_stride_b, const void* k, cons
                         int hkv, int L, const int32_t* kv_len_dev, int D, void* out, void* ws,
                         size_t ws_bytes, void* stream);
 
+/* ---- causal self-attention over a prompt (prefill) --------------------------------------------
+ * Replaces, for a prompt without cached keys and without an additive mask,
+ * complexity_deep/core/attention.py:163-177 (repeat_interleave of the KV heads +
+ * scaled_dot_product_attention(is_causal=True)); the reference's Triton analogue is
+ * complexity_deep/cuda/fused_attention.py:121-233.
+ *   out[b*S + s, h*D : (h+1)*D] = softmax_{t <= s}(scale * q[b,s,h] . k[b,t,h/G]) v[b,t,h/G],  G = hq / hkv
+ * qkv: [B * S, (hq + 2*hkv) * D] — the fused projection buffer after Q/K norm + RoPE (q heads,
+ * then k heads, then v heads along a row); q, k, v are read in place from its column slices and
+ * grouped KV heads are never copied.  out: [B * S, hq * D] (the operand of o_proj).  Any S
+ * (ragged last tiles are masked); D is 64 or 128; hq % hkv == 0.  QK^T and PV run on tcgen05
+ * with the scores, probabilities and the output accumulator in tensor memory.
+ * cd_attention_prefill_supported returns 1 for shapes the kernel takes. */
+int cd_attention_prefill_supported(int B, int S, int hq, int hkv, int D);
+int cd_attention_prefill(const void* qkv, void* out, int B, int S, int hq, int hkv, int D,
+                         float scale, void* stream);
+
 /* ---- expert up-projection with fused SwiGLU ---------------------------------------------
  * Replaces gate/up GEMMs and silu(gate)*up of the routed experts
  * (token_routed_mlp.py:171-173) or, with num_groups = 1 and seg_offsets = NULL, of the
