@@ -108,9 +108,12 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnP
   const int head = blockIdx.y;
   const int batch = blockIdx.z;
   const int kv_head = head / (p.hq / p.hkv);
-  const int qt[2] = {2 * pair, 2 * pair + 1};
-  const int n_kv[2] = {qt[0] + 1, qt[1] < p.q_tiles ? qt[1] + 1 : 0};   // KV tiles of A and B
-  const int n_max = n_kv[1] > n_kv[0] ? n_kv[1] : n_kv[0];
+  // query tiles 2 * pair (A) and 2 * pair + 1 (B); tile t sees KV tiles 0 .. t
+  const int n_kv_a = 2 * pair + 1;
+  const int n_kv_b = (2 * pair + 1 < p.q_tiles) ? 2 * pair + 2 : 0;     // 0: B does not exist
+  auto qt_of = [&](int x) { return 2 * pair + x; };
+  auto n_kv_of = [&](int x) { return x ? n_kv_b : n_kv_a; };
+  const int n_max = n_kv_b > n_kv_a ? n_kv_b : n_kv_a;
   const int row0 = batch * p.S;                       // first token row of this sequence
   const int q_col = head * D;
   const int k_col = (p.hq + kv_head) * D;
@@ -144,12 +147,12 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnP
   if (warp == 8) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      const int q_tiles_here = n_kv[1] > 0 ? 2 : 1;
+      const int q_tiles_here = n_kv_b > 0 ? 2 : 1;
       mbar_arrive_expect_tx(q_full, q_tiles_here * L::kTileBytes);
       for (int x = 0; x < q_tiles_here; ++x)
         for (int d = 0; d < kDBlocks; ++d)
           tma_load_2d(smem + L::kQOff + x * L::kTileBytes + d * L::kBoxBytes, &tm_qkv, q_full,
-                      q_col + d * 64, row0 + qt[x] * kQTile);
+                      q_col + d * 64, row0 + qt_of(x) * kQTile);
       bool ok = true;
       for (int j = 0; j < n_max && ok; ++j) {
         const int s = j & 1;
@@ -207,33 +210,33 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnP
       if (ok) {
         tc_fence_after();
         issue_s(0, 0);
-        if (n_kv[1] > 0) issue_s(1, 0);
+        if (n_kv_b > 0) issue_s(1, 0);
         umma_commit(&k_empty[0]);   // K_0 is free once both first products have read it
       }
       for (int j = 0; j < n_max && ok; ++j) {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1u;
         for (int x = 0; x < 2 && ok; ++x) {
-          if (j >= n_kv[x]) continue;
-          const bool last_user = (x == 1) || (j >= n_kv[1]);   // of K_j / V_j among the two tiles
+          if (j >= n_kv_of(x)) continue;
+          const bool last_user = (x == 1) || (j >= n_kv_b);   // of K_j / V_j among the two tiles
           if (!mbar_wait(&p_full[x], j & 1u, abort_flag, wait_limit)) { ok = false; break; }
-          if (x == 0 || j >= n_kv[0]) {   // first PV of this KV tile: V_j must have landed
+          if (x == 0 || j >= n_kv_a) {   // first PV of this KV tile: V_j must have landed
             if (!mbar_wait(&v_full[s], ph, abort_flag, wait_limit)) { ok = false; break; }
           }
           tc_fence_after();
           issue_pv(x, j);
           if (last_user) umma_commit(&v_empty[s]);
           umma_commit(&o_done[x]);
-          if (j + 1 < n_kv[x]) {
+          if (j + 1 < n_kv_of(x)) {
             const int s1 = (j + 1) & 1;
             const uint32_t ph1 = ((j + 1) >> 1) & 1u;
-            if (x == 0 || j + 1 >= n_kv[0]) {   // first S of the next KV tile: K_{j+1} must have landed
+            if (x == 0 || j + 1 >= n_kv_a) {   // first S of the next KV tile: K_{j+1} must have landed
               if (!mbar_wait(&k_full[s1], ph1, abort_flag, wait_limit)) { ok = false; break; }
               tc_fence_after();
             }
             issue_s(x, j + 1);
             // K_{j+1} is free once the last tile that uses it has issued its S
-            if (x == 1 || j + 1 >= n_kv[1]) umma_commit(&k_empty[s1]);
+            if (x == 1 || j + 1 >= n_kv_b) umma_commit(&k_empty[s1]);
           }
         }
       }
@@ -243,8 +246,8 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnP
     // ---------------------------------------------------------------- softmax warps
     const int x = warp >> 2;                 // query tile of this warp group
     const int quarter = warp & 3;            // TMEM lane quarter this warp may access
-    const int n_mine = n_kv[x];
-    const int q_pos = qt[x] * kQTile + quarter * 32 + lane;     // position of this thread's row
+    const int n_mine = n_kv_of(x);
+    const int q_pos = qt_of(x) * kQTile + quarter * 32 + lane;     // position of this thread's row
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t s_tmem = tmem_base + lane_addr + s_col(x);
     const uint32_t o_tmem = tmem_base + lane_addr + o_col(x);
@@ -256,20 +259,35 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnP
       tc_fence_after();
       const bool diagonal = (j == n_mine - 1);
       const int k_pos0 = j * kKvTile;
-      // pass 1: row maximum
+      // keys of this tile the row may see: all 128, fewer on the diagonal tile (causal)
+      const int n_vis = diagonal ? min(kKvTile, max(q_pos - k_pos0 + 1, 0)) : kKvTile;
+      // pass 1: row maximum.  The load of chunk c + 1 is in flight while chunk c is reduced.
       float m_tile = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(s_tmem + c * 32, v);
-        tmem_ld_wait();
-        if (diagonal) {
+      {
+        uint32_t va[32], vb[32];
+        tmem_ld32(s_tmem, va);
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (k_pos0 + c * 32 + i <= q_pos) m_tile = fmaxf(m_tile, __uint_as_float(v[i]));
-        } else {
+        for (int c = 0; c < 4; ++c) {
+          uint32_t (&cur)[32] = (c & 1) ? vb : va;
+          uint32_t (&nxt)[32] = (c & 1) ? va : vb;
+          tmem_ld_wait();
+          if (c < 3) tmem_ld32(s_tmem + (c + 1) * 32, nxt);
+          if (!diagonal) {
+            float m0 = __uint_as_float(cur[0]), m1 = __uint_as_float(cur[1]);
+            float m2 = __uint_as_float(cur[2]), m3 = __uint_as_float(cur[3]);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) m_tile = fmaxf(m_tile, __uint_as_float(v[i]));
+            for (int i = 4; i < 32; i += 4) {
+              m0 = fmaxf(m0, __uint_as_float(cur[i]));
+              m1 = fmaxf(m1, __uint_as_float(cur[i + 1]));
+              m2 = fmaxf(m2, __uint_as_float(cur[i + 2]));
+              m3 = fmaxf(m3, __uint_as_float(cur[i + 3]));
+            }
+            m_tile = fmaxf(m_tile, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (c * 32 + i < n_vis) m_tile = fmaxf(m_tile, __uint_as_float(cur[i]));
+          }
         }
       }
       const float m_new = fmaxf(m_ref, m_tile);
@@ -293,27 +311,35 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnP
       }
       if (grow) m_ref = m_new;
       // pass 2: exponentials, row sum, P (bf16, two per column) into the first 64 columns of S
+      // (chunk c's probabilities land on columns whose scores were consumed with chunk c / 2)
       const float m_scaled = m_ref * p.scale_log2;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(s_tmem + c * 32, v);
-        tmem_ld_wait();
-        uint32_t pk[16];
+      {
+        uint32_t va[32], vb[32];
+        float l0 = 0.f, l1 = 0.f;
+        tmem_ld32(s_tmem, va);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float e0 = fast_exp2(fmaf(__uint_as_float(v[2 * i]), p.scale_log2, -m_scaled));
-          float e1 = fast_exp2(fmaf(__uint_as_float(v[2 * i + 1]), p.scale_log2, -m_scaled));
-          if (diagonal) {
-            if (k_pos0 + c * 32 + 2 * i > q_pos) e0 = 0.f;
-            if (k_pos0 + c * 32 + 2 * i + 1 > q_pos) e1 = 0.f;
+        for (int c = 0; c < 4; ++c) {
+          uint32_t (&cur)[32] = (c & 1) ? vb : va;
+          uint32_t (&nxt)[32] = (c & 1) ? va : vb;
+          tmem_ld_wait();
+          if (c < 3) tmem_ld32(s_tmem + (c + 1) * 32, nxt);
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            float e0 = fast_exp2(fmaf(__uint_as_float(cur[2 * i]), p.scale_log2, -m_scaled));
+            float e1 = fast_exp2(fmaf(__uint_as_float(cur[2 * i + 1]), p.scale_log2, -m_scaled));
+            if (diagonal) {
+              if (c * 32 + 2 * i >= n_vis) e0 = 0.f;
+              if (c * 32 + 2 * i + 1 >= n_vis) e1 = 0.f;
+            }
+            l0 += e0;
+            l1 += e1;
+            const __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
+            pk[i] = *reinterpret_cast<const uint32_t*>(&b2);
           }
-          const __nv_bfloat162 b = __floats2bfloat162_rn(e0, e1);
-          pk[i] = *reinterpret_cast<const uint32_t*>(&b);
-          // the row sum uses the rounded values the tensor cores will see
-          l_sum += __bfloat162float(b.x) + __bfloat162float(b.y);
+          tmem_st16(s_tmem + c * 16, pk);
         }
-        tmem_st16(s_tmem + c * 16, pk);
+        l_sum += l0 + l1;
       }
       tmem_st_wait();
       tc_fence_before();
