@@ -24,7 +24,7 @@ namespace cdeep {
 namespace {
 
 constexpr int kAttnThreads = 128;
-constexpr int kMaxGroup = 8;    // query heads per KV head handled by one block
+constexpr int kMaxGroup = 4;    // query heads per KV head handled by one block (the entry point refuses more)
 constexpr int kLanesPerRow = 8;
 
 __device__ __forceinline__ float lo_f(uint32_t v) { return __uint_as_float(v << 16); }
@@ -32,9 +32,12 @@ __device__ __forceinline__ float hi_f(uint32_t v) { return __uint_as_float(v & 0
 
 // Blocks per (batch, kv head) pair.  Also evaluated on the device when the cache length is
 // read from device memory, so both forms split (and therefore round) identically.
+// kTargetBlocks is a tuning constant (16 blocks for each of a B200's 148 SMs), not a limit: any
+// other SM count only changes how many blocks share the work.
+constexpr int kTargetBlocks = 16 * 148;
 __host__ __device__ inline int choose_splits(int B, int hkv, int L) {
   const int pairs = B * hkv;
-  int splits = (16 * 148 + pairs - 1) / pairs;      // several waves of blocks: small tail
+  int splits = (kTargetBlocks + pairs - 1) / pairs;   // several waves of blocks: small tail
   // at least 512 rows per block (measured against 128 and 256: 10-15 % faster for short
   // caches and few sequences, equal elsewhere)
   const int max_splits = (L + 511) / 512;

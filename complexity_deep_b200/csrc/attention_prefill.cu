@@ -184,13 +184,16 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnP
       // S_j = Q K_j^T into score buffer j & 1: D / 16 MMAs, Q from TMEM (8 columns per step of
       // 16 elements), K_j from the 64-column boxes of its stage
       auto issue_s = [&](int j) {
-        const uint32_t ka = k_addr + (j % kKvStages) * L::kTileBytes;
+        // one descriptor per burst; a step of 16 elements along K is +2 (units of 16 bytes) inside
+        // a 64-column box, the next box is kBoxBytes further (the address field cannot overflow:
+        // shared-memory addresses stay below 256 KB)
+        const uint64_t db0 = make_smem_desc_sw128(k_addr + (j % kKvStages) * L::kTileBytes);
         const uint32_t d_tmem = tmem_base + kSCol0 + (j & 1) * 128;
+        const uint32_t a_tmem = tmem_base + kQCol;
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint64_t db = make_smem_desc_sw128(ka + (k >> 2) * L::kBoxBytes) + 2u * (k & 3);
-          umma_bf16_tmem_a(d_tmem, tmem_base + kQCol + 8u * k, db, idesc_s, k != 0 ? 1u : 0u);
-        }
+        for (int k = 0; k < D / 16; ++k)
+          umma_bf16_tmem_a(d_tmem, a_tmem + 8u * k, db0 + ((k >> 2) * (L::kBoxBytes >> 4) + 2u * (k & 3)),
+                           idesc_s, k != 0 ? 1u : 0u);
         umma_commit(&s_full[j & 1]);
         umma_commit(&k_empty[j % kKvStages]);   // K_j is free once these products have read it
       };
@@ -198,14 +201,14 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnP
       // 0-63) and 64-95 (keys 64-127) of its score buffer, the V tile is read N-major: 16 key
       // rows = 2048 bytes further per step
       auto issue_pv = [&](int j) {
-        const uint32_t va = v_addr + (j % kKvStages) * L::kTileBytes;
+        const uint64_t db0 = make_smem_desc_mn_sw128(v_addr + (j % kKvStages) * L::kTileBytes, L::kBoxBytes);
         const uint32_t p_tmem = tmem_base + kSCol0 + (j & 1) * 128;
+        const uint32_t o_acc = tmem_base + kOCol;
+        const uint32_t first = j != 0 ? 1u : 0u;
 #pragma unroll
-        for (int k = 0; k < kKvTile / 16; ++k) {
-          const uint64_t db = make_smem_desc_mn_sw128(va + k * 2048, L::kBoxBytes);
-          umma_bf16_tmem_a(tmem_base + kOCol, p_tmem + (k < 4 ? 8u * k : 32u + 8u * k), db, idesc_o,
-                           (j | k) != 0 ? 1u : 0u);
-        }
+        for (int k = 0; k < kKvTile / 16; ++k)
+          umma_bf16_tmem_a(o_acc, p_tmem + (k < 4 ? 8u * k : 32u + 8u * k), db0 + k * (2048u >> 4), idesc_o,
+                           k != 0 ? 1u : first);
         umma_commit(&v_empty[j % kKvStages]);
         umma_commit(o_done);
       };

@@ -64,6 +64,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking test of a phase (a few cycles when the phase has completed; try_wait, which may
+// suspend the thread, costs ~175 cycles on B200 even then).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred P;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Longest time any single pipeline wait may take before the kernel gives up (ns).
 // A healthy wait is a few microseconds; this only ends a broken pipeline.
 constexpr uint64_t kWaitLimitNs = 2000ull * 1000ull * 1000ull;
@@ -78,6 +94,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
   // slow to read, and a read on every short wait put its latency on the critical path of
   // pipelines that wait once per k-block (few-row GEMMs).  The limit therefore counts from
   // the first read.
+  // fast path: in a pipeline that runs ahead most waits find their phase already complete
+  if (mbar_test_wait(bar, parity)) return true;
   uint64_t t0 = 0;
   uint32_t spins = 0;
   while (true) {
