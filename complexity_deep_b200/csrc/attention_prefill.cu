@@ -9,26 +9,23 @@
 // slices of the fused projection buffer [T, (hq + 2 hkv) * D] (token-major, T = B * S) and
 // the result is written as [T, hq * D], the operand layout of o_proj.
 //
-// Work decomposition: one CTA per (sequence, query head, 128-row query tile), heavy tiles (late
-// rows, which see the most keys) first.
+// Work decomposition: one CTA per (sequence, query head, pair of 128-row query tiles).  The
+// two query tiles A and B of a CTA share the K / V tiles in shared memory and take turns on
+// the tensor pipe: while the softmax warps of A work on their 128 x 128 scores, the MMA warp
+// issues B's products, and vice versa.
 //
-//   warp  0     TMA producer (the K / V ring, 3 stages each)
-//   warp  1     MMA issuer + TMEM owner
-//   warps 2-9   softmax: two threads per query row (= TMEM lane), 64 score columns each
+//   warps 0-3   softmax of tile A (a thread owns one query row = one TMEM lane)
+//   warps 4-7   softmax of tile B
+//   warp  8     TMA producer (Q once, then the K / V ring)
+//   warp  9     MMA issuer + TMEM owner
 //
-// Both products take their A operand from tensor memory, so the tensor cores read only ONE
-// operand per instruction from shared memory (a 128 x 128 x 16 product fed from shared memory
-// on both sides needs the full 128 bytes per clock of the SM and measured at half rate here):
-//   * Q (bf16, two elements per column) is written to TMEM once per CTA by the softmax threads;
-//   * S_j = Q K_j^T goes to one of TWO score buffers, so the product for tile j + 1 runs while
-//     the softmax warps work on tile j;
-//   * softmax warps: row max, p = exp2(scale * (s - m)), row sum; P (bf16) overwrites the first
-//     columns of the thread's own score columns;
-//   * O += P_j V_j with P from TMEM and the V tile read N-major from shared memory.
-// The softmax of tile j + 1 does not wait for O: the running maximum m is only raised when it
-// grew by more than 2^8 in the exp2 domain (then O and the row sum are rescaled in TMEM, after
-// the pending product has finished); otherwise the stale maximum is kept, which is exact as long
-// as the final division uses the matching row sum.
+// Per KV tile j and query tile X:  S_X = Q_X K_j^T  (accumulator in TMEM, 128 columns)
+//   -> softmax warps: row max, p = exp2(scale * (s - m)), row sum; P (bf16) is written back
+//      into the first 64 columns of S_X
+//   -> O_X += P_X V_j  (A operand = P from TMEM, B operand = the V tile, N-major)
+// The running maximum m is only raised when it grew by more than 2^8 in the exp2 domain
+// (then O and the row sum are rescaled in TMEM); otherwise the stale maximum is kept, which
+// is exact as long as the final division uses the matching row sum.
 #include <cstdint>
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -43,21 +40,14 @@ namespace {
 
 constexpr int kQTile = 128;      // query rows per tile = TMEM lanes
 constexpr int kKvTile = 128;     // keys per tile
-constexpr int kSoftmaxWarps = 8;
-constexpr int kProducerWarp = 0;   // the two single-thread roles come first: lower warp ids are
-constexpr int kMmaWarp = 1;        // favoured by the warp scheduler over the eight softmax warps
-constexpr int kFirstSoftmaxWarp = 2;
 constexpr int kAttnThreads = 320;
-constexpr int kKvStages = 3;
 constexpr float kRescaleThreshold = 8.0f;   // log2 of the growth of the maximum that forces a rescale
 
 struct AttnParams {
-  const __nv_bfloat16* qkv;   // [T, ld]
-  int ld;
-  long long T;      // B * S rows
   int S;            // sequence length
   int hq, hkv;      // query / kv heads
   int q_tiles;      // ceil(S / 128)
+  int pairs;        // ceil(q_tiles / 2)
   float scale_log2; // softmax scale * log2(e)
   __nv_bfloat16* out;   // [T, hq * D]
   int ldo;
@@ -68,14 +58,14 @@ struct AttnParams {
 template <int D>
 struct AttnSmem {
   static constexpr int kBoxBytes = 128 * 64 * 2;           // one TMA box: 128 rows x 64 columns
-  static constexpr int kTileBytes = (D / 64) * kBoxBytes;  // a K or V tile
-  static constexpr int kKOff = 0;                          // K ring
-  static constexpr int kVOff = kKvStages * kTileBytes;     // V ring
-  static constexpr int kBarOff = 2 * kKvStages * kTileBytes;
-  static constexpr int kNumBars = 1 + 4 * kKvStages + 5;   // q_ready, k/v full/empty, s_full x2, p_full x2, o_done
+  static constexpr int kTileBytes = (D / 64) * kBoxBytes;  // a Q, K or V tile
+  static constexpr int kQOff = 0;                          // Q_A, Q_B
+  static constexpr int kKOff = 2 * kTileBytes;             // K ring (2 stages)
+  static constexpr int kVOff = 4 * kTileBytes;             // V ring (2 stages)
+  static constexpr int kBarOff = 6 * kTileBytes;
+  static constexpr int kNumBars = 1 + 8 + 6;               // q_full, k/v full/empty x2, s_full/p_full/o_done x2
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
-  static constexpr int kXchOff = kMiscOff + 16;            // exchange between the two threads of a row:
-  static constexpr int kTotal = kXchOff + 128 * 6 * 4;     // 128 rows x 6 floats
+  static constexpr int kTotal = kMiscOff + 16;
   static constexpr int kDynamic = kTotal + 1024;
 };
 
@@ -90,23 +80,22 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
 attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnParams p) {
   using L = AttnSmem<D>;
   constexpr int kDBlocks = D / 64;                 // 64-column boxes per tile
-  constexpr uint32_t kTmemCols = 512;
-  constexpr uint32_t kQCol = 0;                    // Q: D / 2 columns (two bf16 per column)
-  constexpr uint32_t kSCol0 = 64;                  // two score buffers of 128 columns
-  constexpr uint32_t kOCol = 320;                  // O: D columns
+  constexpr uint32_t kTmemCols = 512;   // S_A, S_B (128 columns each), O_A, O_B (D each)
+  auto s_col = [](int x) { return static_cast<uint32_t>(x * 128); };
+  auto o_col = [](int x) { return static_cast<uint32_t>(256 + x * D); };
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
-  uint64_t* q_ready = bars;                       // [1]
-  uint64_t* k_full = bars + 1;                    // [kKvStages]
-  uint64_t* k_empty = k_full + kKvStages;
-  uint64_t* v_full = k_empty + kKvStages;
-  uint64_t* v_empty = v_full + kKvStages;
-  uint64_t* s_full = v_empty + kKvStages;         // [2] per score buffer
-  uint64_t* p_full = s_full + 2;                  // [2]
-  uint64_t* o_done = p_full + 2;                  // [1]
+  uint64_t* q_full = bars;            // [1]
+  uint64_t* k_full = bars + 1;        // [2]
+  uint64_t* k_empty = bars + 3;       // [2]
+  uint64_t* v_full = bars + 5;        // [2]
+  uint64_t* v_empty = bars + 7;       // [2]
+  uint64_t* s_full = bars + 9;        // [2] per query tile
+  uint64_t* p_full = bars + 11;       // [2]
+  uint64_t* o_done = bars + 13;       // [2]
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(smem + L::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kMiscOff + 4);
 
@@ -114,34 +103,37 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnP
   const int lane = threadIdx.x & 31;
   const uint64_t wait_limit = p.wait_limit_ns ? p.wait_limit_ns : kWaitLimitNs;
 
-  // work item: heavy tiles (late rows of the sequence see the most keys) are scheduled first
-  const int qt = p.q_tiles - 1 - static_cast<int>(blockIdx.x);
+  // work item: heavy pairs (late rows of the sequence see the most keys) are scheduled first
+  const int pair = p.pairs - 1 - static_cast<int>(blockIdx.x);
   const int head = blockIdx.y;
   const int batch = blockIdx.z;
   const int kv_head = head / (p.hq / p.hkv);
-  const int n_kv = qt + 1;                            // tile qt sees KV tiles 0 .. qt
-  const long long row0 = static_cast<long long>(batch) * p.S;   // first token row of this sequence
+  // query tiles 2 * pair (A) and 2 * pair + 1 (B); tile t sees KV tiles 0 .. t
+  const int n_kv_a = 2 * pair + 1;
+  const int n_kv_b = (2 * pair + 1 < p.q_tiles) ? 2 * pair + 2 : 0;     // 0: B does not exist
+  auto qt_of = [&](int x) { return 2 * pair + x; };
+  auto n_kv_of = [&](int x) { return x ? n_kv_b : n_kv_a; };
+  const int n_max = n_kv_b > n_kv_a ? n_kv_b : n_kv_a;
+  const int row0 = batch * p.S;                       // first token row of this sequence
   const int q_col = head * D;
   const int k_col = (p.hq + kv_head) * D;
   const int v_col = (p.hq + p.hkv + kv_head) * D;
 
-  if (warp == kProducerWarp && lane == 0) {
-    mbar_init(q_ready, kSoftmaxWarps);
-    for (int s = 0; s < kKvStages; ++s) {
+  if (warp == 8 && lane == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
       mbar_init(&k_full[s], 1);
       mbar_init(&k_empty[s], 1);
       mbar_init(&v_full[s], 1);
       mbar_init(&v_empty[s], 1);
+      mbar_init(&s_full[s], 1);
+      mbar_init(&p_full[s], 4);     // one arrival per softmax warp of the tile
+      mbar_init(&o_done[s], 1);
     }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(&s_full[b], 1);
-      mbar_init(&p_full[b], kSoftmaxWarps);     // one arrival per softmax warp
-    }
-    mbar_init(o_done, 1);
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tm_qkv);
-  } else if (warp == kMmaWarp) {
+  } else if (warp == 9) {
     tmem_alloc(tmem_base_slot, kTmemCols);
     tmem_relinquish();
   }
@@ -152,14 +144,20 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnP
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
 
-  if (warp == kProducerWarp) {
+  if (warp == 8) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
+      const int q_tiles_here = n_kv_b > 0 ? 2 : 1;
+      mbar_arrive_expect_tx(q_full, q_tiles_here * L::kTileBytes);
+      for (int x = 0; x < q_tiles_here; ++x)
+        for (int d = 0; d < kDBlocks; ++d)
+          tma_load_2d(smem + L::kQOff + x * L::kTileBytes + d * L::kBoxBytes, &tm_qkv, q_full,
+                      q_col + d * 64, row0 + qt_of(x) * kQTile);
       bool ok = true;
-      for (int j = 0; j < n_kv && ok; ++j) {
-        const int s = j % kKvStages;
-        const uint32_t ph = (j / kKvStages) & 1u;
-        const int kv_row = static_cast<int>(row0) + j * kKvTile;
+      for (int j = 0; j < n_max && ok; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1u;
+        const int kv_row = row0 + j * kKvTile;
         if (!mbar_wait(&k_empty[s], ph ^ 1u, abort_flag, wait_limit)) { ok = false; break; }
         mbar_arrive_expect_tx(&k_full[s], L::kTileBytes);
         for (int d = 0; d < kDBlocks; ++d)
@@ -173,155 +171,135 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnP
       }
     }
     __syncwarp();
-  } else if (warp == kMmaWarp) {
+  } else if (warp == 9) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(kQTile, kKvTile);         // S = Q K^T
       constexpr uint32_t idesc_o = make_idesc_bf16(kQTile, D, true);         // O = P V (V N-major)
+      const uint32_t q_addr = smem_u32(smem + L::kQOff);
       const uint32_t k_addr = smem_u32(smem + L::kKOff);
       const uint32_t v_addr = smem_u32(smem + L::kVOff);
       bool ok = true;
-      // S_j = Q K_j^T into score buffer j & 1: D / 16 MMAs, Q from TMEM (8 columns per step of
-      // 16 elements), K_j from the 64-column boxes of its stage
-      auto issue_s = [&](int j) {
-        // one descriptor per burst; a step of 16 elements along K is +2 (units of 16 bytes) inside
-        // a 64-column box, the next box is kBoxBytes further (the address field cannot overflow:
-        // shared-memory addresses stay below 256 KB)
-        const uint64_t db0 = make_smem_desc_sw128(k_addr + (j % kKvStages) * L::kTileBytes);
-        const uint32_t d_tmem = tmem_base + kSCol0 + (j & 1) * 128;
-        const uint32_t a_tmem = tmem_base + kQCol;
+      // S_X(j) = Q_X K_j^T: D / 16 MMAs over the 64-column boxes of Q and K
+      auto issue_s = [&](int x, int j) {
+        const uint32_t qa = q_addr + x * L::kTileBytes;
+        const uint32_t ka = k_addr + (j & 1) * L::kTileBytes;
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k)
-          umma_bf16_tmem_a(d_tmem, a_tmem + 8u * k, db0 + ((k >> 2) * (L::kBoxBytes >> 4) + 2u * (k & 3)),
-                           idesc_s, k != 0 ? 1u : 0u);
-        umma_commit(&s_full[j & 1]);
-        umma_commit(&k_empty[j % kKvStages]);   // K_j is free once these products have read it
+        for (int d = 0; d < kDBlocks; ++d) {
+          const uint64_t da = make_smem_desc_sw128(qa + d * L::kBoxBytes);
+          const uint64_t db = make_smem_desc_sw128(ka + d * L::kBoxBytes);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_bf16(tmem_base + s_col(x), da + 2u * k, db + 2u * k, idesc_s, (d | k) != 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[x]);
       };
-      // O (+)= P_j V_j: 8 MMAs of 16 keys; P (two bf16 per column) sits in columns 0-31 (keys
-      // 0-63) and 64-95 (keys 64-127) of its score buffer, the V tile is read N-major: 16 key
-      // rows = 2048 bytes further per step
-      auto issue_pv = [&](int j) {
-        const uint64_t db0 = make_smem_desc_mn_sw128(v_addr + (j % kKvStages) * L::kTileBytes, L::kBoxBytes);
-        const uint32_t p_tmem = tmem_base + kSCol0 + (j & 1) * 128;
-        const uint32_t o_acc = tmem_base + kOCol;
+      // O_X (+)= P_X V_j: 8 MMAs of 16 keys; P sits in the first 64 columns of S_X (two bf16 per
+      // column), the V tile is read N-major: 16 key rows = 2048 bytes further per step
+      auto issue_pv = [&](int x, int j) {
+        const uint32_t va = v_addr + (j & 1) * L::kTileBytes;
+#pragma unroll
+        const uint64_t db0 = make_smem_desc_mn_sw128(va, L::kBoxBytes);
         const uint32_t first = j != 0 ? 1u : 0u;
-#pragma unroll
         for (int k = 0; k < kKvTile / 16; ++k)
-          umma_bf16_tmem_a(o_acc, p_tmem + (k < 4 ? 8u * k : 32u + 8u * k), db0 + k * (2048u >> 4), idesc_o,
+          umma_bf16_tmem_a(tmem_base + o_col(x), tmem_base + s_col(x) + 8u * k, db0 + k * 128u, idesc_o,
                            k != 0 ? 1u : first);
-        umma_commit(&v_empty[j % kKvStages]);
-        umma_commit(o_done);
       };
-      if (!mbar_wait(q_ready, 0, abort_flag, wait_limit)) ok = false;
-      // The scores run TWO tiles ahead of the softmax: S(j + 2) is issued in the same burst as
-      // PV(j) (it overwrites the buffer of P(j), which the in-order tensor pipe has consumed by
-      // then), so the pipe's start-up latency is paid once per burst of 16 instructions and
-      // the softmax warps always find their next scores ready.
-      for (int j = 0; j < 2 && j < n_kv && ok; ++j) {
-        if (!mbar_wait(&k_full[j % kKvStages], 0, abort_flag, wait_limit)) { ok = false; break; }
+      if (!mbar_wait(q_full, 0, abort_flag, wait_limit)) ok = false;
+      if (ok && !mbar_wait(&k_full[0], 0, abort_flag, wait_limit)) ok = false;
+      if (ok) {
         tc_fence_after();
-        issue_s(j);
+        issue_s(0, 0);
+        if (n_kv_b > 0) issue_s(1, 0);
+        umma_commit(&k_empty[0]);   // K_0 is free once both first products have read it
       }
-      for (int j = 0; j < n_kv && ok; ++j) {
-        // operands that were requested long ago first, then the probabilities
-        if (!mbar_wait(&v_full[j % kKvStages], (j / kKvStages) & 1u, abort_flag, wait_limit)) { ok = false; break; }
-        if (j + 2 < n_kv &&
-            !mbar_wait(&k_full[(j + 2) % kKvStages], ((j + 2) / kKvStages) & 1u, abort_flag, wait_limit)) { ok = false; break; }
-        if (!mbar_wait(&p_full[j & 1], (j >> 1) & 1u, abort_flag, wait_limit)) { ok = false; break; }
-        tc_fence_after();
-        issue_pv(j);
-        if (j + 2 < n_kv) {
-          issue_s(j + 2);
+      for (int j = 0; j < n_max && ok; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1u;
+        for (int x = 0; x < 2 && ok; ++x) {
+          if (j >= n_kv_of(x)) continue;
+          const bool last_user = (x == 1) || (j >= n_kv_b);   // of K_j / V_j among the two tiles
+          if (!mbar_wait(&p_full[x], j & 1u, abort_flag, wait_limit)) { ok = false; break; }
+          if (x == 0 || j >= n_kv_a) {   // first PV of this KV tile: V_j must have landed
+            if (!mbar_wait(&v_full[s], ph, abort_flag, wait_limit)) { ok = false; break; }
+          }
+          tc_fence_after();
+          issue_pv(x, j);
+          if (last_user) umma_commit(&v_empty[s]);
+          umma_commit(&o_done[x]);
+          if (j + 1 < n_kv_of(x)) {
+            const int s1 = (j + 1) & 1;
+            const uint32_t ph1 = ((j + 1) >> 1) & 1u;
+            if (x == 0 || j + 1 >= n_kv_a) {   // first S of the next KV tile: K_{j+1} must have landed
+              if (!mbar_wait(&k_full[s1], ph1, abort_flag, wait_limit)) { ok = false; break; }
+              tc_fence_after();
+            }
+            issue_s(x, j + 1);
+            // K_{j+1} is free once the last tile that uses it has issued its S
+            if (x == 1 || j + 1 >= n_kv_b) umma_commit(&k_empty[s1]);
+          }
         }
       }
     }
     __syncwarp();
   } else {
     // ---------------------------------------------------------------- softmax warps
-    // Two threads per query row: softmax warps w and w + 4 share a TMEM lane quarter and take the two
-    // halves of the 128 score columns (and of the D output columns); the halves exchange their
-    // row maxima through shared memory, ordered by a named barrier of the two warps.  Each
-    // thread only ever writes tensor-memory columns it alone reads.
+    const int x = warp >> 2;                 // query tile of this warp group
     const int quarter = warp & 3;            // TMEM lane quarter this warp may access
-    const int half = (warp - kFirstSoftmaxWarp) >> 2;   // column half
-    const int row = quarter * 32 + lane;     // row within the tile
-    const int q_pos = qt * kQTile + row;     // position of this thread's row in its sequence
+    const int n_mine = n_kv_of(x);
+    const int q_pos = qt_of(x) * kQTile + quarter * 32 + lane;     // position of this thread's row
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-    const uint32_t o_tmem = tmem_base + lane_addr + kOCol + half * (D / 2);
-    const uint32_t pair_bar = 1 + quarter;   // named barrier of the two warps of a lane quarter
-    float* xch = reinterpret_cast<float*>(smem + L::kXchOff) + row * 6;   // maxima [parity][half], row sums [half]
-
-    {
-      // this thread's half of its Q row -> TMEM (two bf16 per column, the A operand layout)
-      const long long grow_ = row0 + q_pos;
-      const uint4* src = reinterpret_cast<const uint4*>(p.qkv + grow_ * p.ld + q_col + half * (D / 2));
-      uint32_t qv[D / 4];
-#pragma unroll
-      for (int i = 0; i < D / 16; ++i) {
-        uint4 t = make_uint4(0, 0, 0, 0);
-        if (grow_ < p.T) t = src[i];
-        qv[4 * i] = t.x; qv[4 * i + 1] = t.y; qv[4 * i + 2] = t.z; qv[4 * i + 3] = t.w;
-      }
-      const uint32_t q_tmem = tmem_base + lane_addr + kQCol + half * (D / 4);
-      if constexpr (D == 128) tmem_st32(q_tmem, qv); else tmem_st16(q_tmem, qv);
-      tmem_st_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(q_ready);
-    }
-
+    const uint32_t s_tmem = tmem_base + lane_addr + s_col(x);
+    const uint32_t o_tmem = tmem_base + lane_addr + o_col(x);
     float m_ref = -INFINITY;                 // maximum the stored exponentials refer to (raw scores)
-    float l_sum = 0.f;                       // this thread's half of the row sum
+    float l_sum = 0.f;
     bool ok = true;
-    // (after a wait gave up, `ok` is false and the remaining iterations only keep the pair
-    // barrier counts of the two warps equal, so nobody is left waiting at a named barrier)
-    for (int j = 0; j < n_kv; ++j) {
-      if (ok && !mbar_wait(&s_full[j & 1], (j >> 1) & 1u, abort_flag, wait_limit)) ok = false;
-      ok = __all_sync(0xffffffffu, ok);   // warp-uniform: the tensor-memory instructions below are warp-wide
-                  tc_fence_after();
-      const bool diagonal = (j == n_kv - 1);
-      // keys of this thread's 64 columns the row may see: all, fewer on the diagonal tile
-      const int n_vis = diagonal ? min(64, max(q_pos - j * kKvTile - half * 64 + 1, 0)) : 64;
-      const uint32_t s_mine = tmem_base + lane_addr + kSCol0 + (j & 1) * 128 + half * 64;
-      uint32_t v[64];
-      tmem_ld32(s_mine, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
-      tmem_ld32(s_mine + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
-      tmem_ld_wait();   // (harmless on stale data when !ok: nothing below is stored then)
-      float m_part;
-      if (!diagonal) {
-        float m0 = __uint_as_float(v[0]), m1 = __uint_as_float(v[1]);
-        float m2 = __uint_as_float(v[2]), m3 = __uint_as_float(v[3]);
+    for (int j = 0; j < n_mine && ok; ++j) {
+      if (!mbar_wait(&s_full[x], j & 1u, abort_flag, wait_limit)) { ok = false; break; }
+      tc_fence_after();
+      const bool diagonal = (j == n_mine - 1);
+      const int k_pos0 = j * kKvTile;
+      // keys of this tile the row may see: all 128, fewer on the diagonal tile (causal)
+      const int n_vis = diagonal ? min(kKvTile, max(q_pos - k_pos0 + 1, 0)) : kKvTile;
+      // pass 1: row maximum.  The load of chunk c + 1 is in flight while chunk c is reduced.
+      float m_tile = -INFINITY;
+      {
+        uint32_t va[32], vb[32];
+        tmem_ld32(s_tmem, va);
 #pragma unroll
-        for (int i = 4; i < 64; i += 4) {
-          m0 = fmaxf(m0, __uint_as_float(v[i]));
-          m1 = fmaxf(m1, __uint_as_float(v[i + 1]));
-          m2 = fmaxf(m2, __uint_as_float(v[i + 2]));
-          m3 = fmaxf(m3, __uint_as_float(v[i + 3]));
+        for (int c = 0; c < 4; ++c) {
+          uint32_t (&cur)[32] = (c & 1) ? vb : va;
+          uint32_t (&nxt)[32] = (c & 1) ? va : vb;
+          tmem_ld_wait();
+          if (c < 3) tmem_ld32(s_tmem + (c + 1) * 32, nxt);
+          if (!diagonal) {
+            float m0 = __uint_as_float(cur[0]), m1 = __uint_as_float(cur[1]);
+            float m2 = __uint_as_float(cur[2]), m3 = __uint_as_float(cur[3]);
+#pragma unroll
+            for (int i = 4; i < 32; i += 4) {
+              m0 = fmaxf(m0, __uint_as_float(cur[i]));
+              m1 = fmaxf(m1, __uint_as_float(cur[i + 1]));
+              m2 = fmaxf(m2, __uint_as_float(cur[i + 2]));
+              m3 = fmaxf(m3, __uint_as_float(cur[i + 3]));
+            }
+            m_tile = fmaxf(m_tile, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (c * 32 + i < n_vis) m_tile = fmaxf(m_tile, __uint_as_float(cur[i]));
+          }
         }
-        m_part = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
-      } else {
-        m_part = -INFINITY;
-#pragma unroll
-        for (int i = 0; i < 64; ++i)
-          if (i < n_vis) m_part = fmaxf(m_part, __uint_as_float(v[i]));
       }
-      // exchange with the thread that holds the other half of the row
-      xch[(j & 1) * 2 + half] = m_part;
-      asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
-      const float m_tile = fmaxf(m_part, xch[(j & 1) * 2 + (half ^ 1)]);
       const float m_new = fmaxf(m_ref, m_tile);
       const bool grow = (j == 0) || ((m_new - m_ref) * p.scale_log2 > kRescaleThreshold);
-      if (!ok) continue;
       if (j > 0 && __any_sync(0xffffffffu, grow)) {
-        // O must be complete before it is rescaled: PV(j - 1) is the j-th product
-        if (!mbar_wait(o_done, (j - 1) & 1u, abort_flag, wait_limit)) ok = false;
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) continue;
+        // O of this tile must be complete before it is rescaled: PV(j - 1) is the j-th product
+        if (!mbar_wait(&o_done[x], (j - 1) & 1u, abort_flag, wait_limit)) { ok = false; break; }
         tc_fence_after();
         const float alpha = grow ? fast_exp2((m_ref - m_new) * p.scale_log2) : 1.0f;
         l_sum *= alpha;
 #pragma unroll 1
-        for (int c = 0; c < D / 64; ++c) {     // this thread's D / 2 output columns
+        for (int c = 0; c < D / 32; ++c) {
           uint32_t o[32];
           tmem_ld32(o_tmem + c * 32, o);
           tmem_ld_wait();
@@ -332,50 +310,51 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnP
         tmem_st_wait();
       }
       if (grow) m_ref = m_new;
-      // exponentials, row sum, P (bf16, two per column): this half's 64 probabilities go to the
-      // first 32 of ITS OWN score columns; the MMA warp reads keys 0-63 at column 0 and keys
-      // 64-127 at column 64 of the buffer
-            const float m_scaled = m_ref * p.scale_log2;
-      float l0 = 0.f, l1 = 0.f;
+      // pass 2: exponentials, row sum, P (bf16, two per column) into the first 64 columns of S
+      // (chunk c's probabilities land on columns whose scores were consumed with chunk c / 2)
+      const float m_scaled = m_ref * p.scale_log2;
+      {
+        uint32_t va[32], vb[32];
+        float l0 = 0.f, l1 = 0.f;
+        tmem_ld32(s_tmem, va);
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t pk[16];
+        for (int c = 0; c < 4; ++c) {
+          uint32_t (&cur)[32] = (c & 1) ? vb : va;
+          uint32_t (&nxt)[32] = (c & 1) ? va : vb;
+          tmem_ld_wait();
+          if (c < 3) tmem_ld32(s_tmem + (c + 1) * 32, nxt);
+          uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float e0 = fast_exp2(fmaf(__uint_as_float(v[c * 32 + 2 * i]), p.scale_log2, -m_scaled));
-          float e1 = fast_exp2(fmaf(__uint_as_float(v[c * 32 + 2 * i + 1]), p.scale_log2, -m_scaled));
-          if (diagonal) {
-            if (c * 32 + 2 * i >= n_vis) e0 = 0.f;
-            if (c * 32 + 2 * i + 1 >= n_vis) e1 = 0.f;
+          for (int i = 0; i < 16; ++i) {
+            float e0 = fast_exp2(fmaf(__uint_as_float(cur[2 * i]), p.scale_log2, -m_scaled));
+            float e1 = fast_exp2(fmaf(__uint_as_float(cur[2 * i + 1]), p.scale_log2, -m_scaled));
+            if (diagonal) {
+              if (c * 32 + 2 * i >= n_vis) e0 = 0.f;
+              if (c * 32 + 2 * i + 1 >= n_vis) e1 = 0.f;
+            }
+            l0 += e0;
+            l1 += e1;
+            const __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
+            pk[i] = *reinterpret_cast<const uint32_t*>(&b2);
           }
-          l0 += e0;
-          l1 += e1;
-          const __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
-          pk[i] = *reinterpret_cast<const uint32_t*>(&b2);
+          tmem_st16(s_tmem + c * 16, pk);
         }
-        tmem_st16(s_mine + c * 16, pk);
+        l_sum += l0 + l1;
       }
-      l_sum += l0 + l1;
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[j & 1]);
-          }
-    {
-      // full row sum = this half + the other half
-      xch[4 + half] = l_sum;
-      asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
-      l_sum += xch[4 + (half ^ 1)];
+      if (lane == 0) mbar_arrive(&p_full[x]);
     }
-    if (ok) {
-      // epilogue: O / l -> bf16 -> out[row, head * D + this thread's D / 2 columns]
-      if (__all_sync(0xffffffffu, mbar_wait(o_done, (n_kv - 1) & 1u, abort_flag, wait_limit))) {
+    if (ok && n_mine > 0) {
+      // epilogue: O / l -> bf16 -> out[row, head * D ...]
+      if (mbar_wait(&o_done[x], (n_mine - 1) & 1u, abort_flag, wait_limit)) {
         tc_fence_after();
         const float inv = 1.0f / l_sum;
         const bool row_ok = q_pos < p.S;
-        __nv_bfloat16* dst = p.out + (row0 + q_pos) * p.ldo + q_col + half * (D / 2);
+        __nv_bfloat16* dst = p.out + static_cast<long long>(row0 + q_pos) * p.ldo + q_col;
 #pragma unroll 1
-        for (int c = 0; c < D / 64; ++c) {
+        for (int c = 0; c < D / 32; ++c) {
           uint32_t o[32];
           tmem_ld32(o_tmem + c * 32, o);
           tmem_ld_wait();
@@ -386,9 +365,9 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnP
               uint32_t* ww = reinterpret_cast<uint32_t*>(&w);
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
-                const __nv_bfloat162 b2 = __floats2bfloat162_rn(
+                const __nv_bfloat162 b = __floats2bfloat162_rn(
                     __uint_as_float(o[q4 * 8 + 2 * i]) * inv, __uint_as_float(o[q4 * 8 + 2 * i + 1]) * inv);
-                ww[i] = *reinterpret_cast<const uint32_t*>(&b2);
+                ww[i] = *reinterpret_cast<const uint32_t*>(&b);
               }
               *reinterpret_cast<uint4*>(dst + c * 32 + q4 * 8) = w;
             }
@@ -401,7 +380,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tm_qkv, const AttnP
   // ---------------------------------------------------------------- teardown
   tc_fence_before();
   __syncthreads();
-  if (warp == kMmaWarp) {
+  if (warp == 9) {
     __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
@@ -418,19 +397,17 @@ cudaError_t launch_attention_prefill(const void* qkv, void* out, int B, int S, i
   CUtensorMap tm;
   if (!encode_map_2d(&tm, qkv, T, N, N, 128)) return cudaErrorInvalidValue;
   AttnParams p;
-  p.qkv = static_cast<const __nv_bfloat16*>(qkv);
-  p.ld = N;
-  p.T = T;
   p.S = S;
   p.hq = hq;
   p.hkv = hkv;
   p.q_tiles = (S + kQTile - 1) / kQTile;
+  p.pairs = (p.q_tiles + 1) / 2;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.out = static_cast<__nv_bfloat16*>(out);
   p.ldo = hq * D;
   p.wait_limit_ns = 0;
   p.status = status;
-  const dim3 grid(static_cast<unsigned>(p.q_tiles), static_cast<unsigned>(hq), static_cast<unsigned>(B));
+  const dim3 grid(static_cast<unsigned>(p.pairs), static_cast<unsigned>(hq), static_cast<unsigned>(B));
   static bool attr_done[2] = {false, false};
   if (D == 128) {
     if (!attr_done[1]) {
