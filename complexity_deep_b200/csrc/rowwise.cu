@@ -43,7 +43,10 @@ constexpr int kMaxVec = 16;  // register path: H <= 16 * 256 = 4096, H % 256 == 
 // One warp per row; the row lives in registers between the reduction and the scaling, so
 // x is read from HBM exactly once.  kSplit: `res` is the low part of a split-bf16 value
 // (x + res carries 16 significant bits); the sum then stays in fp32 and nothing is written back.
-template <bool kSplit>
+// NV: uint4 per lane (H / 256) when known at compile time — the row then needs exactly NV (2 NV
+// for a split row) 16-byte registers per lane, which keeps enough warps resident to cover HBM
+// latency; NV = 0 is the generic form for any H <= 4096 with H % 256 == 0.
+template <bool kSplit, int NV>
 __global__ void __launch_bounds__(kNormWarps * 32)
 rmsnorm_rows_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
                     const __nv_bfloat16* __restrict__ w, float eps,
@@ -54,22 +57,23 @@ rmsnorm_rows_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
   const int row = blockIdx.x * kNormWarps + (threadIdx.x >> 5);
   if (row >= T) return;
   const int lane = threadIdx.x & 31;
-  const int nv = H >> 8;  // uint4 (8 bf16) per lane
+  constexpr int kVec = NV ? NV : kMaxVec;
+  const int nv = NV ? NV : (H >> 8);  // uint4 (8 bf16) per lane
   const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * H);
   const uint4* rr = res ? reinterpret_cast<const uint4*>(res + static_cast<size_t>(row) * H)
                         : nullptr;
-  uint4 buf[kMaxVec];
-  uint4 low[kSplit ? kMaxVec : 1];
+  uint4 buf[kVec];
+  uint4 low[kSplit ? kVec : 1];
 #pragma unroll
-  for (int v = 0; v < kMaxVec; ++v)
+  for (int v = 0; v < kVec; ++v)
     if (v < nv) buf[v] = xr[v * 32 + lane];
   if constexpr (kSplit) {
 #pragma unroll
-    for (int v = 0; v < kMaxVec; ++v)
+    for (int v = 0; v < kVec; ++v)
       if (v < nv) low[v] = rr ? rr[v * 32 + lane] : make_uint4(0, 0, 0, 0);
   } else if (rr) {
 #pragma unroll
-    for (int v = 0; v < kMaxVec; ++v)
+    for (int v = 0; v < kVec; ++v)
       if (v < nv) {
         const uint4 r = rr[v * 32 + lane];
         uint32_t* a = reinterpret_cast<uint32_t*>(&buf[v]);
@@ -80,13 +84,13 @@ rmsnorm_rows_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
     if (sum_out) {
       uint4* so = reinterpret_cast<uint4*>(sum_out + static_cast<size_t>(row) * H);
 #pragma unroll
-      for (int v = 0; v < kMaxVec; ++v)
+      for (int v = 0; v < kVec; ++v)
         if (v < nv) so[v * 32 + lane] = buf[v];
     }
   }
   float ss = 0.f;
 #pragma unroll
-  for (int v = 0; v < kMaxVec; ++v)
+  for (int v = 0; v < kVec; ++v)
     if (v < nv) {
       const uint32_t* a = reinterpret_cast<const uint32_t*>(&buf[v]);
       const uint32_t* b = reinterpret_cast<const uint32_t*>(&low[kSplit ? v : 0]);
@@ -106,7 +110,7 @@ rmsnorm_rows_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
   uint4* orw = reinterpret_cast<uint4*>(out + static_cast<size_t>(orow) * H);
   const uint4* wr = reinterpret_cast<const uint4*>(w);
 #pragma unroll
-  for (int v = 0; v < kMaxVec; ++v)
+  for (int v = 0; v < kVec; ++v)
     if (v < nv) {
       const uint4 wv = wr[v * 32 + lane];
       const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
@@ -478,10 +482,16 @@ cudaError_t launch_rmsnorm(const void* x, const void* residual, const void* weig
   auto ob = static_cast<__nv_bfloat16*>(out);
   if ((H & 255) == 0 && H <= kMaxVec * 256) {
     const int blocks = (T + kNormWarps - 1) / kNormWarps;
-    return split ? launch_kernel(rmsnorm_rows_kernel<true>, dim3(blocks), dim3(kNormWarps * 32), 0,
-                                 stream, xb, rb, wb, eps, sb, ob, dst_rows, T, H)
-                 : launch_kernel(rmsnorm_rows_kernel<false>, dim3(blocks), dim3(kNormWarps * 32), 0,
-                                 stream, xb, rb, wb, eps, sb, ob, dst_rows, T, H);
+    auto go = [&](auto kern) {
+      return launch_kernel(kern, dim3(blocks), dim3(kNormWarps * 32), 0, stream, xb, rb, wb, eps, sb,
+                           ob, dst_rows, T, H);
+    };
+    switch (H >> 8) {   // hidden sizes 768 / 1024 / 2048 get their own instantiation (fewer registers)
+      case 3: return split ? go(rmsnorm_rows_kernel<true, 3>) : go(rmsnorm_rows_kernel<false, 3>);
+      case 4: return split ? go(rmsnorm_rows_kernel<true, 4>) : go(rmsnorm_rows_kernel<false, 4>);
+      case 8: return split ? go(rmsnorm_rows_kernel<true, 8>) : go(rmsnorm_rows_kernel<false, 8>);
+      default: return split ? go(rmsnorm_rows_kernel<true, 0>) : go(rmsnorm_rows_kernel<false, 0>);
+    }
   } else {
     return launch_kernel(rmsnorm_generic_kernel, dim3(T), dim3(128), 0, stream, xb, rb, wb, eps, sb,
                          ob, dst_rows, T, H, split ? 1 : 0);
