@@ -721,6 +721,47 @@ def run_layer(args):
         dist.destroy_process_group()
 
 
+def run_attention(args):
+    """Prefill attention alone: cd_attention_prefill against torch SDPA (cuDNN) on the same
+    buffer, 16 Q / 8 KV heads of 128 (the 1B configuration), kernel time from CUDA events."""
+    import torch.nn.functional as F
+    from complexity_deep_b200 import ops
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    B, S, hq, hkv, D = args.batch or 32, args.seq_len, 16, 8, 128
+    g = torch.Generator(device=dev).manual_seed(0)
+    qkv = torch.randn(B * S, (hq + 2 * hkv) * D, device=dev, generator=g).to(torch.bfloat16)
+    q = qkv[:, :hq * D].view(B, S, hq, D).transpose(1, 2)
+    k = qkv[:, hq * D:(hq + hkv) * D].view(B, S, hkv, D).transpose(1, 2)
+    v = qkv[:, (hq + hkv) * D:].view(B, S, hkv, D).transpose(1, 2)
+    fns = {"cd_attention_prefill": lambda: ops.attention_prefill(qkv, B, S, hq, hkv, D),
+           "torch_sdpa": lambda: F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)}
+    flop = 4 * B * hq * S * S * D / 2
+    out = {}
+    for name, fn in fns.items():
+        for _ in range(args.warmup):
+            fn()
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(args.steps):
+            fn()
+        t1.record()
+        torch.cuda.synchronize()
+        ms = t0.elapsed_time(t1) / args.steps
+        out[name] = {"ms": round(ms, 4), "tflops": round(flop / ms / 1e9, 1)}
+    ops.status_fetch()
+    a = fns["cd_attention_prefill"]().float().view(B, S, hq, D).transpose(1, 2)
+    diff = float((a - fns["torch_sdpa"]().float()).abs().max())
+    pk = peaks()
+    print(json.dumps({"metric": "prefill attention TFLOP/s (bf16)", "value": out["cd_attention_prefill"]["tflops"],
+                      "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+                      "config": {"workload": "attn_prefill", "batch": B, "seq_len": S, "q_heads": hq,
+                                 "kv_heads": hkv, "head_dim": D, "flop_per_launch": flop},
+                      "kernels": out, "frac_of_peak": round(out["cd_attention_prefill"]["tflops"] / pk["bf16_tflops"], 4),
+                      "max_abs_diff_vs_sdpa": diff, "dtype": "bf16", "data": "synthetic", "impl": "b200"}), flush=True)
+
+
 def run_decode(args):
     """1B-class decode: concurrent sequences with a prefilled KV cache
     of 4096 tokens (values N(0,1) bf16), one new Zipf token per sequence per step, the new
@@ -883,7 +924,9 @@ def main():
     ap.add_argument("--ep-exchange", default="peer", choices=["peer", "nccl"],
                     help="ep_layer: peer stores from the kernels, or NCCL all-to-all")
     ap.add_argument("--cache-len", type=int, default=4096, help="decode_1b: prefilled KV tokens")
-    ap.add_argument("--workload", default="prefill_1b", choices=["prefill_1b", "decode_1b"] + list(LAYER_CONFIGS),
+    ap.add_argument("--seq-len", type=int, default=SEQ_LEN, help="attn_prefill: sequence length")
+    ap.add_argument("--workload", default="prefill_1b",
+                    choices=["prefill_1b", "decode_1b", "attn_prefill"] + list(LAYER_CONFIGS),
                     help="prefill_1b is the headline; the layer modes report MoE-layer TFLOP/s")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "b200":
@@ -894,6 +937,8 @@ def main():
         run_reference_gpu(args)
     elif args.workload == "decode_1b":
         run_decode(args)
+    elif args.workload == "attn_prefill":
+        run_attention(args)
     elif args.workload != "prefill_1b":
         run_layer(args)
     else:

@@ -177,7 +177,6 @@ int cd_decode_attention(const void* q, long long q_stride_b, const void* k, cons
 int cd_attention_prefill_supported(int B, int S, int hq, int hkv, int D) {
   if (B < 1 || S < 1 || hq < 1 || hkv < 1 || hq % hkv) return 0;
   if (D != 64 && D != 128) return 0;
-  if (hq > 65535 || B > 65535) return 0;                         // grid dimensions y / z
   if (static_cast<long long>(B) * S > 0x7fffffffLL - 256) return 0;   // token rows are 32-bit TMA coordinates
   return 1;
 }
