@@ -37,6 +37,14 @@ const char* cd_last_cuda_error(void) { return g_cuda_err; }
 
 int cd_max_groups(void) { return kMaxGroups; }
 
+size_t cd_splitk_workspace_bytes(void) { return splitk_workspace_bytes(); }
+
+int cd_splitk_ranges(int T, int K, int N) { return splitk_ranges_dense(T, N, K); }
+
+int cd_splitk_workspace_set(void* workspace, size_t bytes, void* stream) {
+  return splitk_workspace_set(workspace, bytes, as_stream(stream));
+}
+
 int cd_status_fetch(int* h_status) {
   if (!h_status) return CD_ERR_INVALID;
   int* d = device_status_word();

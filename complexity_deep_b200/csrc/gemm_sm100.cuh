@@ -103,6 +103,13 @@ struct GemmParams {
   int rope_S, rope_pos0;   // row r sits at position rope_pos0 + r % rope_S
   int rope_q_cols;         // columns [0, rope_q_cols) are q heads, [rope_q_cols, rope_cols) k heads
   int rope_cols;
+  // split-K for few-row calls (CG = 1): the K loop of every output tile is cut into `splits`
+  // ranges computed by different CTAs; each writes its fp32 partial tile to sk_scratch and
+  // counts in sk_counters[tile]; the CTA that arrives last adds the partials and runs the fused
+  // epilogue (and puts the counter back to zero for the next launch)
+  int splits;              // 1 = off
+  float* sk_scratch;       // [tiles * splits][128][BN] fp32
+  int* sk_counters;        // [tiles], zero between launches
   // self-test of the failure path: with `selftest_stall` the producer issues no loads, so the
   // pipeline waits run into `wait_limit_ns` (0 = the default limit) and the kernel must leave
   // cleanly with the status word raised
@@ -252,6 +259,8 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
       mbar_init(&tmem_empty[a], EW * CG);  // one arrival per epilogue warp (of both CTAs)
     }
     *abort_flag = 0;
+    *reinterpret_cast<int*>(smem + L::kMiscOff + 8) = 0;
+    *reinterpret_cast<int*>(smem + L::kMiscOff + 12) = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmA0);
     tma_prefetch_desc(&tmB0);
@@ -290,6 +299,11 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
 
   const uint32_t tmem_base = *tmem_base_slot;
   const int total_tiles = prefix[p.num_groups + (p.N2 > 0 ? 1 : 0)];
+  // split-K only in the narrow single-CTA instantiations (the few-row problems it is for never
+  // take the 256-wide tile, whose epilogue has no registers to spare)
+  constexpr bool kSplitK = (CG == 1 && BN <= 128);
+  const int splits = (kSplitK && p.splits > 1) ? p.splits : 1;
+  const int total_units = total_tiles * splits;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -297,7 +311,10 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
       uint32_t it = 0;
       int gcur = 0;
       bool ok = true;
-      for (int t = tile0; t < total_tiles && ok; t += tstride) {
+      for (int u = tile0; u < total_units && ok; u += tstride) {
+        const int t = u / splits;
+        const int sp = u - t * splits;
+        const int kb_lo = (sp * kb_total) / splits, kb_hi = ((sp + 1) * kb_total) / splits;
         const TileCoord c = decode_tile(t, gcur, prefix, seg, p.num_groups, p.M, n_tiles, n_tiles2,
                                         p.band, BN, kTileM);
         const bool second = c.group >= p.num_groups;   // dense problem against B1, K segment 0 only
@@ -305,7 +322,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
         const int b0_row = c.group * p.b0_group_rows + c.n0 + static_cast<int>(crank) * (BN / CG);
         const int b1_row = (second ? 0 : c.group * p.b1_group_rows) + c.n0 +
                            static_cast<int>(crank) * (BN / CG);
-        for (int kb = 0; kb < kb_total; ++kb, ++it) {
+        for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
           const uint32_t s = it % S;
           const uint32_t ph = (it / S) & 1u;
           if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag, wait_limit)) {
@@ -362,7 +379,9 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
       uint32_t it = 0;
       uint32_t tcount = 0;
       bool ok = true;
-      for (int t = tile0; t < total_tiles && ok; t += tstride, ++tcount) {
+      for (int u = tile0; u < total_units && ok; u += tstride, ++tcount) {
+        const int sp = u % splits;
+        const int kb_lo = (sp * kb_total) / splits, kb_hi = ((sp + 1) * kb_total) / splits;
         const uint32_t acc = tcount & 1u;
         const uint32_t acc_ph = (tcount >> 1) & 1u;
         if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1u, abort_flag, wait_limit)) {
@@ -371,7 +390,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kAccCols;
-        for (int kb = 0; kb < kb_total; ++kb, ++it) {
+        for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
           const uint32_t s = it % S;
           const uint32_t ph = (it / S) & 1u;
           if (!mbar_wait(&full_bar[s], ph, abort_flag, wait_limit)) {
@@ -387,10 +406,10 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
             // advancing 16 bf16 (32 bytes) along K inside the swizzle row: +2 in the
             // descriptor's 16-byte address units
             if constexpr (CG == 2)
-              umma_bf16_pair(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+              umma_bf16_pair(d_tmem, da + 2u * k, db + 2u * k, idesc, ((kb - kb_lo) | k) != 0 ? 1u : 0u);
             else
               umma_bf16(d_tmem + (k % kChains) * BN, da + 2u * k, db + 2u * k, idesc,
-                        (kb | (k / kChains)) != 0 ? 1u : 0u);
+                        ((kb - kb_lo) | (k / kChains)) != 0 ? 1u : 0u);
           }
           // frees the stage (in both CTAs of a pair) once these MMAs have read it
           if constexpr (CG == 2) umma_commit_pair(&empty_bar[s]); else umma_commit(&empty_bar[s]);
@@ -419,7 +438,11 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
     uint32_t tcount = 0;
     int gcur = 0;
     bool ok = true;
-    for (int t = tile0; t < total_tiles && ok; t += tstride, ++tcount) {
+    int* sk_arrivals = reinterpret_cast<int*>(smem + L::kMiscOff + 12);   // split-K: epilogue-warp barrier
+    int sk_target = 0;
+    for (int u = tile0; u < total_units && ok; u += tstride, ++tcount) {
+      const int t = u / splits;
+      const int sp = u - t * splits;
       const TileCoord c = decode_tile(t, gcur, prefix, seg, p.num_groups, p.M, n_tiles, n_tiles2,
                                       p.band, BN, kTileM);
       const bool second = c.group >= p.num_groups;
@@ -485,7 +508,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
         }
         cp_async_commit();
       };
-      if (has_res && ehalf < nsub) {
+      if (splits == 1 && has_res && ehalf < nsub) {
         fetch_residual(0);
         if (ehalf + kEpiHalves < nsub) fetch_residual(1);
       }
@@ -504,6 +527,86 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
       }
       tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kAccCols;
+
+      // split-K: hand this CTA's partial tile over; only the CTA that arrives last goes on
+      const float* sk_row = nullptr;    // this lane's row in partial 0 of the tile (last CTA only)
+      if (splits > 1) {
+        constexpr int kTileFloats = kBlockM * BN;
+        float* mine = p.sk_scratch + (static_cast<size_t>(t) * splits + sp) * kTileFloats +
+                      (quarter * 32 + lane) * BN;
+#pragma unroll 1
+        for (int cc = 0; cc < BN / 32; ++cc) {
+          if (((cc >> 1) % kEpiHalves) != ehalf) continue;
+          uint32_t v[32];
+          tmem_ld32(t_row + cc * 32, v);
+          if constexpr (kChains == 2) {
+            uint32_t v2[32];
+            tmem_ld32(t_row + BN + cc * 32, v2);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(v2[j]));
+          }
+          tmem_ld_wait();
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            *reinterpret_cast<uint4*>(mine + cc * 32 + q * 4) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+        }
+        __threadfence();
+        volatile int* sk_flag = reinterpret_cast<volatile int*>(smem + L::kMiscOff + 8);
+        // barrier of the epilogue warps on a shared-memory counter; like every wait of this
+        // kernel it gives up when another role has raised the abort flag (a named barrier would
+        // wait forever for a warp that left its loop)
+        auto epi_sync = [&]() {
+          __syncwarp();
+          if (lane == 0) atomicAdd(sk_arrivals, 1);
+          sk_target += EW;
+          while (*reinterpret_cast<volatile int*>(sk_arrivals) < sk_target) {
+            if (*abort_flag) { ok = false; break; }
+          }
+          __syncwarp();
+        };
+        epi_sync();
+        if (warp == 2 && lane == 0) {
+          const int old = atomicAdd(p.sk_counters + t, 1);
+          __threadfence();                    // the other CTAs' partials are visible before they are read
+          const int last = (old == splits - 1) ? 1 : 0;
+          if (last) p.sk_counters[t] = 0;     // every other CTA of the tile has counted: ready for the next launch
+          *sk_flag = last;
+        }
+        epi_sync();
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        const bool sk_last = *sk_flag != 0;
+        if (!sk_last) {                     // not the last: the accumulator is free again, next unit
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+          continue;
+        }
+        __threadfence();
+        sk_row = p.sk_scratch + static_cast<size_t>(t) * splits * kTileFloats + (quarter * 32 + lane) * BN;
+        if (has_res && ehalf < nsub) {
+          fetch_residual(0);
+          if (ehalf + kEpiHalves < nsub) fetch_residual(1);
+        }
+      }
+      // the accumulator values of 32 columns starting at `col`, summed over the partial tiles
+      auto sk_sum = [&](int col, uint32_t (&v)[32]) {
+        float a[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) a[j] = 0.f;
+        for (int sidx = 0; sidx < splits; ++sidx) {
+          const float4* src = reinterpret_cast<const float4*>(sk_row + static_cast<size_t>(sidx) * (kBlockM * BN) + col);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const float4 f = __ldcg(src + q);
+            a[4 * q] += f.x; a[4 * q + 1] += f.y; a[4 * q + 2] += f.z; a[4 * q + 3] += f.w;
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(a[j]);
+      };
 
       // coalesced copy-out of one staged 32 x 64 sub-tile: 4 rows x 128 bytes per warp instruction
       auto copy_out = [&](const uint8_t* buf, int col0) {
@@ -648,6 +751,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
             __syncwarp();
           }
           tmem_ld_wait();
+          if (sk_row) sk_sum(sub * 32, v);
           const bool has_lo = p.residual_lo != nullptr;
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
@@ -743,6 +847,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
               __syncwarp();
             }
             tmem_ld_wait();
+            if (sk_row) sk_sum(sub * 64 + hh * 32, v);
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
               const int col = colh + q * 8;
@@ -812,6 +917,10 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
               }
             }
             tmem_ld_wait();
+            if (sk_row) {
+              sk_sum(sub * 64 + half * 32, g);
+              sk_sum(BN / 2 + sub * 64 + half * 32, u);
+            }
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
               float h[8];

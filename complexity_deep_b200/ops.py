@@ -8,6 +8,7 @@ back to PyTorch operators.
 from __future__ import annotations
 
 import ctypes
+import os
 from dataclasses import dataclass
 from typing import Optional, Tuple
 
@@ -565,9 +566,43 @@ def moe_combine(h_shared: torch.Tensor, wd_shared: torch.Tensor,
     return (out, out_lo) if want_lo else out
 
 
+# device index -> the split-K workspace registered with the library (kept alive here; None =
+# switched off by the caller)
+_SPLIT_K_WS: dict = {}
+_SPLIT_K_ROWS = 512          # calls of more rows never qualify (their tiles fill the SMs)
+_SPLIT_K_AUTO = os.environ.get("CDEEP_SPLIT_K", "1") != "0"
+
+
+def split_k(enable: bool = True, device: Optional[torch.device] = None) -> None:
+    """Registers (or withdraws) the workspace that lets the few-row projections of a decode step
+    cut their K loop over several CTAs (cd_splitk_workspace_set).  The workspace is shared by
+    every call on the device: keep launches that may split on one stream."""
+    lib = _lib.load()
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        if enable:
+            ws = torch.empty(lib.cd_splitk_workspace_bytes(), dtype=torch.uint8, device=dev)
+            _lib.check(lib.cd_splitk_workspace_set(ws.data_ptr(), ws.numel(), _stream()),
+                       "cd_splitk_workspace_set")
+            _SPLIT_K_WS[dev.index] = ws
+        else:
+            _lib.check(lib.cd_splitk_workspace_set(None, 0, _stream()), "cd_splitk_workspace_set")
+            torch.cuda.current_stream().synchronize()
+            _SPLIT_K_WS[dev.index] = None      # stays off: the automatic registration skips this device
+
+
+def _split_k_auto(x: torch.Tensor) -> None:
+    # first few-row projection on a device: register the workspace (not while a graph is being
+    # captured; the model's warm-up pass before the capture comes through here)
+    if (_SPLIT_K_AUTO and x.shape[0] <= _SPLIT_K_ROWS and x.device.index not in _SPLIT_K_WS
+            and not torch.cuda.is_current_stream_capturing()):
+        split_k(True, x.device)
+
+
 def mu_qkv(x: torch.Tensor, mu_prev: Optional[torch.Tensor], w: torch.Tensor,
            w_mu: Optional[torch.Tensor]) -> torch.Tensor:
     lib = _lib.load()
+    _split_k_auto(x)
     _need(x, "x")
     _need(w, "qkv weight")
     T, H = x.shape
@@ -626,6 +661,7 @@ def mu_proj(h: torch.Tensor, w: torch.Tensor, mu_param: torch.Tensor, mu_min: fl
     _need(h, "hidden_states")
     _need(w, "mu_proj.weight")
     _need(mu_param, "mu")
+    _split_k_auto(h)
     T, H = h.shape
     out = torch.empty(T, H, dtype=BF16, device=h.device)
     lo, hi = out_clamp if out_clamp is not None else (0.0, 0.0)
@@ -644,6 +680,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = 
     lib = _lib.load()
     _need(x, "x")
     _need(w, "weight")
+    _split_k_auto(x)
     T, K = x.shape
     N = w.shape[0]
     if w.shape[1] != K:

@@ -43,6 +43,22 @@ const char* cd_last_cuda_error(void);
  * cd_moe_up_pair, cd_moe_down and cd_moe_down_push return CD_ERR_UNSUPPORTED (text in
  * cd_last_cuda_error) beyond it.  The dispatch entry points accept up to 256 experts. */
 int cd_max_groups(void);
+/* Split-K for projections of few rows (decode; no counterpart in the reference).  A dense
+ * projection (cd_linear, cd_mu_qkv, cd_mu_proj, cd_moe_up with one group) whose output tiles
+ * occupy at most half of the SMs cuts the K loop of every tile into up to 8 ranges computed by
+ * different CTAs; fp32 partial tiles go through this workspace and the CTA that finishes a tile
+ * last adds them and runs the same fused epilogue, so results differ from the unsplit launch only
+ * by the order of the fp32 additions.  Off until a workspace is registered for the current
+ * device; cd_splitk_workspace_bytes() is a size that suits every eligible call (a smaller one
+ * turns splitting off for the calls it cannot hold).  The workspace is shared by all calls on
+ * the device: launches that may split must be ordered on one stream (or by events), and the
+ * memory must stay valid until cd_splitk_workspace_set(NULL, 0, stream) or the last launch has
+ * finished.  `stream` orders the clearing of the workspace's counters. */
+size_t cd_splitk_workspace_bytes(void);
+int cd_splitk_workspace_set(void* workspace, size_t bytes, void* stream);
+/* Number of K ranges cd_linear (or cd_mu_proj; cd_mu_qkv with K = the sum of its two K extents)
+ * would use for a [T, K] x [N, K]^T call on the current device as it is set up now (1 = unsplit). */
+int cd_splitk_ranges(int T, int K, int N);
 /* Synchronises the current device, copies the kernels' status word to *h_status
  * (0 = every bounded wait completed) and clears it. */
 int cd_status_fetch(int* h_status);
