@@ -42,7 +42,7 @@ bool make_map(CUtensorMap* m, const void* base, long long rows, long long cols, 
   if (!fn) return false;
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
   cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
-  cuuint32_t box[2] = {static_cast<cuuint32_t>(kBlockK), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(kBoxK), static_cast<cuuint32_t>(box_rows)};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -59,10 +59,11 @@ struct DeviceInfo {
 };
 constexpr int kSkCounterBytes = 1024;   // head of the workspace: one arrival counter per output tile
 constexpr int kSkMaxTiles = kSkCounterBytes / 4;
-// Measured on B200 (32 rows, 2048 output columns): an unsplit tile costs 4.7 us + 0.29 us per k-block of
-// 64, handing the partial tiles over costs about 4.7 us: a split pays from about 48 k-blocks.
-constexpr int kSkMinBlocksPerSplit = 16; // k-blocks per K range
-constexpr int kSkMinBlocks = 48;         // shortest K loop that is split at all
+// Measured on B200 (32 rows, 2048 output columns): an unsplit launch costs 4.9 us + 0.21 us per 64
+// elements of K, handing the partial tiles over costs about 4.5 us: two ranges pay from about 48
+// boxes of 64 (K = 4096: 18.4 -> 16.0 us, K = 5632: 23.4 -> 18.5 us).
+constexpr int kSkMinBlocksPerSplit = 16; // 64-element boxes of K per range
+constexpr int kSkMinBlocks = 48;         // shortest K loop (in boxes) that is split at all
 constexpr int kSkMaxSplits = 8;
 constexpr int kMaxDevices = 64;
 DeviceInfo g_dev[kMaxDevices];
@@ -137,8 +138,9 @@ cudaError_t launch_any(int block_n, int kind, int grid, const CUtensorMap& a0,
 // Accumulator-tile width for the store epilogue.
 // Many tiles (prefill): the 256-wide tile whenever it gives (almost) every SM a tile; the GEMM
 // is then bound by tensor throughput.  Few tiles (decode): an output tile is one chain of K/16
-// dependent MMA instructions that cost ~140 cycles each whatever their width (measured: time
-// = 3.8 us + 0.30 us per 64-wide k-block for 32-, 64- and 128-wide tiles alike), so the time
+// MMA instructions issued by one thread, which cost that thread the same whatever their width up
+// to 128 columns (measured: 40 .. 64 cycles per instruction plus about 300 per pipeline stage;
+// time = 4.9 us + 0.21 us per 64 elements of K with two boxes per stage), so the time
 // is set by how many tiles the busiest SM runs one after the other: the narrowest tile that
 // still leaves at most one tile per SM; if even 256-wide tiles are more than that, the width
 // with the fewest waves.  For grouped calls every non-empty group has at least one row tile.
@@ -179,11 +181,13 @@ int choose_cta_group(int M, int block_n, int sm_count) {
 // Split-K: a dense call whose output tiles leave at least half of the SMs idle is one chain of
 // K / 16 dependent MMAs per tile; cutting K into ranges shortens the chain.  Needs a registered
 // workspace, single CTAs and a tile of at most 128 columns.  Returns the number of K ranges.
-int plan_splits(const DeviceInfo& di, int M, int N, int block_n, int kb_total) {
+int plan_splits(const DeviceInfo& di, int M, int N, int block_n, int kb_total, int k_boxes) {
   const long long tiles = static_cast<long long>((M + kBlockM - 1) / kBlockM) * ((N + block_n - 1) / block_n);
-  if (!di.sk_ws || block_n > 128 || tiles > kSkMaxTiles || tiles * 2 > di.sm_count || kb_total < kSkMinBlocks) return 1;
+  if (!di.sk_ws || block_n > 128 || tiles > kSkMaxTiles || tiles * 2 > di.sm_count ||
+      kb_total * k_boxes < kSkMinBlocks)
+    return 1;
   int splits = static_cast<int>(di.sm_count / tiles);
-  if (splits > kb_total / kSkMinBlocksPerSplit) splits = kb_total / kSkMinBlocksPerSplit;
+  if (splits > kb_total * k_boxes / kSkMinBlocksPerSplit) splits = kb_total * k_boxes / kSkMinBlocksPerSplit;
   if (splits > kSkMaxSplits) splits = kSkMaxSplits;
   const size_t need =
       kSkCounterBytes + static_cast<size_t>(tiles) * splits * kBlockM * block_n * sizeof(float);
@@ -270,7 +274,8 @@ int splitk_ranges_dense(int M, int N, int K) {
   if (!di || M <= 0 || N <= 0 || K <= 0) return 1;
   const int bn = store_block_n_impl(M, N, 1, di->sm_count);
   if (choose_cta_group(M, bn, di->sm_count) != 1) return 1;
-  return plan_splits(*di, M, N, bn, (K + kBlockK - 1) / kBlockK);
+  const int kblock = kBoxK * gemm_k_boxes(bn, 1);
+  return plan_splits(*di, M, N, bn, (K + kblock - 1) / kblock, gemm_k_boxes(bn, 1));
 }
 
 int launch_gemm(int M, int N, int num_groups, const int* seg_offsets, const GemmOperand& op0,
@@ -397,10 +402,11 @@ int launch_gemm(int M, int N, int num_groups, const int* seg_offsets, const Gemm
   if (units < 1) units = 1;
 
   {
-    const int kb_total = (op0.K + kBlockK - 1) / kBlockK + (op1 ? (op1->K + kBlockK - 1) / kBlockK : 0);
+    const int kblock = kBoxK * gemm_k_boxes(block_n, cg);
+    const int kb_total = (op0.K + kblock - 1) / kblock + (op1 ? (op1->K + kblock - 1) / kblock : 0);
     const bool eligible = cg == 1 && num_groups == 1 && !second && !epi.rope_cos &&
                           !epi.selftest_stall && (epi.kind != kEpiSwiGLU || block_n >= 64);
-    const int splits = eligible ? plan_splits(*di, M, N, block_n, kb_total) : 1;
+    const int splits = eligible ? plan_splits(*di, M, N, block_n, kb_total, gemm_k_boxes(block_n, cg)) : 1;
     if (splits > 1) {
       p.splits = splits;
       p.sk_counters = static_cast<int*>(di->sk_ws);

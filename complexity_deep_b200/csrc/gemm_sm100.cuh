@@ -29,7 +29,14 @@
 namespace cdeep {
 
 constexpr int kBlockM = 128;       // rows per tile = TMEM lanes
-constexpr int kBlockK = 64;        // bf16 elements per k-block = one 128-byte swizzle row
+constexpr int kBoxK = 64;          // bf16 elements per TMA box row = one 128-byte swizzle row
+// Boxes per operand and pipeline stage.  The thread that issues the MMAs pays a fixed price per
+// stage (barrier wait, fence, commit: about 300 cycles measured) on top of 40 .. 64 cycles per
+// tcgen05.mma of a tile up to 128 columns wide, so the narrow tiles of few-row calls, whose K loop
+// is bound by that thread, take two boxes (128 elements of K) per stage: 0.29 -> 0.21 us per 64
+// elements of K.  Wide tiles are bound by the tensor pipe and want many fine stages instead
+// (with two boxes the 1B prefill step was 5 % slower).
+__host__ __device__ constexpr int gemm_k_boxes(int bn, int cg) { return (cg == 1 && bn <= 64) ? 2 : 1; }
 constexpr int kUmmaK = 16;         // K of one tcgen05.mma for 16-bit inputs
 constexpr int kMaxGroups = 128;
 constexpr int kEpiCols = 64;          // output columns per epilogue sub-tile (128 bytes of bf16)
@@ -122,6 +129,8 @@ struct GemmParams {
 // CTA stages its 128 rows of A and its BN / 2 rows of B.
 template <int BN, int CG, int EW = 4>
 struct GemmSmem {
+  static constexpr int kKBoxes = gemm_k_boxes(BN, CG);
+  static constexpr int kBlockK = kBoxK * kKBoxes;   // bf16 elements of K per pipeline stage (k-block)
   static constexpr int kABytes = kBlockM * kBlockK * 2;
   static constexpr int kBBytes = (BN / CG) * kBlockK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
@@ -212,6 +221,8 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
   constexpr bool kSplit = (EPI == kEpiStoreSplit);
   using L = GemmSmem<BN, CG, EW>;
   constexpr int S = L::kStages;
+  constexpr int kKBoxes = L::kKBoxes;
+  constexpr int kBlockK = L::kBlockK;
   constexpr int kTileM = kBlockM * CG;             // rows per tile (per CTA pair when CG = 2)
   const uint32_t crank = (CG == 2) ? cluster_ctarank() : 0u;  // 0 = leader
   const int tile0 = blockIdx.x / CG;               // both CTAs of a pair walk the same tiles
@@ -337,26 +348,26 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
             if (crank == 0) mbar_arrive_expect_tx(&full_bar[s], 2 * L::kStageBytes);
             const uint32_t bar = map_to_cta(smem_u32(&full_bar[s]), 0);
             if (second) {
-              tma_load_2d_pair(a_dst, &tmA0, bar, kb * kBlockK, a_row);
-              tma_load_2d_pair(b_dst, &tmB1, bar, kb * kBlockK, b1_row);
+              for (int h = 0; h < kKBoxes; ++h) tma_load_2d_pair(a_dst + h * (L::kABytes / kKBoxes), &tmA0, bar, kb * kBlockK + h * kBoxK, a_row);
+              for (int h = 0; h < kKBoxes; ++h) tma_load_2d_pair(b_dst + h * (L::kBBytes / kKBoxes), &tmB1, bar, kb * kBlockK + h * kBoxK, b1_row);
             } else if (kb < kb0) {
-              tma_load_2d_pair(a_dst, &tmA0, bar, kb * kBlockK, a_row);
-              tma_load_2d_pair(b_dst, &tmB0, bar, kb * kBlockK, b0_row);
+              for (int h = 0; h < kKBoxes; ++h) tma_load_2d_pair(a_dst + h * (L::kABytes / kKBoxes), &tmA0, bar, kb * kBlockK + h * kBoxK, a_row);
+              for (int h = 0; h < kKBoxes; ++h) tma_load_2d_pair(b_dst + h * (L::kBBytes / kKBoxes), &tmB0, bar, kb * kBlockK + h * kBoxK, b0_row);
             } else {
-              tma_load_2d_pair(a_dst, &tmA1, bar, (kb - kb0) * kBlockK, a_row);
-              tma_load_2d_pair(b_dst, &tmB1, bar, (kb - kb0) * kBlockK, b1_row);
+              for (int h = 0; h < kKBoxes; ++h) tma_load_2d_pair(a_dst + h * (L::kABytes / kKBoxes), &tmA1, bar, (kb - kb0) * kBlockK + h * kBoxK, a_row);
+              for (int h = 0; h < kKBoxes; ++h) tma_load_2d_pair(b_dst + h * (L::kBBytes / kKBoxes), &tmB1, bar, (kb - kb0) * kBlockK + h * kBoxK, b1_row);
             }
           } else {
             mbar_arrive_expect_tx(&full_bar[s], L::kStageBytes);
             if (second) {
-              tma_load_2d(a_dst, &tmA0, &full_bar[s], kb * kBlockK, a_row);
-              tma_load_2d(b_dst, &tmB1, &full_bar[s], kb * kBlockK, b1_row);
+              for (int h = 0; h < kKBoxes; ++h) tma_load_2d(a_dst + h * (L::kABytes / kKBoxes), &tmA0, &full_bar[s], kb * kBlockK + h * kBoxK, a_row);
+              for (int h = 0; h < kKBoxes; ++h) tma_load_2d(b_dst + h * (L::kBBytes / kKBoxes), &tmB1, &full_bar[s], kb * kBlockK + h * kBoxK, b1_row);
             } else if (kb < kb0) {
-              tma_load_2d(a_dst, &tmA0, &full_bar[s], kb * kBlockK, a_row);
-              tma_load_2d(b_dst, &tmB0, &full_bar[s], kb * kBlockK, b0_row);
+              for (int h = 0; h < kKBoxes; ++h) tma_load_2d(a_dst + h * (L::kABytes / kKBoxes), &tmA0, &full_bar[s], kb * kBlockK + h * kBoxK, a_row);
+              for (int h = 0; h < kKBoxes; ++h) tma_load_2d(b_dst + h * (L::kBBytes / kKBoxes), &tmB0, &full_bar[s], kb * kBlockK + h * kBoxK, b0_row);
             } else {
-              tma_load_2d(a_dst, &tmA1, &full_bar[s], (kb - kb0) * kBlockK, a_row);
-              tma_load_2d(b_dst, &tmB1, &full_bar[s], (kb - kb0) * kBlockK, b1_row);
+              for (int h = 0; h < kKBoxes; ++h) tma_load_2d(a_dst + h * (L::kABytes / kKBoxes), &tmA1, &full_bar[s], (kb - kb0) * kBlockK + h * kBoxK, a_row);
+              for (int h = 0; h < kKBoxes; ++h) tma_load_2d(b_dst + h * (L::kBBytes / kKBoxes), &tmB1, &full_bar[s], (kb - kb0) * kBlockK + h * kBoxK, b1_row);
             }
           }
         }
@@ -399,16 +410,19 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
           }
           tc_fence_after();
           const uint32_t a_addr = smem_u32(smem + s * L::kStageBytes);
-          const uint64_t da = make_smem_desc_sw128(a_addr);
-          const uint64_t db = make_smem_desc_sw128(a_addr + L::kABytes);
+          const uint64_t da0 = make_smem_desc_sw128(a_addr);
+          const uint64_t db0 = make_smem_desc_sw128(a_addr + L::kABytes);
 #pragma unroll
           for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-            // advancing 16 bf16 (32 bytes) along K inside the swizzle row: +2 in the
-            // descriptor's 16-byte address units
+            // box k / 4 of the stage (descriptor addresses are in 16-byte units); inside the box,
+            // advancing 16 bf16 (32 bytes) along K within the swizzle row is +2
+            constexpr int kPerBox = kBoxK / kUmmaK;
+            const uint64_t da = da0 + static_cast<uint64_t>((k / kPerBox) * (L::kABytes / kKBoxes / 16) + 2 * (k % kPerBox));
+            const uint64_t db = db0 + static_cast<uint64_t>((k / kPerBox) * (L::kBBytes / kKBoxes / 16) + 2 * (k % kPerBox));
             if constexpr (CG == 2)
-              umma_bf16_pair(d_tmem, da + 2u * k, db + 2u * k, idesc, ((kb - kb_lo) | k) != 0 ? 1u : 0u);
+              umma_bf16_pair(d_tmem, da, db, idesc, ((kb - kb_lo) | k) != 0 ? 1u : 0u);
             else
-              umma_bf16(d_tmem + (k % kChains) * BN, da + 2u * k, db + 2u * k, idesc,
+              umma_bf16(d_tmem + (k % kChains) * BN, da, db, idesc,
                         ((kb - kb_lo) | (k / kChains)) != 0 ? 1u : 0u);
           }
           // frees the stage (in both CTAs of a pair) once these MMAs have read it
