@@ -10,6 +10,7 @@ import os
 from ctypes import c_char_p, c_float, c_int, c_longlong, c_size_t, c_void_p
 
 LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libcdeep.so")
+CHECKS_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libcdeep_checks.so")
 
 ABI_VERSION = 3
 
@@ -19,6 +20,7 @@ SIGNATURES = {
     "cd_error_string": (c_char_p, [c_int]),
     "cd_last_cuda_error": (c_char_p, []),
     "cd_max_groups": (c_int, []),
+    "cd_checks_enabled": (c_int, []),
     "cd_splitk_workspace_bytes": (c_size_t, []),
     "cd_splitk_workspace_set": (c_int, [c_void_p, c_size_t, c_void_p]),
     "cd_splitk_ranges": (c_int, [c_int, c_int, c_int]),
@@ -85,24 +87,29 @@ class CdeepError(RuntimeError):
     """A libcdeep entry point returned a non-zero status."""
 
 
-def load() -> ctypes.CDLL:
-    """Loads the library once; raises when it is missing or its ABI version differs."""
-    global _lib
-    if _lib is not None:
-        return _lib
-    if not os.path.exists(LIB_PATH):
+def open_library(path: str) -> ctypes.CDLL:
+    """Opens one build of the library and binds every declared entry point."""
+    if not os.path.exists(path):
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m complexity_deep_b200.build` "
+            f"{path} is missing: build it with `python -m complexity_deep_b200.build` "
             "(nvcc, sm_100a). There is no CPU or PyTorch fallback for these kernels.")
-    lib = ctypes.CDLL(LIB_PATH)
+    lib = ctypes.CDLL(path)
     for name, (res, args) in SIGNATURES.items():
         fn = getattr(lib, name)  # AttributeError if a declared symbol is not exported
         fn.restype = res
         fn.argtypes = args
     if lib.cd_version() != ABI_VERSION:
         raise ImportError(f"libcdeep ABI {lib.cd_version()} != expected {ABI_VERSION}; rebuild")
-    _lib = lib
     return lib
+
+
+def load() -> ctypes.CDLL:
+    """Loads the library once; raises when it is missing or its ABI version differs.
+    CDEEP_CHECKS=1 in the environment selects the checking build (libcdeep_checks.so)."""
+    global _lib
+    if _lib is None:
+        _lib = open_library(CHECKS_LIB_PATH if os.environ.get("CDEEP_CHECKS") == "1" else LIB_PATH)
+    return _lib
 
 
 def check(status: int, what: str) -> None:

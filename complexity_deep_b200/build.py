@@ -12,8 +12,11 @@ import sys
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libcdeep.so")
+# the checking build: same sources with -DCDEEP_CHECKS (device-side validation of indices that
+# kernels read from device memory; see include/cdeep.h, cd_checks_enabled)
+CHECKS_LIB_PATH = os.path.join(PKG_DIR, "libcdeep_checks.so")
 SOURCES = ["api.cu", "gemm.cu", "route.cu", "rowwise.cu", "attention_decode.cu", "attention_prefill.cu", "pack.cu"]
-HEADERS = ["ptx.cuh", "gemm_sm100.cuh", "kernels.h", os.path.join("..", "..", "include", "cdeep.h")]
+HEADERS = ["ptx.cuh", "checks.cuh", "gemm_sm100.cuh", "kernels.h", os.path.join("..", "..", "include", "cdeep.h")]
 
 
 def _nvcc() -> str:
@@ -23,30 +26,35 @@ def _nvcc() -> str:
     raise RuntimeError("nvcc not found: libcdeep.so cannot be built")
 
 
-def is_stale() -> bool:
-    if not os.path.exists(LIB_PATH):
+def is_stale(checks: bool = False) -> bool:
+    lib = CHECKS_LIB_PATH if checks else LIB_PATH
+    if not os.path.exists(lib):
         return True
-    built = os.path.getmtime(LIB_PATH)
+    built = os.path.getmtime(lib)
     deps = [os.path.join(CSRC, s) for s in SOURCES + HEADERS]
     return any(os.path.exists(d) and os.path.getmtime(d) > built for d in deps)
 
 
-def _compile_one(nvcc: str, src: str, obj: str, verbose: bool):
+def _compile_one(nvcc: str, src: str, obj: str, verbose: bool, checks: bool = False):
     cmd = [nvcc, "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
            "-Xcompiler", "-fPIC", "-c", src, "-o", obj]
+    if checks:
+        cmd[1:1] = ["-DCDEEP_CHECKS"]
     if verbose:
         cmd[1:1] = ["-Xptxas", "-v"]
     return src, subprocess.run(cmd, cwd=CSRC, capture_output=True, text=True)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, checks: bool = False) -> str:
     """Compiles every CUDA source of the package (in parallel, one object per source, objects
-    of unchanged sources are re-used) and links them into one shared library."""
-    if not force and not is_stale():
-        return LIB_PATH
+    of unchanged sources are re-used) and links them into one shared library.  checks=True
+    builds the checking variant (libcdeep_checks.so) instead."""
+    lib_path = CHECKS_LIB_PATH if checks else LIB_PATH
+    if not force and not is_stale(checks):
+        return lib_path
     from concurrent.futures import ThreadPoolExecutor
     nvcc = _nvcc()
-    obj_dir = os.path.join(CSRC, "build")
+    obj_dir = os.path.join(CSRC, "build_checks" if checks else "build")
     os.makedirs(obj_dir, exist_ok=True)
     headers = [os.path.join(CSRC, h) for h in HEADERS]
     newest_header = max(os.path.getmtime(h) for h in headers if os.path.exists(h))
@@ -58,19 +66,19 @@ def build(force: bool = False, verbose: bool = False) -> str:
         if force or verbose or not os.path.exists(obj) or os.path.getmtime(obj) < src_time:
             jobs.append((src, obj))
     with ThreadPoolExecutor(max_workers=min(8, max(1, len(jobs)))) as pool:
-        results = list(pool.map(lambda j: _compile_one(nvcc, j[0], j[1], verbose), jobs))
+        results = list(pool.map(lambda j: _compile_one(nvcc, j[0], j[1], verbose, checks), jobs))
     for src, proc in results:
         if proc.returncode != 0:
             raise RuntimeError(f"nvcc failed on {src}:\n" + proc.stdout + proc.stderr)
         if verbose:
             sys.stderr.write(proc.stderr)
     link = subprocess.run([nvcc, "-shared", "-Xcompiler", "-fPIC", "-gencode",
-                           "arch=compute_100a,code=sm_100a", "-o", LIB_PATH] + objs,
+                           "arch=compute_100a,code=sm_100a", "-o", lib_path] + objs,
                           cwd=CSRC, capture_output=True, text=True)
     if link.returncode != 0:
         raise RuntimeError("link failed:\n" + link.stdout + link.stderr)
-    return LIB_PATH
+    return lib_path
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, checks="--checks" in sys.argv))

@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 #include "../../include/cdeep.h"
 #include "gemm_sm100.cuh"
+#include "checks.cuh"
 #include "kernels.h"
 
 namespace cdeep {
@@ -29,6 +30,7 @@ const char* cd_error_string(int status) {
     case CD_ERR_CUDA: return "CUDA call failed";
     case CD_ERR_UNSUPPORTED: return "unsupported shape";
     case CD_ERR_TIMEOUT: return "a kernel gave up on a bounded wait";
+    case CD_ERR_BOUNDS: return "checking build: a kernel met an index, address or segment table out of range";
     default: return "unknown status";
   }
 }
@@ -36,6 +38,8 @@ const char* cd_error_string(int status) {
 const char* cd_last_cuda_error(void) { return g_cuda_err; }
 
 int cd_max_groups(void) { return kMaxGroups; }
+
+int cd_checks_enabled(void) { return kChecks ? 1 : 0; }
 
 size_t cd_splitk_workspace_bytes(void) { return splitk_workspace_bytes(); }
 
@@ -306,6 +310,7 @@ int cd_moe_down(const void* h_routed, int I_e, const void* wd_routed, const void
   epi.ldo = H;
   epi.out_cols = H;
   epi.row_map = row_map;
+  epi.out_rows = T;
   epi.residual = residual;
   epi.ldr = H;
   epi.residual_lo = residual_lo;
@@ -381,6 +386,7 @@ int cd_moe_combine(const void* h_shared, int I_s, const void* wd_shared, const v
   epi.ldo = H;
   epi.out_cols = H;
   epi.row_map = row_map;
+  epi.out_rows = T;
   epi.residual = residual;
   epi.ldr = H;
   epi.residual_lo = residual_lo;

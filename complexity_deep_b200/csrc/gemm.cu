@@ -359,6 +359,7 @@ int launch_gemm(int M, int N, int num_groups, const int* seg_offsets, const Gemm
   p.ldo = epi.ldo;
   p.out_cols = epi.out_cols;
   p.row_map = epi.row_map;
+  p.out_rows = epi.out_rows;
   p.out_row_ptrs = epi.out_row_ptrs;
   p.residual = static_cast<const __nv_bfloat16*>(epi.residual);
   p.ldr = epi.ldr;

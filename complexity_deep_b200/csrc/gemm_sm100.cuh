@@ -24,6 +24,7 @@
 //   * plain projections with an optional residual (o_proj, lm_head).
 #pragma once
 #include <cuda_bf16.h>
+#include "checks.cuh"
 #include "ptx.cuh"
 
 namespace cdeep {
@@ -80,6 +81,7 @@ struct GemmParams {
   int ldo;
   int out_cols;            // valid output columns (N for store, N/2-ish width I for SwiGLU)
   const int* row_map;      // sorted row -> destination row (nullptr = identity)
+  int out_rows;            // rows of the destination (checking build: row_map entries must lie below; 0 = unknown)
   const long long* out_row_ptrs;  // sorted row -> ADDRESS of its destination row (overrides out /
                                   // row_map; rows may live in another GPU's peer-mapped memory)
   const __nv_bfloat16* residual;  // indexed like out (nullptr = none)
@@ -292,16 +294,23 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
   griddep_launch_dependents();
   if (warp == 2 && lane == 0) {
     int acc = 0;
+    bool bad = false;
     prefix[0] = 0;
     for (int g = 0; g < p.num_groups; ++g) {
       const int lo = p.seg_offsets ? p.seg_offsets[g] : 0;
       const int hi = p.seg_offsets ? p.seg_offsets[g + 1] : p.M;
+      if (kChecks && (lo < 0 || hi < lo || hi > p.M)) bad = true;
       seg[g] = lo;
       seg[g + 1] = hi;
       acc += ((hi - lo + kTileM - 1) / kTileM) * n_tiles;
       prefix[g + 1] = acc;
     }
     if (p.N2 > 0) prefix[p.num_groups + 1] = acc + ((p.M + kTileM - 1) / kTileM) * n_tiles2;
+    if (kChecks && bad) {
+      // checking build: a segment table that is not 0 <= s[0] <= s[1] <= ... <= M schedules nothing
+      atomicMax(p.status, kStatusBounds);
+      for (int g = 0; g <= p.num_groups + 1; ++g) prefix[g] = 0;
+    }
   }
   tc_fence_before();
   __syncthreads();
@@ -466,12 +475,23 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
       const uint32_t acc = tcount & 1u;
       const uint32_t acc_ph = (tcount >> 1) & 1u;
       const int r = c.m0 + static_cast<int>(crank) * kBlockM + quarter * 32 + lane;
-      const bool row_ok = r < c.row_end;
+      bool row_ok = r < c.row_end;
       int orow = 0;
       if constexpr (kStore) {
         orow = row_ok ? (p.row_map ? p.row_map[r] : r) : 0;
+        if (kChecks && row_ok && p.row_map && p.out_rows > 0 && !index_ok(orow, p.out_rows, p.status)) {
+          row_ok = false;   // checking build: a row whose destination is out of range is not stored
+          orow = 0;
+        }
       } else {
         orow = row_ok ? r : 0;
+      }
+      // destination row addresses when rows are pushed to arbitrary (peer) memory
+      const bool use_ptrs = kStore && p.out_row_ptrs != nullptr;
+      long long my_ptr = 0;
+      if (use_ptrs) {
+        my_ptr = row_ok ? p.out_row_ptrs[r] : 0;
+        if (kChecks && row_ok && !row_address_ok(my_ptr, p.status)) row_ok = false;
       }
       // destination rows in the coalesced mapping: it * 4 + lane / 8
       int crow[8];
@@ -481,11 +501,9 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
         crow[it] = __shfl_sync(0xffffffffu, orow, it * 4 + crow_l);
         cvalid |= (__shfl_sync(0xffffffffu, row_ok ? 1 : 0, it * 4 + crow_l) ? 1u : 0u) << it;
       }
-      // destination row addresses when rows are pushed to arbitrary (peer) memory
       long long cptr[8];
-      const bool use_ptrs = kStore && p.out_row_ptrs != nullptr;
       if (use_ptrs) {
-        const long long mine = row_ok ? p.out_row_ptrs[r] : 0;
+        const long long mine = my_ptr;
 #pragma unroll
         for (int it = 0; it < 8; ++it) {
           const unsigned lo = __shfl_sync(0xffffffffu, static_cast<unsigned>(mine), it * 4 + crow_l);

@@ -104,6 +104,7 @@ struct GemmEpilogueArgs {
   int ldo;
   int out_cols;
   const int* row_map;
+  int out_rows;            // rows of the destination buffer (checking build: bound of row_map entries; 0 = unknown)
   const long long* out_row_ptrs;  // per sorted row: address of its destination row (may be peer memory)
   const void* residual;
   int ldr;

@@ -12,6 +12,7 @@
 #include <cstdint>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include "checks.cuh"
 #include "kernels.h"
 
 namespace cdeep {
@@ -51,7 +52,7 @@ __global__ void __launch_bounds__(kNormWarps * 32)
 rmsnorm_rows_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
                     const __nv_bfloat16* __restrict__ w, float eps,
                     __nv_bfloat16* __restrict__ sum_out, __nv_bfloat16* __restrict__ out,
-                    const int* __restrict__ dst_rows, int T, int H) {
+                    const int* __restrict__ dst_rows, int T, int H, int* status) {
   griddep_wait();               // the previous kernel's writes are visible from here
   griddep_launch_dependents();  // the next kernel may be scheduled
   const int row = blockIdx.x * kNormWarps + (threadIdx.x >> 5);
@@ -107,6 +108,7 @@ rmsnorm_rows_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
   ss = warp_sum(ss);
   const float rstd = rsqrtf(ss / static_cast<float>(H) + eps);
   const int orow = dst_rows ? dst_rows[row] : row;
+  if (kChecks && dst_rows && !index_ok(orow, T, status)) return;   // checking build: row not stored
   uint4* orw = reinterpret_cast<uint4*>(out + static_cast<size_t>(orow) * H);
   const uint4* wr = reinterpret_cast<const uint4*>(w);
 #pragma unroll
@@ -136,7 +138,7 @@ __global__ void __launch_bounds__(128)
 rmsnorm_generic_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
                        const __nv_bfloat16* __restrict__ w, float eps,
                        __nv_bfloat16* __restrict__ sum_out, __nv_bfloat16* __restrict__ out,
-                       const int* __restrict__ dst_rows, int T, int H, int split) {
+                       const int* __restrict__ dst_rows, int T, int H, int split, int* status) {
   griddep_wait();               // the previous kernel's writes are visible from here
   griddep_launch_dependents();  // the next kernel may be scheduled
   __shared__ float s_part[4];
@@ -161,6 +163,7 @@ rmsnorm_generic_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
   const float tot = s_part[0] + s_part[1] + s_part[2] + s_part[3];
   const float rstd = rsqrtf(tot / static_cast<float>(H) + eps);
   const int orow = dst_rows ? dst_rows[row] : row;
+  if (kChecks && dst_rows && !index_ok(orow, T, status)) return;   // checking build: row not stored
   for (int c = threadIdx.x; c < H; c += blockDim.x) {
     float v = __bfloat162float(xr[c]);
     if (rr && split) v += __bfloat162float(rr[c]);
@@ -172,14 +175,16 @@ rmsnorm_generic_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
 // out[j, :] = x[src_rows[j], :]
 __global__ void __launch_bounds__(256)
 gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ src_rows,
-                   __nv_bfloat16* __restrict__ out, int T, int H) {
+                   __nv_bfloat16* __restrict__ out, int T, int H, int* status) {
   griddep_wait();               // the previous kernel's writes are visible from here
   griddep_launch_dependents();  // the next kernel may be scheduled
   const int warps_per_block = blockDim.x >> 5;
   const int j = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
   if (j >= T) return;
   const int lane = threadIdx.x & 31;
-  const size_t src = static_cast<size_t>(src_rows[j]) * H;
+  const int src_row = src_rows[j];
+  if (kChecks && !index_ok(src_row, T, status)) return;   // checking build: row not copied
+  const size_t src = static_cast<size_t>(src_row) * H;
   const size_t dst = static_cast<size_t>(j) * H;
   if ((H & 7) == 0) {
     const uint4* s = reinterpret_cast<const uint4*>(x + src);
@@ -480,11 +485,12 @@ cudaError_t launch_rmsnorm(const void* x, const void* residual, const void* weig
   auto wb = static_cast<const __nv_bfloat16*>(weight);
   auto sb = static_cast<__nv_bfloat16*>(sum_out);
   auto ob = static_cast<__nv_bfloat16*>(out);
+  int* status = kChecks ? device_status_word() : nullptr;
   if ((H & 255) == 0 && H <= kMaxVec * 256) {
     const int blocks = (T + kNormWarps - 1) / kNormWarps;
     auto go = [&](auto kern) {
       return launch_kernel(kern, dim3(blocks), dim3(kNormWarps * 32), 0, stream, xb, rb, wb, eps, sb,
-                           ob, dst_rows, T, H);
+                           ob, dst_rows, T, H, status);
     };
     switch (H >> 8) {   // hidden sizes 768 / 1024 / 2048 get their own instantiation (fewer registers)
       case 3: return split ? go(rmsnorm_rows_kernel<true, 3>) : go(rmsnorm_rows_kernel<false, 3>);
@@ -494,7 +500,7 @@ cudaError_t launch_rmsnorm(const void* x, const void* residual, const void* weig
     }
   } else {
     return launch_kernel(rmsnorm_generic_kernel, dim3(T), dim3(128), 0, stream, xb, rb, wb, eps, sb,
-                         ob, dst_rows, T, H, split ? 1 : 0);
+                         ob, dst_rows, T, H, split ? 1 : 0, status);
   }
   return cudaGetLastError();
 }
@@ -505,7 +511,8 @@ cudaError_t launch_gather_rows(const void* x, const int* src_rows, void* out, in
   const int wpb = 8;
   return launch_kernel(gather_rows_kernel, dim3((T + wpb - 1) / wpb), dim3(wpb * 32), 0, stream,
                        static_cast<const __nv_bfloat16*>(x), src_rows,
-                       static_cast<__nv_bfloat16*>(out), T, H);
+                       static_cast<__nv_bfloat16*>(out), T, H,
+                       kChecks ? device_status_word() : nullptr);
 }
 
 cudaError_t launch_push_rows(const void* x, const int* src_rows, const int* offsets,

@@ -100,6 +100,9 @@ def status_fetch() -> int:
     lib = _lib.load()
     st = ctypes.c_int(0)
     _lib.check(lib.cd_status_fetch(ctypes.byref(st)), "cd_status_fetch")
+    if st.value == 4:
+        raise _lib.CdeepError("checking build: a libcdeep kernel met an index, address or segment "
+                              "table out of range and skipped the access")
     if st.value != 0:
         raise _lib.CdeepError("a libcdeep kernel gave up on a bounded wait (pipeline error)")
     return st.value

@@ -32,6 +32,8 @@ extern "C" {
 #define CD_ERR_CUDA 2         /* a CUDA runtime / driver call failed; see cd_last_cuda_error */
 #define CD_ERR_UNSUPPORTED 3  /* shape outside what the kernels implement */
 #define CD_ERR_TIMEOUT 4      /* a kernel gave up on a bounded wait (reported by cd_status_fetch) */
+#define CD_ERR_BOUNDS 5       /* checking build only: an index / address / segment table read from device
+                                 memory was out of range (reported by cd_status_fetch) */
 
 /* ABI version of this header (bumped on any signature change; currently 3). */
 int cd_version(void);
@@ -59,8 +61,18 @@ int cd_splitk_workspace_set(void* workspace, size_t bytes, void* stream);
 /* Number of K ranges cd_linear (or cd_mu_proj; cd_mu_qkv with K = the sum of its two K extents)
  * would use for a [T, K] x [N, K]^T call on the current device as it is set up now (1 = unsplit). */
 int cd_splitk_ranges(int T, int K, int N);
-/* Synchronises the current device, copies the kernels' status word to *h_status
- * (0 = every bounded wait completed) and clears it. */
+/* 1 when this library is the checking build (libcdeep_checks.so, compiled with -DCDEEP_CHECKS),
+ * else 0.  The checking build validates what its kernels read from device memory before using it
+ * as an index or address — row_map of cd_moe_down / cd_moe_combine (entries in [0, T)), dst_rows of
+ * cd_rmsnorm / cd_rmsnorm_split and src_rows of cd_gather_rows (in [0, T)), out_row_ptrs of
+ * cd_moe_down_push (non-null, 16-byte aligned), seg_offsets of every grouped call
+ * (0 <= s[0] <= ... <= s[G] <= T) — and, on a violation, skips the access (a bad segment table:
+ * the whole launch) and raises the status word to 4.  It is the stand-in for a memory checker on
+ * machines where none may run; the normal build trusts its caller. */
+int cd_checks_enabled(void);
+/* Synchronises the current device, copies the kernels' status word to *h_status and clears it.
+ * 0 = nothing to report; 1 = a bounded pipeline wait ran out; 2 = cd_peer_barrier ran out;
+ * 4 = the checking build met an index out of range (the largest value seen is kept). */
 int cd_status_fetch(int* h_status);
 
 /* Self-test of the kernels' failure detection (no counterpart in the reference).  Every wait of
@@ -262,9 +274,9 @@ int cd_moe_combine(const void* h_shared, int I_s, const void* wd_shared, const v
                    void* out_lo, int T, int H, void* stream);
 
 /* ---- expert-parallel exchange by peer stores --------------------------------------------------
- * (The reference has no distributed code; these two entry points replace the NCCL all-to-alls
- * of the expert-parallel layer with stores into peer-mapped memory, issued by the kernels that
- * produce the rows.  The caller provides peer-mapped buffers, e.g. CUDA IPC or symmetric
+ * (The reference has no distributed code; the entry points of this section replace the NCCL
+ * all-to-alls of the expert-parallel layer with stores into peer-mapped memory, issued by the
+ * kernels that produce the rows.  The caller provides peer-mapped buffers, e.g. CUDA IPC or symmetric
  * memory, and orders the phases with a barrier across the GPUs.)
  *
  * cd_push_rows: sorted row j (= x[src_rows[j]], or x[j] when src_rows is NULL) of expert e

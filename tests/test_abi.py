@@ -24,6 +24,10 @@ def test_library_builds_and_exports_header_symbols():
         assert hasattr(lib, name), f"{name} declared in cdeep.h but not exported"
     # the ctypes table binds exactly the declared entry points
     assert sorted(_lib.SIGNATURES) == declared
+    # the checking build exports the same entry points and says what it is
+    checks = _lib.open_library(build.build(checks=True))
+    assert checks.cd_checks_enabled() == 1 and _lib.load().cd_checks_enabled() == 0
+    assert checks.cd_error_string(5).startswith(b"checking build")
 
 
 def test_version_and_error_strings():
