@@ -24,6 +24,7 @@ SIGNATURES = {
     "cd_splitk_workspace_bytes": (c_size_t, []),
     "cd_splitk_workspace_set": (c_int, [c_void_p, c_size_t, c_void_p]),
     "cd_splitk_ranges": (c_int, [c_int, c_int, c_int]),
+    "cd_splitk_config": (c_int, [c_int]),
     "cd_status_fetch": (c_int, [ctypes.POINTER(c_int)]),
     "cd_selftest_wait_timeout": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "cd_route_workspace_bytes": (c_size_t, [c_int, c_int]),

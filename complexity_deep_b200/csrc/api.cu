@@ -43,6 +43,8 @@ int cd_checks_enabled(void) { return kChecks ? 1 : 0; }
 
 size_t cd_splitk_workspace_bytes(void) { return splitk_workspace_bytes(); }
 
+int cd_splitk_config(int flags) { return splitk_config(flags); }
+
 int cd_splitk_ranges(int T, int K, int N) { return splitk_ranges_dense(T, N, K); }
 
 int cd_splitk_workspace_set(void* workspace, size_t bytes, void* stream) {

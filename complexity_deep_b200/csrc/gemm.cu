@@ -65,6 +65,8 @@ constexpr int kSkMaxTiles = kSkCounterBytes / 4;
 constexpr int kSkMinBlocksPerSplit = 16; // 64-element boxes of K per range
 constexpr int kSkMinBlocks = 48;         // shortest K loop (in boxes) that is split at all
 constexpr int kSkMaxSplits = 8;
+// which forms of split-K a launch may take: bit 0 the cluster form, bit 1 the workspace form
+int g_splitk_flags = 3;
 constexpr int kMaxDevices = 64;
 DeviceInfo g_dev[kMaxDevices];
 std::mutex g_mu;
@@ -76,6 +78,8 @@ cudaError_t launch_one(int grid, const CUtensorMap& a0, const CUtensorMap& b0,
                        const CUtensorMap& a1, const CUtensorMap& b1, const GemmParams& p,
                        DeviceInfo& di, cudaStream_t stream) {
   constexpr int bi = (BN == 256) ? 3 : (BN == 128) ? 2 : (BN == 64) ? 1 : 0;
+  // CTA pairs are clusters of 2; the cluster form of split-K launches clusters of `splits` CTAs
+  const unsigned cluster = (CG == 2) ? 2u : (p.sk_cluster ? static_cast<unsigned>(p.splits) : 1u);
   auto kern = gemm_bf16_sm100_kernel<BN, EPI, CG>;
   constexpr int smem = GemmSmem<BN, CG, gemm_epi_warps<BN, EPI>()>::kDynamic;
   if (!di.attr_set[bi][EPI][CG - 1]) {
@@ -90,7 +94,7 @@ cudaError_t launch_one(int grid, const CUtensorMap& a0, const CUtensorMap& b0,
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = CG;
+  attr[0].val.clusterDim.x = cluster;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   // the kernel waits for its predecessor itself (griddep_wait) after its set-up
@@ -183,7 +187,7 @@ int choose_cta_group(int M, int block_n, int sm_count) {
 // workspace, single CTAs and a tile of at most 128 columns.  Returns the number of K ranges.
 int plan_splits(const DeviceInfo& di, int M, int N, int block_n, int kb_total, int k_boxes) {
   const long long tiles = static_cast<long long>((M + kBlockM - 1) / kBlockM) * ((N + block_n - 1) / block_n);
-  if (!di.sk_ws || block_n > 128 || tiles > kSkMaxTiles || tiles * 2 > di.sm_count ||
+  if (!(g_splitk_flags & 2) || !di.sk_ws || block_n > 128 || tiles > kSkMaxTiles || tiles * 2 > di.sm_count ||
       kb_total * k_boxes < kSkMinBlocks)
     return 1;
   int splits = static_cast<int>(di.sm_count / tiles);
@@ -192,6 +196,43 @@ int plan_splits(const DeviceInfo& di, int M, int N, int block_n, int kb_total, i
   const size_t need =
       kSkCounterBytes + static_cast<size_t>(tiles) * splits * kBlockM * block_n * sizeof(float);
   return (splits < 2 || need > di.sk_bytes) ? 1 : splits;
+}
+
+// Cluster split-K for a dense store-epilogue call of few rows: 128-wide tiles (the widest whose
+// MMA costs the issuing thread no more than a narrow one) and 4 or 2 K ranges per tile, when that
+// beats the narrowest-tile choice.  Times in ns from the measured model of one launch:
+// fixed 4.9 us, 0.21 us (tiles up to 64 wide) or 0.29 us (128 wide) per 64 elements of K on the
+// busiest SM, 4.4 us (4 ranges) or 5.1 us (2 ranges) for the exchange of partial tiles inside the
+// cluster: writing the partial tile, the barrier across the cluster (which also absorbs the skew
+// between its CTAs), the remote reads, the closing cluster barrier.  With that the form pays from
+// K = 3072: K = 4096 18.5 -> 14.3 us, K = 5632 23.6 -> 16.0 us (32 rows, 2048 columns).
+struct ClusterSplitPlan {
+  int splits;   // 1 = keep the unsplit launch
+};
+ClusterSplitPlan plan_cluster_split(int M, int N, int kb64, int unsplit_bn, int sm_count) {
+  // CDEEP_CLUSTER_SPLITK=0 turns the form off, =2 / =4 force that many ranges (tuning aid)
+  static const int forced = [] {
+    const char* e = getenv("CDEEP_CLUSTER_SPLITK");
+    return e ? atoi(e) : -1;
+  }();
+  ClusterSplitPlan plan{1};
+  if (forced == 0 || !(g_splitk_flags & 1)) return plan;
+  const long long m_tiles = (M + kBlockM - 1) / kBlockM;
+  auto tiles = [&](int bn) { return m_tiles * ((N + bn - 1) / bn); };
+  const long long waves = (tiles(unsplit_bn) + sm_count - 1) / sm_count;
+  const long long unsplit_ns = 4900 + waves * kb64 * (unsplit_bn <= 64 ? 210 : (unsplit_bn == 128 ? 290 : 330));
+  long long best = unsplit_ns;
+  for (int s : {4, 2}) {
+    if (forced > 0 && s != forced) continue;
+    if (tiles(128) * s > sm_count - sm_count / 8) continue;   // one wave, with room to place whole clusters
+    if (kb64 / s < 4) continue;
+    const long long ns = 4900 + (s == 4 ? 4400 : 5100) + 310LL * ((kb64 + s - 1) / s);
+    if (ns + 500 < best) {
+      best = ns;
+      plan.splits = s;
+    }
+  }
+  return plan;
 }
 
 }  // namespace
@@ -246,6 +287,13 @@ int* device_status_word() {
   return di ? di->status : nullptr;
 }
 
+int splitk_config(int flags) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  const int old = g_splitk_flags;
+  if (flags >= 0) g_splitk_flags = flags & 3;
+  return old;
+}
+
 size_t splitk_workspace_bytes() {
   // the counters, then one fp32 partial tile (128 x 128 at most) for every CTA of a full grid
   return kSkCounterBytes + static_cast<size_t>(current_sm_count()) * kBlockM * 128 * sizeof(float);
@@ -274,6 +322,10 @@ int splitk_ranges_dense(int M, int N, int K) {
   if (!di || M <= 0 || N <= 0 || K <= 0) return 1;
   const int bn = store_block_n_impl(M, N, 1, di->sm_count);
   if (choose_cta_group(M, bn, di->sm_count) != 1) return 1;
+  if (bn <= 128 && choose_cta_group(M, 128, di->sm_count) == 1) {
+    const int cs = plan_cluster_split(M, N, (K + kBoxK - 1) / kBoxK, bn, di->sm_count).splits;
+    if (cs > 1) return cs;
+  }
   const int kblock = kBoxK * gemm_k_boxes(bn, 1);
   return plan_splits(*di, M, N, bn, (K + kblock - 1) / kblock, gemm_k_boxes(bn, 1));
 }
@@ -319,6 +371,14 @@ int launch_gemm(int M, int N, int num_groups, const int* seg_offsets, const Gemm
   DeviceInfo* di = device_info(&st);
   if (!di) return st;
 
+  // dense store-epilogue calls of few rows may take the cluster form of split-K (128-wide tiles)
+  int csk_splits = 1;
+  if (num_groups == 1 && !second && epi.kind == kEpiStore && !epi.rope_cos && !epi.selftest_stall &&
+      !epi.out_row_ptrs && block_n <= 128 && choose_cta_group(M, 128, di->sm_count) == 1) {
+    const int kb64 = (op0.K + kBoxK - 1) / kBoxK + (op1 ? (op1->K + kBoxK - 1) / kBoxK : 0);
+    csk_splits = plan_cluster_split(M, N, kb64, block_n, di->sm_count).splits;
+    if (csk_splits > 1) block_n = 128;
+  }
   const int cg = choose_cta_group(M, block_n, di->sm_count);
   const int b_box = block_n / cg;
   CUtensorMap a0, b0, a1, b1;
@@ -407,8 +467,13 @@ int launch_gemm(int M, int N, int num_groups, const int* seg_offsets, const Gemm
     const int kb_total = (op0.K + kblock - 1) / kblock + (op1 ? (op1->K + kblock - 1) / kblock : 0);
     const bool eligible = cg == 1 && num_groups == 1 && !second && !epi.rope_cos &&
                           !epi.selftest_stall && (epi.kind != kEpiSwiGLU || block_n >= 64);
-    const int splits = eligible ? plan_splits(*di, M, N, block_n, kb_total, gemm_k_boxes(block_n, cg)) : 1;
-    if (splits > 1) {
+    const int splits = (eligible && csk_splits == 1)
+                           ? plan_splits(*di, M, N, block_n, kb_total, gemm_k_boxes(block_n, cg)) : 1;
+    if (csk_splits > 1) {
+      p.splits = csk_splits;
+      p.sk_cluster = 1;
+      units = ((M + kBlockM - 1) / kBlockM) * n_tiles * csk_splits;   // one unit per CTA, clusters of `splits`
+    } else if (splits > 1) {
       p.splits = splits;
       p.sk_counters = static_cast<int*>(di->sk_ws);
       p.sk_scratch = reinterpret_cast<float*>(static_cast<char*>(di->sk_ws) + kSkCounterBytes);

@@ -119,6 +119,12 @@ struct GemmParams {
   int splits;              // 1 = off
   float* sk_scratch;       // [tiles * splits][128][BN] fp32
   int* sk_counters;        // [tiles], zero between launches
+  // split-K inside a cluster (store epilogues, BN / splits a multiple of 32): the launch has
+  // tiles x splits CTAs in clusters of `splits`; the CTAs of a cluster hold the partial tiles of
+  // one output tile in their shared memory, CTA s reduces and stores the columns
+  // [s * BN / splits, (s + 1) * BN / splits) of it, reading the others' partials through
+  // distributed shared memory.  No workspace, no atomics.
+  int sk_cluster;          // 1 = the cluster form (sk_scratch / sk_counters unused)
   // self-test of the failure path: with `selftest_stall` the producer issues no loads, so the
   // pipeline waits run into `wait_limit_ns` (0 = the default limit) and the kernel must leave
   // cleanly with the status word raised
@@ -147,7 +153,7 @@ struct GemmSmem {
   // after the tiles: epilogue staging, barriers, TMEM base, abort flag, schedule tables
   static constexpr int kEpiOff = kTileBytes;
   static constexpr int kBarOff = kEpiOff + kEpiBytes;
-  static constexpr int kNumBars = 2 * kStages + 4;
+  static constexpr int kNumBars = 2 * kStages + 5;   // full, empty, tmem_full[2], tmem_empty[2], split-K
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
   static constexpr int kPrefixOff = kMiscOff + 16;
   static constexpr int kSegOff = kPrefixOff + (kMaxGroups + 2) * 4;
@@ -247,6 +253,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
   uint64_t* empty_bar = full_bar + S;
   uint64_t* tmem_full = empty_bar + S;   // [2]
   uint64_t* tmem_empty = tmem_full + 2;  // [2]
+  uint64_t* sk_bar = tmem_empty + 2;     // cluster split-K: every partial tile of the cluster is written
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(smem + L::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kMiscOff + 4);
   int* prefix = reinterpret_cast<int*>(smem + L::kPrefixOff);
@@ -271,6 +278,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
       mbar_init(&tmem_full[a], 1);
       mbar_init(&tmem_empty[a], EW * CG);  // one arrival per epilogue warp (of both CTAs)
     }
+    mbar_init(sk_bar, (p.splits > 1 ? p.splits : 1) * EW);  // one arrival per epilogue warp of the cluster
     *abort_flag = 0;
     *reinterpret_cast<int*>(smem + L::kMiscOff + 8) = 0;
     *reinterpret_cast<int*>(smem + L::kMiscOff + 12) = 0;
@@ -314,14 +322,16 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
   }
   tc_fence_before();
   __syncthreads();
+  constexpr bool kSplitK = (CG == 1 && BN <= 128);
+  const bool csk = kSplitK && kStore && p.splits > 1 && p.sk_cluster != 0;   // uniform over the launch
   if constexpr (CG == 2) cluster_sync_all();  // the peer's barriers exist before anyone signals them
+  else if (csk) cluster_sync_all();
   tc_fence_after();
 
   const uint32_t tmem_base = *tmem_base_slot;
   const int total_tiles = prefix[p.num_groups + (p.N2 > 0 ? 1 : 0)];
   // split-K only in the narrow single-CTA instantiations (the few-row problems it is for never
   // take the 256-wide tile, whose epilogue has no registers to spare)
-  constexpr bool kSplitK = (CG == 1 && BN <= 128);
   const int splits = (kSplitK && p.splits > 1) ? p.splits : 1;
   const int total_units = total_tiles * splits;
 
@@ -514,8 +524,10 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
       // output columns of this tile and the number of sub-tiles (64 columns; 32 for the split
       // store, whose staged rows hold 64 bytes of high parts followed by 64 bytes of low parts)
       constexpr int kSubCols = kSplit ? 32 : kEpiCols;
-      const int ocol_base = kStore ? c.n0 : c.n0 / 2;
-      const int ocol_span = kStore ? BN : BN / 2;
+      // cluster split-K: this CTA finishes only its slice of the tile's columns
+      const int sk_col_lo = csk ? sp * (BN / splits) : 0;
+      const int ocol_base = (kStore ? c.n0 : c.n0 / 2) + sk_col_lo;
+      const int ocol_span = csk ? BN / splits : (kStore ? BN : BN / 2);
       const int ocols = min(ocol_span, out_cols - ocol_base);
       const int nsub = (ocols + kSubCols - 1) / kSubCols;
       const int col_end = ocol_base + ocols;   // one past the last output column of this tile
@@ -562,7 +574,85 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
 
       // split-K: hand this CTA's partial tile over; only the CTA that arrives last goes on
       const float* sk_row = nullptr;    // this lane's row in partial 0 of the tile (last CTA only)
-      if (splits > 1) {
+      uint32_t sk_part = 0;             // cluster form: shared-memory address of this lane's partial row
+      constexpr uint32_t kPartMask = (BN / 4 - 1) & 31;   // 16-byte chunks of a row are XOR-swizzled by row
+      if (csk) {
+        // this thread's accumulator row, all BN columns, to the start of the (now idle) tile ring
+        const uint32_t prow = static_cast<uint32_t>(quarter * 32 + lane);
+        sk_part = smem_u32(smem) + prow * (BN * 4);
+#pragma unroll 1
+        for (int cc = 0; cc < BN / 32; ++cc) {
+          uint32_t v[32];
+          tmem_ld32(t_row + cc * 32, v);
+          if constexpr (kChains == 2) {
+            uint32_t v2[32];
+            tmem_ld32(t_row + BN + cc * 32, v2);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(v2[j]));
+          }
+          tmem_ld_wait();
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const uint32_t chunk = static_cast<uint32_t>(cc * 8 + q);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(
+                             sk_part + ((chunk ^ (prow & kPartMask)) << 4)),
+                         "r"(v[4 * q]), "r"(v[4 * q + 1]), "r"(v[4 * q + 2]), "r"(v[4 * q + 3])
+                         : "memory");
+          }
+        }
+        fence_acq_rel_cluster();
+        __syncwarp();
+        if (lane == 0) {
+          for (int q = 0; q < splits; ++q)
+            mbar_arrive_cluster(map_to_cta(smem_u32(sk_bar), static_cast<uint32_t>(q)));
+        }
+        if (!mbar_wait_cluster(sk_bar, 0, abort_flag, wait_limit)) {
+          ok = false;
+          break;
+        }
+        fence_acq_rel_cluster();
+        {
+          // Sum this CTA's column slice over the partial tiles of the cluster, in rank order, and
+          // leave the sums in place of the slice in this CTA's own partial tile (nobody else
+          // reads those columns of it).  Remote shared memory is read in whole 128-byte row
+          // pieces: `cpr` lanes cover the slice of one row, a warp instruction covers 32 / cpr
+          // rows (a lane-per-row pattern costs 32 remote transactions per instruction: 7 us).
+          const uint32_t cpr = static_cast<uint32_t>(BN / splits) >> 2;   // 16-byte chunks per row slice: 8 or 16
+          const uint32_t rpl = 32u / cpr;
+          const uint32_t chunk = (static_cast<uint32_t>(sk_col_lo) >> 2) + (static_cast<uint32_t>(lane) % cpr);
+          const uint32_t ring = smem_u32(smem);
+          // two row groups per round, so eight remote loads are in flight before the first is used
+          for (uint32_t it = 0; it < 32u / rpl; it += 2) {
+            uint32_t addr[2];
+            float4 f[2][4];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const uint32_t row = static_cast<uint32_t>(quarter * 32) + (it + h) * rpl + static_cast<uint32_t>(lane) / cpr;
+              addr[h] = ring + row * (BN * 4) + ((chunk ^ (row & kPartMask)) << 4);
+#pragma unroll
+              for (int q = 0; q < 4; ++q)
+                if (q < splits) f[h][q] = ld_shared_cluster_f4(map_to_cta(addr[h], static_cast<uint32_t>(q)));
+            }
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              float4 a = f[h][0];
+#pragma unroll
+              for (int q = 1; q < 4; ++q)
+                if (q < splits) { a.x += f[h][q].x; a.y += f[h][q].y; a.z += f[h][q].z; a.w += f[h][q].w; }
+              asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr[h]), "f"(a.x), "f"(a.y),
+                           "f"(a.z), "f"(a.w)
+                           : "memory");
+            }
+          }
+          __syncwarp();
+        }
+        if (has_res && ehalf < nsub) {
+          fetch_residual(0);
+          if (ehalf + kEpiHalves < nsub) fetch_residual(1);
+        }
+      } else if (splits > 1) {
         constexpr int kTileFloats = kBlockM * BN;
         float* mine = p.sk_scratch + (static_cast<size_t>(t) * splits + sp) * kTileFloats +
                       (quarter * 32 + lane) * BN;
@@ -628,6 +718,23 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
         float a[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) a[j] = 0.f;
+        if (csk) {
+          // 32 columns of this CTA's slice, already summed over the cluster (see above)
+          const uint32_t prow = static_cast<uint32_t>(quarter * 32 + lane);
+          const uint32_t chunk0 = static_cast<uint32_t>(sk_col_lo + col) >> 2;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            float4 f;
+            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                         : "=f"(f.x), "=f"(f.y), "=f"(f.z), "=f"(f.w)
+                         : "r"(sk_part + (((chunk0 + q) ^ (prow & kPartMask)) << 4))
+                         : "memory");
+            a[4 * q] = f.x; a[4 * q + 1] = f.y; a[4 * q + 2] = f.z; a[4 * q + 3] = f.w;
+          }
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(a[j]);
+          return;
+        }
         for (int sidx = 0; sidx < splits; ++sidx) {
           const float4* src = reinterpret_cast<const float4*>(sk_row + static_cast<size_t>(sidx) * (kBlockM * BN) + col);
 #pragma unroll
@@ -783,7 +890,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
             __syncwarp();
           }
           tmem_ld_wait();
-          if (sk_row) sk_sum(sub * 32, v);
+          if (sk_row || csk) sk_sum(sub * 32, v);
           const bool has_lo = p.residual_lo != nullptr;
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
@@ -879,7 +986,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
               __syncwarp();
             }
             tmem_ld_wait();
-            if (sk_row) sk_sum(sub * 64 + hh * 32, v);
+            if (sk_row || csk) sk_sum(sub * 64 + hh * 32, v);
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
               const int col = colh + q * 8;
@@ -990,6 +1097,7 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
   tc_fence_before();
   __syncthreads();
   if constexpr (CG == 2) cluster_sync_all();  // the leader's MMAs read the peer's memory until here
+  else if (csk) cluster_sync_all();           // the cluster's CTAs read each other's partial tiles until here
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();

@@ -63,7 +63,8 @@ cudaError_t launch_qk_norm_rope(void* qkv, const void* q_w, const void* k_w, con
 // split-K workspace of the current device (gemm.cu)
 size_t splitk_workspace_bytes();
 int splitk_workspace_set(void* ws, size_t bytes, cudaStream_t stream);
-int splitk_ranges_dense(int M, int N, int K);   // K ranges a dense store-epilogue call would use now
+int splitk_ranges_dense(int M, int N, int K);
+int splitk_config(int flags);   // sets which forms of split-K may be used (negative: query); returns the previous flags   // K ranges a dense store-epilogue call would use now
 
 // Encodes a CUtensorMap (passed as void*) for a 2-D bf16 tensor [rows, cols] with `ld` elements
 // between rows, boxes of [box_rows, 64 columns], 128-byte swizzle, zero fill out of bounds.

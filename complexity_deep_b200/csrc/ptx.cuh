@@ -276,6 +276,48 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
                : "memory");
 }
+// Bounded wait on a barrier of THIS CTA that threads of other CTAs of the cluster arrive on after
+// writing shared memory which this CTA then reads (acquire at cluster scope).
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity,
+                                                  volatile int* abort_flag, uint64_t limit_ns) {
+  uint64_t t0 = 0;
+  uint32_t spins = 0;
+  while (true) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred P;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 P, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if ((++spins & 0xffu) == 0) {
+      if (*abort_flag) return false;
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > limit_ns) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void fence_acq_rel_cluster() {
+  asm volatile("fence.acq_rel.cluster;" ::: "memory");
+}
+// 16 bytes from the shared memory of any CTA of the cluster (address from map_to_cta)
+__device__ __forceinline__ float4 ld_shared_cluster_f4(uint32_t cluster_addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(cluster_addr)
+               : "memory");
+  return v;
+}
 // Tiled load into THIS CTA's shared memory whose byte count is credited to a barrier given
 // as a cluster address (the leader's), so one barrier collects the loads of both CTAs.
 __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* m,

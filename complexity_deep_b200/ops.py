@@ -594,6 +594,12 @@ def split_k(enable: bool = True, device: Optional[torch.device] = None) -> None:
             _SPLIT_K_WS[dev.index] = None      # stays off: the automatic registration skips this device
 
 
+def split_k_config(flags: int = -1) -> int:
+    """Which forms of split-K the few-row projections may take (cd_splitk_config): bit 0 the
+    cluster form, bit 1 the workspace form; negative = query.  Returns the previous flags."""
+    return _lib.load().cd_splitk_config(int(flags))
+
+
 def _split_k_auto(x: torch.Tensor) -> None:
     # first few-row projection on a device: register the workspace (not while a graph is being
     # captured; the model's warm-up pass before the capture comes through here)

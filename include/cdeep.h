@@ -46,16 +46,24 @@ const char* cd_last_cuda_error(void);
  * cd_last_cuda_error) beyond it.  The dispatch entry points accept up to 256 experts. */
 int cd_max_groups(void);
 /* Split-K for projections of few rows (decode; no counterpart in the reference).  A dense
- * projection (cd_linear, cd_mu_qkv, cd_mu_proj, cd_moe_up with one group) whose output tiles
- * occupy at most half of the SMs cuts the K loop of every tile into up to 8 ranges computed by
- * different CTAs; fp32 partial tiles go through this workspace and the CTA that finishes a tile
- * last adds them and runs the same fused epilogue, so results differ from the unsplit launch only
- * by the order of the fp32 additions.  Off until a workspace is registered for the current
- * device; cd_splitk_workspace_bytes() is a size that suits every eligible call (a smaller one
- * turns splitting off for the calls it cannot hold).  The workspace is shared by all calls on
- * the device: launches that may split must be ordered on one stream (or by events), and the
- * memory must stay valid until cd_splitk_workspace_set(NULL, 0, stream) or the last launch has
- * finished.  `stream` orders the clearing of the workspace's counters. */
+ * projection whose output tiles would leave most SMs idle cuts the K loop of every tile into
+ * ranges computed by different CTAs, which then combine their fp32 partial tiles and run the same
+ * fused epilogue; results differ from the unsplit launch only by the order of the fp32 additions,
+ * and do not depend on timing.  Two forms:
+ *  - cluster form (cd_linear, cd_mu_qkv, cd_mu_proj; on by default, needs nothing from the
+ *    caller): 128-wide tiles, 2 or 4 ranges per tile computed by the CTAs of one thread-block
+ *    cluster, which exchange the partial tiles through distributed shared memory; each CTA
+ *    finishes a slice of the tile's columns.
+ *  - workspace form (also cd_moe_up with one group; up to 8 ranges): partial tiles go through a
+ *    caller-provided workspace and the CTA that finishes a tile last adds them.  Off until a
+ *    workspace is registered for the current device; cd_splitk_workspace_bytes() is a size that
+ *    suits every eligible call.  The workspace is shared by all calls on the device: launches
+ *    that may use it must be ordered on one stream (or by events), and the memory must stay valid
+ *    until cd_splitk_workspace_set(NULL, 0, stream) or the last launch has finished.  `stream`
+ *    orders the clearing of the workspace's counters.
+ * cd_splitk_config(flags) chooses the forms a launch may take (bit 0 cluster, bit 1 workspace;
+ * default 3; a negative argument only queries) and returns the previous flags. */
+int cd_splitk_config(int flags);
 size_t cd_splitk_workspace_bytes(void);
 int cd_splitk_workspace_set(void* workspace, size_t bytes, void* stream);
 /* Number of K ranges cd_linear (or cd_mu_proj; cd_mu_qkv with K = the sum of its two K extents)

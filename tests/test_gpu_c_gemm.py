@@ -466,67 +466,84 @@ def test_moe_up_pair_routed_and_shared_one_launch(T, H, I, Is, E, bn, empty):
 # ---- split-K of the few-row projections ---------------------------------------------------
 
 @pytest.fixture
-def split_k_off_then_on():
-    """Runs the test body with the workspace withdrawn first; the test switches it on itself."""
+def split_k_modes():
+    """Hands the test a switch over the forms of split-K (0 none, 1 cluster, 2 workspace) and
+    puts the default back afterwards."""
     from complexity_deep_b200 import ops
-    ops.split_k(False)
+    ops.split_k(True)                  # registers the workspace (used only under mode 2)
+    before = ops.split_k_config(-1)
     yield ops
-    ops.split_k(True)
+    ops.split_k_config(before)
+
+
+def _noise_bound(ref):
+    # one bf16 step at the value's size, plus the fp32 accumulation-order noise of the sum itself
+    return ref.abs() * 2.0 ** -7 + 1e-5 * float(ref.pow(2).mean().sqrt())
 
 
 @pytest.mark.parametrize("T,K,N,with_res", [(32, 4096, 2048, False), (128, 5632, 2048, True),
                                             (8, 3072, 1024, True), (100, 8192, 512, False),
-                                            (256, 4096, 1024, True), (17, 4096 + 64, 264, False)])
-def test_linear_split_k_matches_unsplit_and_fp32(split_k_off_then_on, T, K, N, with_res):
-    """The same call with and without the split-K workspace: both within the projection tolerance
-    of the fp32 product, and within fp32 accumulation-order noise (one bf16 rounding step of the
-    output at most) of each other; twice in a row, so a counter left non-zero would show."""
-    ops = split_k_off_then_on
+                                            (256, 4096, 1024, True), (17, 4096 + 64, 264, False),
+                                            (200, 6144, 1024, True), (32, 2048, 2048, True),
+                                            (32, 8192, 6144, True)])   # the last: two ranges per cluster
+def test_linear_split_k_forms_match_unsplit_and_fp32(split_k_modes, T, K, N, with_res):
+    """The same call unsplit, with the cluster form and with the workspace form of split-K: all
+    within the projection tolerance of the fp32 product and within fp32 accumulation-order noise
+    (one bf16 rounding step of the output at most) of each other; each form twice in a row, so
+    state left behind by a launch (a counter, a barrier phase) would show."""
+    ops = split_k_modes
     from complexity_deep_b200 import _lib
     lib = _lib.load()
     g = torch.Generator().manual_seed(T + K + N)
     x, w = _rand(g, T, K).cuda(), _rand(g, N, K, scale=0.05).cuda()
     res = _rand(g, T, N).cuda() if with_res else None
+    ref = x.float() @ w.float().t() + (res.float() if with_res else 0)
+    ops.split_k_config(0)
     assert lib.cd_splitk_ranges(T, K, N) == 1
     plain = ops.linear(x, w, res)
-    ops.split_k(True)
-    assert lib.cd_splitk_ranges(T, K, N) >= 2, "this shape is meant to split"
-    split1 = ops.linear(x, w, res)
-    split2 = ops.linear(x, w, res)
-    _fetch()
-    ref = x.float() @ w.float().t() + (res.float() if with_res else 0)
     _close(plain, ref)
-    _close(split1, ref)
-    assert torch.equal(split1, split2)                      # fixed order of the partial sums
-    # one bf16 step at the value's size, plus the fp32 accumulation-order noise of the sum itself
-    step = ref.abs() * 2.0 ** -7 + 1e-5 * float(ref.pow(2).mean().sqrt())
-    assert bool(((split1.float() - plain.float()).abs() <= step).all())
+    used = 0
+    for mode in (1, 2):
+        ops.split_k_config(mode)
+        ranges = lib.cd_splitk_ranges(T, K, N)
+        a = ops.linear(x, w, res)
+        b = ops.linear(x, w, res)
+        _fetch()
+        _close(a, ref)
+        assert torch.equal(a, b)                              # fixed order of the partial sums
+        assert bool(((a.float() - plain.float()).abs() <= _noise_bound(ref)).all()), mode
+        used += ranges > 1
+    assert used >= 1 or K < 3072, "this shape is meant to split in at least one form"
 
 
-def test_split_k_through_the_fused_epilogues(split_k_off_then_on):
+def test_split_k_through_the_fused_epilogues(split_k_modes):
     """Split-K in front of every fused epilogue a few-row call can take: the mu K-concatenation,
-    mu_proj's clamped bias and output clamp, the split-bf16 residual stream, and the dense SwiGLU."""
-    ops = split_k_off_then_on
-    ops.split_k(True)
+    mu_proj's clamped bias and output clamp, the split-bf16 residual stream (both forms), and the
+    dense SwiGLU (workspace form)."""
+    ops = split_k_modes
+    from complexity_deep_b200 import _lib
+    lib = _lib.load()
     g = torch.Generator().manual_seed(99)
     T, H = 48, 3072
     x, mu = _rand(g, T, H).cuda(), _rand(g, T, H).cuda()
     w, wm = _rand(g, 768, H, scale=0.05).cuda(), _rand(g, 768, H, scale=0.05).cuda()
-    out = ops.mu_qkv(x, mu, w, wm)
-    _close(out, F.linear(torch.cat([x, mu], -1).float(), torch.cat([w, wm], 1).float()))
-
     wp, mu_param = _rand(g, H, H, scale=0.05).cuda(), (_rand(g, H) * 3).cuda()
-    got = ops.mu_proj(x, wp, mu_param, -2.0, 2.0, out_clamp=(-1.5, 1.5))
-    want = (x.float() @ wp.float().t() + mu_param.float().clamp(-2.0, 2.0)).clamp(-1.5, 1.5)
-    _close(got, want)
-
     r_hi, r_lo = _split(torch.randn(T, H, generator=g))
-    hi, lo = ops.linear(x, wp, r_hi.cuda(), residual_lo=r_lo.cuda(), want_lo=True)
-    ref = x.float().cpu() @ wp.float().cpu().t() + r_hi.float() + r_lo.float()
-    _close(hi, ref)
-    pair_err = float((hi.float().cpu() + lo.float().cpu() - ref).abs().mean())
-    assert pair_err <= 2e-5 * max(1.0, float(ref.pow(2).mean().sqrt()))
-
+    ref_lin = x.float().cpu() @ wp.float().cpu().t() + r_hi.float() + r_lo.float()
+    for mode in (1, 2):
+        ops.split_k_config(mode)
+        assert lib.cd_splitk_ranges(T, 2 * H, 768) > 1
+        assert mode == 2 or lib.cd_splitk_ranges(T, H, H) > 1
+        out = ops.mu_qkv(x, mu, w, wm)
+        _close(out, F.linear(torch.cat([x, mu], -1).float(), torch.cat([w, wm], 1).float()))
+        got = ops.mu_proj(x, wp, mu_param, -2.0, 2.0, out_clamp=(-1.5, 1.5))
+        want = (x.float() @ wp.float().t() + mu_param.float().clamp(-2.0, 2.0)).clamp(-1.5, 1.5)
+        _close(got, want)
+        hi, lo = ops.linear(x, wp, r_hi.cuda(), residual_lo=r_lo.cuda(), want_lo=True)
+        _close(hi, ref_lin)
+        pair_err = float((hi.float().cpu() + lo.float().cpu() - ref_lin).abs().mean())
+        assert pair_err <= 2e-5 * max(1.0, float(ref_lin.pow(2).mean().sqrt())), mode
+    ops.split_k_config(2)
     for bn, I in ((64, 512), (128, 1024)):
         gate, up = _rand(g, I, H, scale=0.05), _rand(g, I, H, scale=0.05)
         packed = ops.pack_gate_up(gate[None].cuda(), up[None].cuda(), bn)
