@@ -36,8 +36,8 @@ EncodeTiledFn encode_tiled_fn() {
 
 // 2-D bf16 tensor [rows, cols] with `ld` elements between rows; box = [box_rows, 64 cols],
 // 128-byte swizzle (one box row = 128 bytes = one swizzle row), zero fill out of bounds.
-bool make_map(CUtensorMap* m, const void* base, long long rows, long long cols, long long ld,
-              int box_rows) {
+bool encode_map(CUtensorMap* m, const void* base, long long rows, long long cols, long long ld,
+                int box_rows) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return false;
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
@@ -48,6 +48,47 @@ bool make_map(CUtensorMap* m, const void* base, long long rows, long long cols, 
                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
+}
+
+// A tensor map is a pure function of (address, shape, stride, box), and an eager decode step
+// asks for the same ~1 000 of them every step (weights always, activations whenever the caller's
+// allocator hands the same buffers back), so each thread keeps the ones it has encoded in a small
+// direct-mapped table: a hit costs a hash and a 128-byte copy instead of a driver call.
+struct MapKey {
+  const void* base;
+  long long rows, cols, ld;
+  int box_rows;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+  }
+};
+struct MapSlot {
+  MapKey key;
+  bool used;
+  CUtensorMap map;
+};
+constexpr int kMapSlots = 2048;   // power of two
+
+bool make_map(CUtensorMap* m, const void* base, long long rows, long long cols, long long ld,
+              int box_rows) {
+  static thread_local MapSlot* table = nullptr;
+  if (!table) table = new MapSlot[kMapSlots]();   // lives as long as the thread
+  const MapKey key{base, rows, cols, ld, box_rows};
+  unsigned long long h = reinterpret_cast<uintptr_t>(base) >> 4;
+  h = (h ^ static_cast<unsigned long long>(rows) * 0x9E3779B97F4A7C15ull) * 0xff51afd7ed558ccdull;
+  h ^= static_cast<unsigned long long>(cols) * 0xc4ceb9fe1a85ec53ull + static_cast<unsigned long long>(ld) * 31 +
+       static_cast<unsigned long long>(box_rows);
+  h ^= h >> 29;
+  MapSlot& slot = table[h & (kMapSlots - 1)];
+  if (slot.used && slot.key == key) {
+    memcpy(m, &slot.map, sizeof(CUtensorMap));
+    return true;
+  }
+  if (!encode_map(m, base, rows, cols, ld, box_rows)) return false;
+  slot.key = key;
+  slot.used = true;
+  memcpy(&slot.map, m, sizeof(CUtensorMap));
+  return true;
 }
 
 struct DeviceInfo {
@@ -414,7 +455,11 @@ int launch_gemm(int M, int N, int num_groups, const int* seg_offsets, const Gemm
   p.seg_offsets = seg_offsets;
   p.b0_group_rows = op0.b_group_rows;
   p.b1_group_rows = op1 ? op1->b_group_rows : 0;
-  p.band = 16;
+  static const int forced_band = [] {   // CDEEP_BAND: m-tiles per scheduling band (tuning aid)
+    const char* e = getenv("CDEEP_BAND");
+    return e ? atoi(e) : 0;
+  }();
+  p.band = forced_band > 0 ? forced_band : 16;
   p.out = static_cast<__nv_bfloat16*>(epi.out);
   p.ldo = epi.ldo;
   p.out_cols = epi.out_cols;

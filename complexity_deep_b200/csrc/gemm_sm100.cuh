@@ -323,7 +323,9 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
   tc_fence_before();
   __syncthreads();
   constexpr bool kSplitK = (CG == 1 && BN <= 128);
-  const bool csk = kSplitK && kStore && p.splits > 1 && p.sk_cluster != 0;   // uniform over the launch
+  // the cluster form of split-K exists for 128-wide store tiles only (uniform over the launch)
+  constexpr bool kClusterSplitK = kSplitK && kStore && BN == 128;
+  const bool csk = kClusterSplitK && p.splits > 1 && p.sk_cluster != 0;
   if constexpr (CG == 2) cluster_sync_all();  // the peer's barriers exist before anyone signals them
   else if (csk) cluster_sync_all();
   tc_fence_after();
@@ -619,7 +621,8 @@ gemm_bf16_sm100_kernel(const __grid_constant__ CUtensorMap tmA0,
           // reads those columns of it).  Remote shared memory is read in whole 128-byte row
           // pieces: `cpr` lanes cover the slice of one row, a warp instruction covers 32 / cpr
           // rows (a lane-per-row pattern costs 32 remote transactions per instruction: 7 us).
-          const uint32_t cpr = static_cast<uint32_t>(BN / splits) >> 2;   // 16-byte chunks per row slice: 8 or 16
+          // 16-byte chunks per row slice: 8 or 16
+          const uint32_t cpr = kClusterSplitK ? (static_cast<uint32_t>(BN / splits) >> 2) : 8u;
           const uint32_t rpl = 32u / cpr;
           const uint32_t chunk = (static_cast<uint32_t>(sk_col_lo) >> 2) + (static_cast<uint32_t>(lane) % cpr);
           const uint32_t ring = smem_u32(smem);
