@@ -573,7 +573,9 @@ def moe_combine(h_shared: torch.Tensor, wd_shared: torch.Tensor,
 # switched off by the caller)
 _SPLIT_K_WS: dict = {}
 _SPLIT_K_ROWS = 512          # calls of more rows never qualify (their tiles fill the SMs)
-_SPLIT_K_AUTO = os.environ.get("CDEEP_SPLIT_K", "1") != "0"
+# the workspace form is opt-in (split_k(True), or CDEEP_SPLIT_K=1 for registration at first use): its
+# workspace is shared by every stream of the device; the cluster form needs none and is always on
+_SPLIT_K_AUTO = os.environ.get("CDEEP_SPLIT_K", "0") == "1"
 
 
 def split_k(enable: bool = True, device: Optional[torch.device] = None) -> None:
