@@ -62,6 +62,8 @@ SIGNATURES = {
     "cd_moe_down": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
                             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                             c_void_p]),
+    "cd_ep_plan": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_longlong, c_int, c_void_p,
+                           c_void_p, c_void_p, c_void_p]),
     "cd_push_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int,
                              c_int, c_void_p]),
     "cd_peer_barrier": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),

@@ -15,7 +15,7 @@ LIB_PATH = os.path.join(PKG_DIR, "libcdeep.so")
 # the checking build: same sources with -DCDEEP_CHECKS (device-side validation of indices that
 # kernels read from device memory; see include/cdeep.h, cd_checks_enabled)
 CHECKS_LIB_PATH = os.path.join(PKG_DIR, "libcdeep_checks.so")
-SOURCES = ["api.cu", "gemm.cu", "route.cu", "rowwise.cu", "attention_decode.cu", "attention_prefill.cu", "pack.cu"]
+SOURCES = ["api.cu", "gemm.cu", "route.cu", "rowwise.cu", "attention_decode.cu", "attention_prefill.cu", "pack.cu", "ep_plan.cu"]
 HEADERS = ["ptx.cuh", "checks.cuh", "gemm_sm100.cuh", "kernels.h", os.path.join("..", "..", "include", "cdeep.h")]
 
 

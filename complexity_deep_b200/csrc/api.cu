@@ -334,6 +334,26 @@ int cd_push_rows(const void* x, const int32_t* src_rows, const int32_t* offsets,
   return e == cudaSuccess ? CD_OK : cuda_fail(e, "push_rows launch");
 }
 
+int cd_ep_plan(const int32_t* counts, int world, int num_experts, int experts_per_rank, int rank,
+               const int64_t* ret_ptrs, int64_t row_bytes, int capacity, int32_t* push_base,
+               int32_t* seg_offsets, int64_t* row_ptrs, void* stream) {
+  if (!counts || !ret_ptrs || !push_base || !seg_offsets || !row_ptrs || capacity < 0 ||
+      row_bytes <= 0 || rank < 0 || rank >= world)
+    return CD_ERR_INVALID;
+  if (!ep_plan_supported(world, num_experts, experts_per_rank)) {
+    snprintf(g_cuda_err, sizeof(g_cuda_err),
+             "cd_ep_plan: %d ranks x %d experts (%d per rank) is outside what one launch holds",
+             world, num_experts, experts_per_rank);
+    return CD_ERR_UNSUPPORTED;
+  }
+  cudaError_t e = launch_ep_plan(counts, world, num_experts, experts_per_rank, rank,
+                                 reinterpret_cast<const long long*>(ret_ptrs), row_bytes, capacity,
+                                 push_base, seg_offsets, reinterpret_cast<long long*>(row_ptrs),
+                                 as_stream(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "ep_plan launch");
+  return CD_OK;
+}
+
 int cd_peer_barrier(const uint64_t* peer_flags, int32_t* flags, int rank, int world, int limit_ms,
                     void* stream) {
   if (!peer_flags || !flags || world < 1 || world > 64 || rank < 0 || rank >= world ||

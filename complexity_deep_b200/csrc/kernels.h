@@ -60,6 +60,13 @@ cudaError_t launch_qk_norm_rope(void* qkv, const void* q_w, const void* k_w, con
                                 long long kv_stride_b = 0, long long kv_stride_h = 0,
                                 long long kv_stride_t = 0, int capacity = 0);
 
+// exchange plan of the expert-parallel layer (ep_plan.cu)
+bool ep_plan_supported(int G, int E, int El);
+cudaError_t launch_ep_plan(const int* counts, int G, int E, int El, int rank,
+                           const long long* ret_ptrs, long long row_bytes, int capacity,
+                           int* push_base, int* seg_offsets, long long* row_ptrs,
+                           cudaStream_t stream);
+
 // split-K workspace of the current device (gemm.cu)
 size_t splitk_workspace_bytes();
 int splitk_workspace_set(void* ws, size_t bytes, cudaStream_t stream);

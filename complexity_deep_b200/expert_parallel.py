@@ -138,6 +138,11 @@ def push_plan_tensors(counts: torch.Tensor, rank: int, experts_per_rank: int,
     return push_base, seg_offsets, row_ptrs
 
 
+def plan_kernel_fits(world: int, num_experts: int) -> bool:
+    """Whether cd_ep_plan takes the count matrix of `world` ranks x `num_experts` experts."""
+    return world * num_experts <= 8192 and num_experts <= 2048
+
+
 def balanced_placement(expert_load, world: int) -> List[int]:
     """Longest-processing-time placement: experts in order of decreasing load each go to the
     rank with the smallest load so far that still has a free slot (E / world slots per rank).
@@ -332,8 +337,12 @@ class ExpertParallelMoE:
         dev = routing.counts.device
         all_counts = torch.empty(self.world, E, dtype=torch.int32, device=dev)
         dist.all_gather_into_tensor(all_counts, routing.counts, group=self.group)
-        out = push_plan_tensors(all_counts, self.rank, self.experts_per_rank, ctx.ret_ptrs,
-                                H * 2, recv.shape[0])
+        if plan_kernel_fits(self.world, E):
+            out = ops.ep_plan(all_counts, self.rank, self.experts_per_rank, ctx.ret_ptrs, H * 2,
+                              recv.shape[0])
+        else:   # more ranks x experts than one plan launch holds: the same arithmetic as tensor operations
+            out = push_plan_tensors(all_counts, self.rank, self.experts_per_rank, ctx.ret_ptrs,
+                                    H * 2, recv.shape[0])
         if len(ctx.plans) > 8:
             ctx.plans.clear()
         ctx.plans[key] = (routing,) + out

@@ -504,6 +504,25 @@ def push_rows(x_sorted: torch.Tensor, offsets: torch.Tensor, push_base: torch.Te
                                     peer_ptrs_dev, T, H, _stream()), "cd_push_rows")
 
 
+def ep_plan(all_counts: torch.Tensor, rank: int, experts_per_rank: int, ret_ptrs: torch.Tensor,
+            row_bytes: int, capacity: int):
+    """Exchange plan of the expert-parallel layer from the [ranks, E] count matrix, one launch
+    (cd_ep_plan): returns (push_base int32 [E], seg_offsets int32 [El + 1], row_ptrs int64 [capacity])."""
+    lib = _lib.load()
+    _need(all_counts, "counts of all ranks", torch.int32)
+    _need(ret_ptrs, "return buffer addresses", torch.int64)
+    G, E = all_counts.shape
+    dev = all_counts.device
+    push_base = torch.empty(E, dtype=torch.int32, device=dev)
+    seg_offsets = torch.empty(experts_per_rank + 1, dtype=torch.int32, device=dev)
+    row_ptrs = torch.empty(capacity, dtype=torch.int64, device=dev)
+    with _Span("ep_plan"):
+        _lib.check(lib.cd_ep_plan(all_counts.data_ptr(), G, E, experts_per_rank, rank,
+                                  ret_ptrs.data_ptr(), row_bytes, capacity, push_base.data_ptr(),
+                                  seg_offsets.data_ptr(), row_ptrs.data_ptr(), _stream()), "cd_ep_plan")
+    return push_base, seg_offsets, row_ptrs
+
+
 def peer_barrier(flag_ptrs: torch.Tensor, flags: torch.Tensor, rank: int, world: int,
                  limit_ms: int = 2000) -> None:
     """Cross-GPU barrier kernel (cd_peer_barrier); `flag_ptrs` int64 [world] addresses of the

@@ -287,6 +287,16 @@ int cd_moe_combine(const void* h_shared, int I_s, const void* wd_shared, const v
  * kernels that produce the rows.  The caller provides peer-mapped buffers, e.g. CUDA IPC or symmetric
  * memory, and orders the phases with a barrier across the GPUs.)
  *
+ * cd_ep_plan: the exchange plan of a routed batch in one launch, from the count matrix of all
+ * ranks (counts[g * num_experts + e] = rows of expert e among rank g's tokens; one all-gather of
+ * cd_route's counts).  Receive buffers are laid out expert-major, source-minor.  Outputs for THIS
+ * rank: push_base[num_experts] (see cd_push_rows), seg_offsets[experts_per_rank + 1] (segments of
+ * this rank's receive buffer, the seg_offsets of cd_moe_up / cd_moe_down_push) and
+ * row_ptrs[capacity] (out_row_ptrs of cd_moe_down_push: for received row r the address
+ * ret_ptrs[home] + (home's sorted offset of the row) * row_bytes in its home rank's return buffer;
+ * entries past the received rows are never used).  world * experts_per_rank == num_experts,
+ * world * num_experts <= 8192.
+ *
  * cd_push_rows: sorted row j (= x[src_rows[j]], or x[j] when src_rows is NULL) of expert e
  * (offsets[e] <= j < offsets[e+1]) is written to row push_base[e] + (j - offsets[e]) of the
  * buffer whose address is peer_ptrs[e / experts_per_rank] (device array of E /
@@ -308,6 +318,9 @@ int cd_moe_combine(const void* h_shared, int I_s, const void* wd_shared, const v
  * number of times; the launch arguments never change, so it can be captured in a CUDA graph. */
 int cd_peer_barrier(const uint64_t* peer_flags, int32_t* flags, int rank, int world, int limit_ms,
                     void* stream);
+int cd_ep_plan(const int32_t* counts, int world, int num_experts, int experts_per_rank, int rank,
+               const int64_t* ret_ptrs, int64_t row_bytes, int capacity, int32_t* push_base,
+               int32_t* seg_offsets, int64_t* row_ptrs, void* stream);
 int cd_push_rows(const void* x, const int32_t* src_rows, const int32_t* offsets,
                  const int32_t* push_base, int E, int experts_per_rank, const uint64_t* peer_ptrs,
                  int T, int H, void* stream);

@@ -81,3 +81,32 @@ def test_deterministic_bytes():
     b = _run(ids, table, 8)
     for x, y in zip(a, b):
         assert x.tobytes() == y.tobytes()
+
+
+@pytest.mark.parametrize("G,El,seed", [(4, 3, 1), (8, 4, 2), (2, 16, 3), (1, 8, 4), (8, 1, 5)])
+def test_ep_plan_kernel_equals_host_plan(G, El, seed):
+    """cd_ep_plan (one launch on the device) against the host arithmetic of the same plan, for
+    every rank: push bases, segment offsets and the return address of every received row are the
+    same integers; entries past the received rows follow the documented rule (last block)."""
+    import numpy as np
+    from complexity_deep_b200 import ops
+    from complexity_deep_b200.expert_parallel import push_plan, push_plan_tensors
+    rng = np.random.default_rng(seed)
+    E, H = G * El, 64
+    counts = rng.integers(0, 300, size=(G, E))
+    counts[rng.integers(0, G), rng.integers(0, E)] = 0
+    counts[:, rng.integers(0, E)] = 0                      # an expert nobody uses
+    ret_base = [1 << 33, *[(1 << 33) + 7000000 * i for i in range(1, G)]]
+    dev = torch.device("cuda:0")
+    c_dev = torch.from_numpy(counts).int().to(dev)
+    ptr_dev = torch.tensor(ret_base, dtype=torch.int64, device=dev)
+    for r in range(G):
+        pb, seg, received, ptrs = push_plan(counts, r, El, ret_base, H * 2)
+        cap = received + 37
+        kpb, kseg, kptrs = ops.ep_plan(c_dev, r, El, ptr_dev, H * 2, cap)
+        assert kpb.dtype == torch.int32 and kseg.dtype == torch.int32 and kptrs.dtype == torch.int64
+        assert np.array_equal(kpb.cpu().numpy(), pb)
+        assert np.array_equal(kseg.cpu().numpy(), seg)
+        assert np.array_equal(kptrs.cpu().numpy()[:received], ptrs)
+        _, _, tptrs = push_plan_tensors(c_dev, r, El, ptr_dev, H * 2, cap)
+        assert torch.equal(kptrs, tptrs)                   # the tail too
