@@ -62,6 +62,7 @@ SIGNATURES = {
     "cd_moe_down": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
                             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                             c_void_p]),
+    "cd_peer_put_i32": (c_int, [c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p]),
     "cd_ep_plan": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_longlong, c_int, c_void_p,
                            c_void_p, c_void_p, c_void_p]),
     "cd_push_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int,

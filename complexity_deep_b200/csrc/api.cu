@@ -354,6 +354,14 @@ int cd_ep_plan(const int32_t* counts, int world, int num_experts, int experts_pe
   return CD_OK;
 }
 
+int cd_peer_put_i32(const int32_t* src, int n, const uint64_t* peer_bufs, int world, int64_t offset,
+                    void* stream) {
+  if (!src || !peer_bufs || n < 0 || world < 1 || world > 64 || offset < 0) return CD_ERR_INVALID;
+  cudaError_t e = launch_peer_put_i32(src, n, reinterpret_cast<const unsigned long long*>(peer_bufs),
+                                      world, offset, as_stream(stream));
+  return e == cudaSuccess ? CD_OK : cuda_fail(e, "peer_put launch");
+}
+
 int cd_peer_barrier(const uint64_t* peer_flags, int32_t* flags, int rank, int world, int limit_ms,
                     void* stream) {
   if (!peer_flags || !flags || world < 1 || world > 64 || rank < 0 || rank >= world ||

@@ -86,7 +86,25 @@ ep_plan_kernel(const int* __restrict__ counts, int G, int E, int El, int rank,
   }
 }
 
+// Copies n int32 from src into every rank's buffer at element offset `offset` (block g writes to
+// rank g; the buffers are peer-mapped).  With offset = rank * n every rank ends up holding the
+// rows of all ranks: an all-gather of a few hundred bytes by plain peer stores, made visible by the
+// cross-GPU barrier that follows it on the stream.
+__global__ void __launch_bounds__(128)
+peer_put_kernel(const int* __restrict__ src, int n, const unsigned long long* __restrict__ peer_bufs,
+                long long offset) {
+  int* dst = reinterpret_cast<int*>(peer_bufs[blockIdx.x]) + offset;
+  for (int i = threadIdx.x; i < n; i += 128) dst[i] = src[i];
+}
+
 }  // namespace
+
+cudaError_t launch_peer_put_i32(const int* src, int n, const unsigned long long* peer_bufs, int world,
+                                long long offset, cudaStream_t stream) {
+  if (n <= 0) return cudaSuccess;
+  peer_put_kernel<<<world, 128, 0, stream>>>(src, n, peer_bufs, offset);
+  return cudaGetLastError();
+}
 
 bool ep_plan_supported(int G, int E, int El) {
   return G >= 1 && El >= 1 && G * El == E && G * E <= kPlanMaxCounts && El * G <= kPlanMaxBlocks;

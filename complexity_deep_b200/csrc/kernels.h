@@ -67,6 +67,9 @@ cudaError_t launch_ep_plan(const int* counts, int G, int E, int El, int rank,
                            int* push_base, int* seg_offsets, long long* row_ptrs,
                            cudaStream_t stream);
 
+cudaError_t launch_peer_put_i32(const int* src, int n, const unsigned long long* peer_bufs, int world,
+                                long long offset, cudaStream_t stream);
+
 // split-K workspace of the current device (gemm.cu)
 size_t splitk_workspace_bytes();
 int splitk_workspace_set(void* ws, size_t bytes, cudaStream_t stream);

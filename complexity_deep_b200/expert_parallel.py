@@ -178,6 +178,9 @@ class _PeerContext:
         self.flags = None        # this rank's barrier signal pad, int32 [1 + world] (symmetric)
         self.flag_ptrs = None    # int64 [world]: every rank's pad as seen from this GPU
         self.plans = {}
+        self.counts = None       # int32 [2, world, E] (symmetric): count matrices of the last two batches
+        self.count_ptrs = None   # int64 [world]: every rank's counts buffer as seen from this GPU
+        self.count_seq = 0       # batches planned so far (selects the slot; the same on every rank)
 
     @classmethod
     def get(cls, key):
@@ -308,6 +311,14 @@ class ExpertParallelMoE:
             ctx.buffers = (recv, ret, recv_h, ret_h)
             ctx.ret_ptrs = torch.tensor([int(p) for p in ret_h.buffer_ptrs], dtype=torch.int64,
                                         device=device)
+            # two slots of [world, E] counts: the all-gather of a batch's counts by peer stores
+            E = self.mlp.num_experts
+            counts = symm_mem.empty(2 * self.world * E, dtype=torch.int32, device=device)
+            counts.zero_()
+            counts_h = symm_mem.rendezvous(counts, group=group)
+            ctx.counts, ctx.counts_handle = counts, counts_h
+            ctx.count_ptrs = torch.tensor([int(p) for p in counts_h.buffer_ptrs], dtype=torch.int64,
+                                          device=device)
             ctx.flags, ctx.flags_handle = flags, flags_h
             ctx.flag_ptrs = torch.tensor([int(p) for p in flags_h.buffer_ptrs], dtype=torch.int64,
                                          device=device)
@@ -325,8 +336,8 @@ class ExpertParallelMoE:
 
     def peer_plan_for(self, routing: ops.Routing, H: int):
         """Exchange plan of a routed batch for the peer-store exchange, computed on the device
-        from one small all-gather of the counts (no device->host copy); cached per batch and
-        shared by all layers of the context."""
+        from the count rows of all ranks (gathered by peer stores: no collective library call,
+        no device->host copy); cached per batch and shared by all layers of the context."""
         recv, ret, recv_h, ret_h = self._peer_buffers(H, routing.counts.device)
         ctx = self._peer_context(H)
         key = id(routing)
@@ -335,8 +346,15 @@ class ExpertParallelMoE:
             return hit[1:]
         E = self.mlp.num_experts
         dev = routing.counts.device
-        all_counts = torch.empty(self.world, E, dtype=torch.int32, device=dev)
-        dist.all_gather_into_tensor(all_counts, routing.counts, group=self.group)
+        # all-gather of the counts by peer stores: every rank writes its row into every rank's
+        # buffer, the barrier makes the rows visible.  Slots alternate; a rank can only be one
+        # batch ahead of another (the later barriers of the layer hold it), so a row is never
+        # overwritten while a peer's plan kernel may still read it.
+        slot = ctx.count_seq & 1
+        ctx.count_seq += 1
+        ops.peer_put_i32(routing.counts, ctx.count_ptrs, self.world, (slot * self.world + self.rank) * E)
+        self._barrier(H)
+        all_counts = ctx.counts[slot * self.world * E:(slot + 1) * self.world * E].view(self.world, E)
         if plan_kernel_fits(self.world, E):
             out = ops.ep_plan(all_counts, self.rank, self.experts_per_rank, ctx.ret_ptrs, H * 2,
                               recv.shape[0])

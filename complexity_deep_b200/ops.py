@@ -504,6 +504,17 @@ def push_rows(x_sorted: torch.Tensor, offsets: torch.Tensor, push_base: torch.Te
                                     peer_ptrs_dev, T, H, _stream()), "cd_push_rows")
 
 
+def peer_put_i32(src: torch.Tensor, peer_bufs: torch.Tensor, world: int, offset: int) -> None:
+    """Stores the int32 vector `src` at element `offset` of every rank's (peer-mapped) buffer
+    (cd_peer_put_i32); visible to the peers after the next peer_barrier."""
+    lib = _lib.load()
+    _need(src, "src", torch.int32)
+    _need(peer_bufs, "peer buffer addresses", torch.int64)
+    with _Span("peer_put"):
+        _lib.check(lib.cd_peer_put_i32(src.data_ptr(), src.numel(), peer_bufs.data_ptr(), world,
+                                       int(offset), _stream()), "cd_peer_put_i32")
+
+
 def ep_plan(all_counts: torch.Tensor, rank: int, experts_per_rank: int, ret_ptrs: torch.Tensor,
             row_bytes: int, capacity: int):
     """Exchange plan of the expert-parallel layer from the [ranks, E] count matrix, one launch

@@ -287,6 +287,11 @@ int cd_moe_combine(const void* h_shared, int I_s, const void* wd_shared, const v
  * kernels that produce the rows.  The caller provides peer-mapped buffers, e.g. CUDA IPC or symmetric
  * memory, and orders the phases with a barrier across the GPUs.)
  *
+ * cd_peer_put_i32: copies n int32 from src to element offset `offset` of the buffer of EVERY
+ * rank (peer_bufs: device array of the world buffers' addresses as seen from this GPU).  With
+ * offset = rank * n, followed by cd_peer_barrier, it is an all-gather of a small table (the
+ * counts of cd_route) without a collective library call.
+ *
  * cd_ep_plan: the exchange plan of a routed batch in one launch, from the count matrix of all
  * ranks (counts[g * num_experts + e] = rows of expert e among rank g's tokens; one all-gather of
  * cd_route's counts).  Receive buffers are laid out expert-major, source-minor.  Outputs for THIS
@@ -317,6 +322,8 @@ int cd_moe_combine(const void* h_shared, int I_s, const void* wd_shared, const v
  * GPU that left the group cannot leave the others spinning.  All GPUs must call it the same
  * number of times; the launch arguments never change, so it can be captured in a CUDA graph. */
 int cd_peer_barrier(const uint64_t* peer_flags, int32_t* flags, int rank, int world, int limit_ms,
+                    void* stream);
+int cd_peer_put_i32(const int32_t* src, int n, const uint64_t* peer_bufs, int world, int64_t offset,
                     void* stream);
 int cd_ep_plan(const int32_t* counts, int world, int num_experts, int experts_per_rank, int rank,
                const int64_t* ret_ptrs, int64_t row_bytes, int capacity, int32_t* push_base,
