@@ -110,3 +110,24 @@ def test_ep_plan_kernel_equals_host_plan(G, El, seed):
         assert np.array_equal(kptrs.cpu().numpy()[:received], ptrs)
         _, _, tptrs = push_plan_tensors(c_dev, r, El, ptr_dev, H * 2, cap)
         assert torch.equal(kptrs, tptrs)                   # the tail too
+
+
+def test_peer_put_places_a_row_in_every_buffer():
+    """cd_peer_put_i32 with the 'peers' being three buffers of this GPU: each gets the row at
+    the given element offset and nothing else is touched; used with offset = rank * n it makes
+    every rank hold the rows of all ranks (the counts of the expert-parallel plan)."""
+    from complexity_deep_b200 import ops
+    dev = torch.device("cuda:0")
+    world, n = 3, 40
+    bufs = [torch.full((2 * world * n,), -7, dtype=torch.int32, device=dev) for _ in range(world)]
+    ptrs = torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64, device=dev)
+    rows = [torch.arange(n, dtype=torch.int32, device=dev) * (r + 1) + 1000 * r for r in range(world)]
+    for slot in (0, 1):
+        for r in range(world):      # what rank r would do
+            ops.peer_put_i32(rows[r] + slot, ptrs, world, (slot * world + r) * n)
+    torch.cuda.synchronize()
+    for b in bufs:
+        got = b.view(2, world, n)
+        for slot in (0, 1):
+            for r in range(world):
+                assert torch.equal(got[slot, r], rows[r] + slot)
