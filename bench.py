@@ -356,6 +356,12 @@ def run_ours(args):
     del graph, model
     torch.cuda.empty_cache()
     if not args.no_layer_records:
+        # The layer records are short measurements (tens of ms) quoted against the BURST peak, like
+        # `bench.py --workload moe_layer / ep_layer` run alone.  Straight after the prefill loops the
+        # GPUs are still in the power-capped state of a long run (and not all to the same degree,
+        # which the layer's cross-GPU barriers then pay as skew): 7.0 instead of 5.6 ms per layer
+        # measured on 4 GPUs.  A pause lets them leave that state; the record carries its SM clock.
+        time.sleep(2.0)
         # second half of the metric, in the same run and process group: the isolated MoE layer on
         # one GPU, the expert-parallel scale-out layer (peer-store exchange) on several
         if world == 1:
@@ -377,7 +383,7 @@ def compact_layer_record(rec: dict) -> dict:
     """The figures of a layer workload that travel inside the prefill line."""
     keep = ("value", "unit", "ms_per_step", "ms_per_step_routing_cached", "tflops_routing_cached",
             "frac_of_peak", "frac_of_peak_routing_cached", "peak_source", "tokens_per_s", "parity",
-            "rows_received_per_gpu", "kernels")
+            "rows_received_per_gpu", "clocks", "kernels")
     out = {k: rec[k] for k in keep if rec.get(k) is not None}
     out["config"] = {k: rec["config"][k] for k in ("workload", "T", "H", "E", "I_e", "I_s",
                                                    "parallelism", "tokens_per_gpu", "flop_per_step")}

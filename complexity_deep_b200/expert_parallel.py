@@ -327,12 +327,12 @@ class ExpertParallelMoE:
             dist.barrier(group=group)
         return ctx.buffers
 
-    def _barrier(self, H: int) -> None:
+    def _barrier(self, H: int, tag: str = "peer_barrier") -> None:
         """Cross-GPU barrier between two phases of the peer exchange (cd_peer_barrier): a
         bounded device-side wait that raises the library's status word instead of spinning
         forever when a rank never arrives."""
         ctx = self._peer_context(H)
-        ops.peer_barrier(ctx.flag_ptrs, ctx.flags, self.rank, self.world, self.barrier_limit_ms)
+        ops.peer_barrier(ctx.flag_ptrs, ctx.flags, self.rank, self.world, self.barrier_limit_ms, tag)
 
     def peer_plan_for(self, routing: ops.Routing, H: int):
         """Exchange plan of a routed batch for the peer-store exchange, computed on the device
@@ -353,7 +353,7 @@ class ExpertParallelMoE:
         slot = ctx.count_seq & 1
         ctx.count_seq += 1
         ops.peer_put_i32(routing.counts, ctx.count_ptrs, self.world, (slot * self.world + self.rank) * E)
-        self._barrier(H)
+        self._barrier(H, "peer_barrier_counts")
         all_counts = ctx.counts[slot * self.world * E:(slot + 1) * self.world * E].view(self.world, E)
         if plan_kernel_fits(self.world, E):
             out = ops.ep_plan(all_counts, self.rank, self.experts_per_rank, ctx.ret_ptrs, H * 2,
@@ -395,7 +395,7 @@ class ExpertParallelMoE:
             packed_s, bn_s = mlp._packed_shared(T)
             h_s = ops.moe_up(x_sorted, None, 1, packed_s, mlp.shared_gate.weight.shape[0], bn_s)
             wd_s = mlp.shared_down.weight.detach()
-        self._barrier(H)                   # all pushes visible; also: peers are done reading `ret`
+        self._barrier(H, "peer_barrier_dispatch")   # all pushes visible; also: peers are done reading `ret`
         # The number of received rows is only known on the device: the GEMMs are launched over
         # the whole buffer and schedule tiles from `seg` (device), so rows past the last segment
         # are never touched.
@@ -403,7 +403,7 @@ class ExpertParallelMoE:
                          mlp.expert_intermediate_size, self.block_n)
         # the epilogue stores every finished row in its home GPU's return buffer
         ops.moe_down_push(h_r, self.down_local, seg, self.experts_per_rank, row_ptrs)
-        self._barrier(H)                   # all routed rows are home; peers are done reading `recv`
+        self._barrier(H, "peer_barrier_return")     # all routed rows are home; peers are done reading `recv`
         y_sorted = ret[:T]
         if h_s is not None:
             return ops.moe_combine(h_s, wd_s, y_sorted, routing.perm, residual, residual_lo, want_lo)

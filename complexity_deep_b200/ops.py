@@ -535,7 +535,7 @@ def ep_plan(all_counts: torch.Tensor, rank: int, experts_per_rank: int, ret_ptrs
 
 
 def peer_barrier(flag_ptrs: torch.Tensor, flags: torch.Tensor, rank: int, world: int,
-                 limit_ms: int = 2000) -> None:
+                 limit_ms: int = 2000, tag: str = "peer_barrier") -> None:
     """Cross-GPU barrier kernel (cd_peer_barrier); `flag_ptrs` int64 [world] addresses of the
     ranks' signal pads, `flags` this rank's pad (int32 [>= 1 + world])."""
     lib = _lib.load()
@@ -543,7 +543,7 @@ def peer_barrier(flag_ptrs: torch.Tensor, flags: torch.Tensor, rank: int, world:
     _need(flags, "flags", torch.int32)
     if flag_ptrs.numel() != world or flags.numel() < 1 + world:
         raise RuntimeError("signal pad too small for the group")
-    with _Span("peer_barrier"):
+    with _Span(tag):
         _lib.check(lib.cd_peer_barrier(flag_ptrs.data_ptr(), flags.data_ptr(), rank, world,
                                        int(limit_ms), _stream()), "cd_peer_barrier")
 
