@@ -3,7 +3,7 @@
 // token_routed_mlp.py:166-170 and the grouped expert GEMMs when the experts live on other GPUs).
 //
 // Input: the count matrix of all ranks, counts[g][e] = rows of expert e among rank g's tokens
-// (one small all-gather).  Receive buffers are laid out expert-major, source-minor — the order
+// (gathered by peer_put_kernel below and the cross-GPU barrier, or by any all-gather).  Receive buffers are laid out expert-major, source-minor — the order
 // the grouped GEMM wants — so for THIS rank the kernel derives
 //   push_base[e]    row in the owner's receive buffer where this rank's rows of expert e start
 //                   (the owner's segment start of e plus the rows of lower-ranked sources),
