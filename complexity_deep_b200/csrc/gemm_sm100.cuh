@@ -33,11 +33,12 @@ constexpr int kBlockM = 128;       // rows per tile = TMEM lanes
 constexpr int kBoxK = 64;          // bf16 elements per TMA box row = one 128-byte swizzle row
 // Boxes per operand and pipeline stage.  The thread that issues the MMAs pays a fixed price per
 // stage (barrier wait, fence, commit: about 300 cycles measured) on top of 40 .. 64 cycles per
-// tcgen05.mma of a tile up to 128 columns wide, so the narrow tiles of few-row calls, whose K loop
-// is bound by that thread, take two boxes (128 elements of K) per stage: 0.29 -> 0.21 us per 64
-// elements of K.  Wide tiles are bound by the tensor pipe and want many fine stages instead
-// (with two boxes the 1B prefill step was 5 % slower).
-__host__ __device__ constexpr int gemm_k_boxes(int bn, int cg) { return (cg == 1 && bn <= 64) ? 2 : 1; }
+// tcgen05.mma of a tile up to 128 columns wide, so the single-CTA tiles up to 128 wide — few-row
+// calls, whose K loop is bound by that thread — take two boxes (128 elements of K) per stage:
+// 0.29 -> 0.21 us per 64 elements of K for 32-wide tiles; for 128-wide tiles (grouped few-row
+// calls, the cluster form of split-K) the gain is a few per cent.  256-wide tiles are bound by the
+// tensor pipe and want many fine stages instead (with two boxes the 1B prefill step was 5 % slower).
+__host__ __device__ constexpr int gemm_k_boxes(int bn, int cg) { return (cg == 1 && bn <= 128) ? 2 : 1; }
 constexpr int kUmmaK = 16;         // K of one tcgen05.mma for 16-bit inputs
 constexpr int kMaxGroups = 128;
 constexpr int kEpiCols = 64;          // output columns per epilogue sub-tile (128 bytes of bf16)
