@@ -381,7 +381,9 @@ def run_ours(args):
 
 def compact_layer_record(rec: dict) -> dict:
     """The figures of a layer workload that travel inside the prefill line."""
-    keep = ("value", "unit", "ms_per_step", "ms_per_step_routing_cached", "tflops_routing_cached",
+    keep = ("value", "unit", "ms_per_step", "ms_per_step_eager", "forward", "replay_equals_eager",
+            "ms_per_step_routing_cached",
+            "tflops_routing_cached",
             "frac_of_peak", "frac_of_peak_routing_cached", "peak_source", "tokens_per_s", "parity",
             "rows_received_per_gpu", "clocks", "kernels")
     out = {k: rec[k] for k in keep if rec.get(k) is not None}
@@ -641,9 +643,57 @@ def layer_record(args, workload, dist, dev, rank, world, local_rank):
     clocks = sampler.stop()
     prof = ops.PROFILE.collect()
     ops.PROFILE.reset(enabled=False)
+    # The same steps replayed from a CUDA graph of the layer (dispatch, exchange plan and barriers
+    # included: they all take their sizes from device memory), new ids copied into the captured
+    # id buffer before every replay: the figure of the layer without the interpreter's launch
+    # overhead, which with several processes per host otherwise shows up as skew at the layer's
+    # first cross-GPU barrier.  All ranks take the replay or none does.
+    ms_eager, forward = ms, "eager"
+    y_replayed = None
+    if args.graph:
+        graph_ok = torch.ones(1, device=dev)
+        g = None
+        try:
+            static_ids = ids[0].clone()
+
+            @torch.no_grad()
+            def step_static():
+                if w_qkv is not None:
+                    ops.mu_qkv(x, mu_prev, w_qkv, w_mu)
+                if ep is not None:
+                    return ep.forward(x.view(1, t_loc, H), static_ids.view(1, t_loc))
+                return mlp(x.view(1, t_loc, H), static_ids.view(1, t_loc))
+
+            static_ids.copy_(ids[1])          # a new version of the buffer: the capture includes the dispatch
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                y_static = step_static()
+        except Exception as exc:              # noqa: BLE001 - any capture problem means the eager figure stands
+            print(f"[bench] {workload}: CUDA-graph capture failed ({exc}); keeping the eager figure",
+                  file=sys.stderr)
+            graph_ok.zero_()
+            g = None
+        if dist is not None:
+            dist.all_reduce(graph_ok, op=dist.ReduceOp.MIN)
+        if bool(graph_ok.item() > 0) and g is not None:
+            for i in range(args.warmup):
+                static_ids.copy_(ids[i])
+                g.replay()
+            barrier()
+            t0.record()
+            for i in range(args.warmup, steps_total):
+                static_ids.copy_(ids[i])
+                g.replay()
+            t1.record()
+            barrier()
+            ms = aggregate_ms(t0.elapsed_time(t1), dist, dev)
+            forward = "cuda_graph_replay of the layer step, new ids copied into the captured buffer every step"
+            y_replayed = y_static.clone()     # output of the last replay: ids[-1]
     # the same layer on an id batch whose dispatch (and exchange plan) is already cached, as
-    # layers 2..L of a forward pass see it
-    y = step(steps_total - 1)
+    # layers 2..L of a forward pass see it (three untimed steps first: the allocator's blocks
+    # settle again after the graph replays, which live in their own pool)
+    for _ in range(3):
+        y = step(steps_total - 1)
     barrier()
     t0.record()
     for _ in range(args.steps):
@@ -652,6 +702,8 @@ def layer_record(args, workload, dist, dev, rank, world, local_rank):
     barrier()
     ms_cached = aggregate_ms(t0.elapsed_time(t1), dist, dev)
     ops.status_fetch()
+    # the replayed step and the eager step saw the same ids last: same bits expected
+    replay_equal = None if y_replayed is None else bool(torch.equal(y_replayed, y))
 
     # parity: sampled rows of THIS rank's output against the fp32 oracle of the unsharded layer
     # on the same bf16-rounded weights and inputs; the worst rank is reported
@@ -686,6 +738,8 @@ def layer_record(args, workload, dist, dev, rank, world, local_rank):
         "metric": "MoE-layer TFLOP/s (bf16)", "value": round(tflops, 1), "unit": "TFLOP/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms / args.steps, 4),
+        "ms_per_step_eager": round(ms_eager / args.steps, 4), "forward": forward,
+        "replay_equals_eager": replay_equal,
         "ms_per_step_routing_cached": round(ms_cached / args.steps, 4),
         "tflops_routing_cached": round(flop * args.steps / (ms_cached / 1e3) / 1e12, 1),
         "higher_is_better": True, "scaling": "strong",
